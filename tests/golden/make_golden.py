@@ -1,0 +1,98 @@
+"""Regenerate ``tests/golden/reference_golden.npz`` by importing the reference's own Python on CPU.
+
+Run once where a checkout of the reference is available:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+It calls only pure-Python/torch-CPU functions of the reference (no GPU, no Triton launch): ``dequantize``, ``split_k``,
+``bucket``, ``packed_shape``, ``input_slice``, ``max_items``, ``output_rows`` and ``sum_rank_partials``.  The outputs are
+small and committed; the tests compare the CPU oracle (and, on a GPU, the kernels) against them, so nothing at test time
+needs the reference.
+"""
+
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+
+def main(ref: str) -> None:
+    sys.path.insert(0, str(Path(ref) / "src"))
+    from tensorfold.cuda import experts as r_experts
+    from tensorfold.cuda.kernels import affine as r_affine
+    from tensorfold.cuda.kernels import qmm as r_qmm
+    from tensorfold.families.qwen3_5.cuda import distributed as r_dist
+    from tensorfold.families.qwen3_5.cuda import qmm as r_lane
+
+    out: dict[str, np.ndarray] = {}
+    g = torch.Generator().manual_seed(20240611)
+
+    # dequantize for every bits x group: 5 rows of 4 groups, raw 32-bit words so every straddle pattern occurs
+    for bits in r_affine.BITS:
+        for gs in r_affine.GROUPS:
+            n, k = 5, gs * 4
+            words = torch.randint(-(2 ** 31), 2 ** 31 - 1, (n, k * bits // 32), generator=g, dtype=torch.int64)
+            words = words.to(torch.int32)
+            scales = (torch.rand((n, 4), generator=g) * 0.02 + 0.001).to(torch.bfloat16)
+            biases = (torch.randn((n, 4), generator=g) * 0.05).to(torch.bfloat16)
+            deq = r_lane.dequantize(words, scales, biases, bits=bits, gs=gs)
+            tag = f"deq_b{bits}_g{gs}"
+            out[tag + "_words"] = words.numpy()
+            out[tag + "_scales"] = scales.view(torch.int16).numpy().view(np.uint16)
+            out[tag + "_biases"] = biases.view(torch.int16).numpy().view(np.uint16)
+            out[tag + "_w"] = deq.numpy()
+            assert r_affine.packed_shape(words.shape, scales.shape, biases.shape, bits, gs) == (n, k)
+
+    # shape-only planning functions
+    shapes = [(4096, 4096), (6144, 5120), (1024, 5120), (5120, 6144), (17408, 5120), (5120, 17408), (14336, 4096),
+              (6144, 8192), (48, 5120), (200, 1024), (1536, 2048), (248320, 5120), (2688, 1856), (1856, 2688),
+              (10240, 5120), (64, 512), (128, 1024)]
+    out["split_k_shapes"] = np.asarray(shapes, dtype=np.int64)
+    out["split_k_g64"] = np.asarray([r_qmm.split_k(n, k, 64) for n, k in shapes], dtype=np.int64)
+    out["split_k_g32"] = np.asarray([r_qmm.split_k(n, k, 32) for n, k in shapes], dtype=np.int64)
+    out["split_k_g64_t296"] = np.asarray([r_qmm.split_k(n, k, 64, 296) for n, k in shapes], dtype=np.int64)
+    ms = [1, 2, 7, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 128, 2048]
+    out["bucket_m"] = np.asarray(ms, dtype=np.int64)
+    out["bucket"] = np.asarray([r_qmm.bucket(m) for m in ms], dtype=np.int64)
+
+    # two-rank input slices for every format (k = 4 groups)
+    rows = []
+    for bits in r_affine.BITS:
+        for gs in r_affine.GROUPS:
+            for rank in (0, 1):
+                (a, b), (g0, g1) = r_affine.input_slice(gs * 4, bits, gs, rank)
+                rows.append([bits, gs, rank, a, b, g0, g1])
+    out["input_slice"] = np.asarray(rows, dtype=np.int64)
+
+    # expert plan capacity
+    cases = [(96, 129, 16), (112, 129, 16), (12288, 129, 64), (14336, 129, 64), (7, 50, 16), (161, 50, 16), (2100, 50, 64)]
+    out["max_items_cases"] = np.asarray(cases, dtype=np.int64)
+    out["max_items"] = np.asarray([r_experts.max_items(*c) for c in cases], dtype=np.int64)
+
+    # partition map: plain halves, segments (k, k, v) and head blocks
+    out["rows_plain_r0"] = r_dist.output_rows(16, 0).numpy()
+    out["rows_plain_r1"] = r_dist.output_rows(16, 1).numpy()
+    out["rows_seg_r0"] = r_dist.output_rows(40, 0, segments=(8, 8, 24)).numpy()
+    out["rows_seg_r1"] = r_dist.output_rows(40, 1, segments=(8, 8, 24)).numpy()
+    out["rows_block_r1"] = r_dist.output_rows(32, 1, block=8).numpy()
+
+    # rank-ordered sum: fp32 add, one rounding
+    p0 = torch.randn((7, 33), generator=g) * 3
+    p1 = torch.randn((7, 33), generator=g) * 3
+    out["rank_p0"], out["rank_p1"] = p0.numpy(), p1.numpy()
+    out["rank_sum_bf16"] = r_dist.sum_rank_partials([p0, p1]).view(torch.int16).numpy().view(np.uint16)
+
+    # expert-table unpack nibble rule (cuda/experts.py:52-53): slot s of a block word holds input 2 (s % 4) + s // 4
+    out["expert_slot_inputs"] = np.asarray([2 * (s % 4) + s // 4 for s in range(8)], dtype=np.int64)
+    out["lane_offsets"] = np.asarray(r_qmm.OFFSETS, dtype=np.int64)
+
+    dest = Path(__file__).with_name("reference_golden.npz")
+    np.savez_compressed(dest, **out)
+    print(f"wrote {dest} ({dest.stat().st_size} bytes, {len(out)} arrays)")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
