@@ -1,0 +1,351 @@
+"""Headline benchmark: affine 4-bit / group-64 quantized matmul weight GB/s on the dense-27B projections.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--rows M] [--impl b200|reference]
+
+A step is one pass of the hot path over one decoder layer's seven projections (q, k, v, o, gate, up, down; 191.6 MB of
+packed weights) at M rows (default 16: the speculative-verify shape).  Steps cycle through a ring of distinct layer
+weights larger than L2, so every pass streams its weights from HBM.  One JSON line is printed by rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+BITS, GS = 4, 64
+FALLBACK_HBM_GBS = 6650.0
+L2_BYTES = 126 * 2 ** 20
+
+
+def weight_bytes(n: int, k: int, bits: int = BITS, gs: int = GS) -> int:
+    return n * k * bits // 8 + 4 * n * k // gs
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 100 ms while the measurement runs (read-only)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        return False
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], 0.0, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = max(mx, float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def layer_shapes():
+    from tensorfold_b200 import synthetic
+
+    return list(synthetic.DENSE_27B.items())
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# the reference arm and the CPU baseline: the oracle's restatement of the reference's CPU path, on the host cores
+# ----------------------------------------------------------------------------------------------------------------------
+
+SAMPLE = ("q_proj", "k_proj", "v_proj", "o_proj")        # attention projections: 41.3 MB of packed weights a step
+
+
+def cpu_pass(inputs, rows: int) -> None:
+    """One pass of the CPU restatement (dequantise to float32 then x.float() @ w.T, all host threads) over the sample."""
+
+    from oracle import native
+
+    for words, s_bits, b_bits, x_bits in inputs:
+        native.qmm_f32(x_bits[:rows], words, s_bits, b_bits, GS, BITS)
+
+
+def cpu_inputs(rows: int):
+    from tensorfold_b200 import synthetic
+
+    out = []
+    for name in SAMPLE:
+        n, k = synthetic.DENSE_27B[name]
+        words, scales, biases = synthetic.affine_weight(n, k, BITS, GS, seed=len(out))
+        x = synthetic.activations(rows, k, len(out))
+        out.append((words.numpy(), synthetic.bf16_bits(scales), synthetic.bf16_bits(biases), synthetic.bf16_bits(x)))
+    return out
+
+
+def sample_bytes() -> int:
+    from tensorfold_b200 import synthetic
+
+    return sum(weight_bytes(*synthetic.DENSE_27B[name]) for name in SAMPLE)
+
+
+def cpu_baseline(rows: int, budget_s: float = 15.0) -> dict:
+    from oracle import native
+
+    inputs = cpu_inputs(rows)
+    cpu_pass(inputs, rows)                               # warm the pages
+    t0, reps = time.perf_counter(), 0
+    while reps < 3 or (time.perf_counter() - t0 < budget_s and reps < 50):
+        cpu_pass(inputs, rows)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": sample_bytes() / dt / 1e9, "unit": "GB/s", "cores": native.threads(), "kind": "port",
+            "sample": f"q/k/v/o projections of one dense-27B layer at M={rows} ({sample_bytes() / 1e6:.1f} MB of packed "
+                      f"weights), {reps} passes of oracle/affine_ref.c (dequantise to float32, float32 dot, OpenMP)"}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import native
+
+    inputs = cpu_inputs(args.rows)
+    for _ in range(min(args.warmup, 2)):
+        cpu_pass(inputs, args.rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_pass(inputs, args.rows)
+    dt = time.perf_counter() - t0
+    value = sample_bytes() * args.steps / dt / 1e9
+    sample = (f"each step = q/k/v/o projections of one dense-27B layer at M={args.rows} "
+              f"({sample_bytes() / 1e6:.1f} MB packed weights) on the host cores")
+    print(json.dumps({
+        "impl": "reference", "metric": "affine_4bit_g64_qmm_weight_gbps", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"dense27b_layer_projections_4bit_g64_M{args.rows}", "rows": args.rows, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": native.threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# the B200 arm
+# ----------------------------------------------------------------------------------------------------------------------
+
+def run_b200(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from tensorfold_b200 import _lib, synthetic
+    from tensorfold_b200.cuda.kernels import qmm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the hot path has no CPU implementation")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    rows = args.rows
+    shapes = layer_shapes()
+    layer_bytes = sum(weight_bytes(n, k) for _, (n, k) in shapes)
+    ring = max(2, -(-4 * L2_BYTES // layer_bytes))          # distinct layers: the ring holds > 4x L2 of weights
+    layers = []
+    for li in range(ring):
+        packed = {}
+        for pi, (name, (n, k)) in enumerate(shapes):
+            w = synthetic.affine_weight(n, k, BITS, GS, seed=1000 * li + pi)
+            packed[name] = qmm.pack(w[0].to(dev), w[1].to(dev), w[2].to(dev), GS)
+        layers.append(packed)
+    host_x = {name: synthetic.activations(rows, k, 31 + i).pin_memory() for i, (name, (n, k)) in enumerate(shapes)}
+    dev_x = {name: t.to(dev) for name, t in host_x.items()}
+    dev_y = {name: torch.empty((rows, n), dtype=torch.bfloat16, device=dev) for name, (n, k) in shapes}
+    host_y = {name: torch.empty((rows, n), dtype=torch.bfloat16).pin_memory() for name, (n, k) in shapes}
+    torch.cuda.synchronize()
+
+    def step(i: int, pdl: bool) -> None:
+        layer = layers[i % ring]
+        for name, _ in shapes:
+            qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=pdl)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):                     # eager warm-up (also the first, configuring, calls)
+        step(i, False)
+    torch.cuda.synchronize()
+
+    stream = torch.cuda.Stream()
+    pdl = not args.no_pdl
+
+    def capture(first: int, count: int, with_copies: bool):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(first, first + count):
+                    if with_copies:
+                        for name, _ in shapes:
+                            dev_x[name].copy_(host_x[name], non_blocking=True)
+                    step(i, pdl)
+                    if with_copies:
+                        for name, _ in shapes:
+                            host_y[name].copy_(dev_y[name], non_blocking=True)
+        return graph
+
+    try:
+        timed = capture(0, args.steps, False)
+    except RuntimeError:
+        pdl = False
+        torch.cuda.synchronize()
+        timed = capture(0, args.steps, False)
+
+    clocks = ClockSampler(local)
+    with clocks:
+        with torch.cuda.stream(stream):
+            timed.replay()                                   # untimed replay: graph upload, instruction caches
+            torch.cuda.synchronize()
+            t_load = time.perf_counter()
+            while time.perf_counter() - t_load < 1.5:        # keep the GPU under this load while clocks are sampled
+                timed.replay()
+            barrier()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            timed.replay()                                   # EXACTLY args.steps steps
+            end.record(stream)
+            barrier()
+            ms = start.elapsed_time(end)
+            trials = []
+            for _ in range(9):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record(stream)
+                timed.replay()
+                e.record(stream)
+                torch.cuda.synchronize()
+                trials.append(s.elapsed_time(e))
+
+            # end to end: host activations in, host results out, one graph replay (copies included) and a sync per step
+            e2e_graphs = [capture(i, 1, True) for i in range(ring)]
+            for g in e2e_graphs:
+                g.replay()
+            torch.cuda.synchronize()
+            barrier()
+            t0 = time.perf_counter()
+            for i in range(args.steps):
+                e2e_graphs[i % ring].replay()
+                stream.synchronize()                         # the step's result is on the host
+            e2e_s = time.perf_counter() - t0
+    if _lib.device_error(dev_y["q_proj"]) != 0:
+        raise RuntimeError("a kernel wait gave up during the benchmark")
+
+    times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+
+    launches = args.steps * len(shapes)
+    io_bytes = sum(2 * rows * (n + k) for _, (n, k) in shapes)
+    algo_bytes_step = layer_bytes + io_bytes
+    value = world * layer_bytes * args.steps / (ms * 1e-3) / 1e9
+    peak, peak_kind = measured_peaks()
+    achieved = algo_bytes_step * args.steps / (ms * 1e-3) / 1e9
+    med = sorted(trials)[len(trials) // 2]
+    if rank == 0:
+        line = {
+            "metric": "affine_4bit_g64_qmm_weight_gbps", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"dense27b_layer_projections_4bit_g64_M{rows}", "rows": rows, "bits": BITS,
+                       "group": GS, "projections": {name: list(shape) for name, shape in shapes},
+                       "weight_bytes_per_step": layer_bytes, "ring_layers": ring,
+                       "l2": f"steps cycle a ring of {ring} distinct layers ({ring * layer_bytes / 1e6:.0f} MB of weights, "
+                             "larger than the 126 MB L2), so no flush is needed",
+                       "launch": "CUDA graph of the timed steps" + (", programmatic dependent launch" if pdl else ""),
+                       "replicas": world > 1},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind, "traffic": None, "kernel": "qmm_tiled_kernel<4,64,%d>" % (rows + 7 >> 3 if rows <= 16 else 8),
+                         "bytes_per_launch": algo_bytes_step / len(shapes), "us_per_launch": ms * 1e3 / launches},
+            "median_of_9": {"ms_per_step": med / args.steps, "value": world * layer_bytes * args.steps / (med * 1e-3) / 1e9},
+            "e2e": {"value": world * layer_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": sum(2 * rows * k for _, (n, k) in shapes),
+                    "d2h_bytes_per_step": sum(2 * rows * n for _, (n, k) in shapes), "ms_per_step": e2e_ms / args.steps},
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(rows)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--rows", type=int, default=16)
+    ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

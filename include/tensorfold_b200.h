@@ -1,0 +1,95 @@
+/* C ABI of libtensorfold_b200.so: the B200 (sm_100a) kernels behind TensorFold's quantized-projection entry points.
+ *
+ * The reference has no C ABI for this path: its boundary is a set of pybind11 functions taking torch tensors, built at
+ * run time by torch.utils.cpp_extension (src/tensorfold/cuda/build.py:28-44).  Each function below names the reference
+ * interface it stands in for (paths inside the reference project).  Conventions:
+ *
+ *   - every pointer is a DEVICE pointer unless its comment says "host";
+ *   - `stream` is a cudaStream_t passed as void* (torch.cuda.current_stream().cuda_stream); nothing here synchronises;
+ *   - the caller owns every buffer; no function allocates device memory;
+ *   - the return value is a status: 0 = OK, TF_ERR_* < 0 for a refused argument (nothing was launched),
+ *     > 0 = a cudaError_t from the launch.  tf_last_error() gives the text for the calling thread;
+ *   - call tf_init(device) once per device before the first launch and before any CUDA-graph capture: it sets the
+ *     kernels' shared-memory attributes and resolves the device's error word.
+ */
+#ifndef TENSORFOLD_B200_H
+#define TENSORFOLD_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TF_OK 0
+#define TF_ERR_ARG (-1)        /* bad shape, size or flag */
+#define TF_ERR_ALIGN (-2)      /* pointer or stride not aligned as documented */
+#define TF_ERR_UNSUPPORTED (-3)
+#define TF_ERR_STATE (-4)      /* tf_init not called for the current device */
+
+/* Library version (major * 10000 + minor * 100 + patch) and the architecture it was built for ("sm_100a"). */
+int tf_version(void);
+const char* tf_arch(void);
+const char* tf_last_error(void);
+
+/* Per-device set-up; replaces the lazy `static bool configured` + cudaFuncSetAttribute of
+ * cuda/kernels/qmm.cu:251-255.  Idempotent. */
+int tf_init(int device);
+
+/* Reads and clears the device error word that kernels set when one of their bounded waits gave up (0 = none).
+ * Synchronises `stream`.  host: *code. */
+int tf_device_error(int device, void* stream, int* code);
+
+/* ---- shape-only planning (host functions) -------------------------------------------------------------------- */
+
+/* K slices of an (n, k) weight: cuda/kernels/qmm.py:105-111 (split_k). */
+int tf_split_k(int n, int k, int gs, int target);
+/* Row tile for m rows, 16/32/64, or TF_ERR_ARG for m < 1: cuda/kernels/qmm.py:114-119 (bucket). */
+int tf_bucket(int m);
+/* int32 words of the tiled tensor of an (n, k) weight: ceil(n / 128) * (k / gs) * (4 * gs * bits + 128). */
+int64_t tf_tiled_words(int n, int k, int bits, int gs);
+/* int32 words of one (128 columns, one group) unit. */
+int tf_unit_words(int bits, int gs);
+
+/* ---- load-time repack -------------------------------------------------------------------------------------- */
+
+/* MLX rows -> tiled units.  words: [n, k * bits / 32] int32; scales, biases: [n, k / gs] bf16; tiled: tf_tiled_words.
+ * Replaces the torch-indexing repack of cuda/kernels/qmm.py:55-82 (pack). */
+int tf_pack(const void* words, const void* scales, const void* biases, int n, int k, int bits, int gs, void* tiled,
+            void* stream);
+/* Exact inverse of tf_pack: cuda/kernels/qmm.py:85-102 (unpack). */
+int tf_unpack(const void* tiled, int n, int k, int bits, int gs, void* words, void* scales, void* biases, void* stream);
+
+/* ---- the matmul ---------------------------------------------------------------------------------------------- */
+
+/* xs[m, g] = sum of x[m, g * gs : (g + 1) * gs] in fp32, with the bits the matmul computes for itself when it is given
+ * no sums.  x: [m, k] bf16, row stride ldx elements (ldx % 2 == 0, base 4-byte aligned).  xs: [m, k / gs] fp32.
+ * Replaces cuda/kernels/qmm.py:122-137 (group_sums). */
+int tf_group_sums(const void* x, int64_t ldx, int m, int k, int gs, float* xs, void* stream);
+
+/* out[m, n] = x @ dequant(w).T over the tiled layout, any m >= 1; a row's bits never depend on m.
+ *   x        [m, k] bf16, base 16-byte aligned, ldx % 8 == 0 (elements)
+ *   xs       optional [m, k / gs] fp32 group sums (NULL: computed in the kernel)
+ *   tiled    units of the weight; sb_stride = int32 words between consecutive 128-column super-blocks
+ *            (0: dense, (k / gs) * tf_unit_words)
+ *   sk       K slices (>= 1, divides k / gs); sums are added in slice order
+ *   out      [m, n] bf16 (out_f32 = 0) or fp32, row stride ldo elements; ignored when reduce = 0 and sk > 1
+ *   part     [sk, m, n] fp32, required when sk > 8 or when reduce = 0 with sk > 1, else may be NULL
+ *   reduce   1: out receives the sum of the slices; 0: the slices stay in part (out untouched)
+ *   pdl      1: launch with programmatic stream serialisation, so this call's weight prefetch overlaps the tail of the
+ *            previous kernel in the stream (it still waits for that kernel before reading x or writing out)
+ * Replaces the pybind function qmm(x, xs, w, scales, biases, out, part, n, sk, gs, bm, f32, reduce) of
+ * cuda/kernels/qmm.cpp:14-44 and, for bits != 4, the Triton launch of cuda/kernels/affine.py:53-68. */
+int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled, int64_t sb_stride, int n, int k,
+           int bits, int gs, int sk, void* out, int64_t ldo, int out_f32, float* part, int reduce, int pdl,
+           void* stream);
+
+/* out[i] = round(part[0][i] + part[1][i] + ...), slices added in order: cuda/kernels/qmm.cu:235-243 (reduce_kernel).
+ * part: [sk, total] fp32; out: [total] bf16 or fp32. */
+int tf_reduce_slices(const float* part, int sk, int64_t total, void* out, int out_f32, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TENSORFOLD_B200_H */

@@ -1,0 +1,331 @@
+// extern "C" entry points (include/tensorfold_b200.h), argument checks, and the small kernels around the matmul:
+// load-time repack and its inverse, group sums, slice reduction.
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/tensorfold_b200.h"
+#include "qmm_launch.h"
+
+namespace tf {
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  snprintf(g_error, sizeof g_error, "%s: %s", what, cudaGetErrorString(e));
+  return static_cast<int>(e);
+}
+
+bool format_ok(int bits, int gs) {
+  return (bits == 2 || bits == 3 || bits == 4 || bits == 5 || bits == 6 || bits == 8) && (gs == 32 || gs == 64 || gs == 128);
+}
+
+constexpr int MAX_DEVICES = 64;
+struct DeviceState {
+  bool ready = false;
+  int* err = nullptr;
+};
+DeviceState g_devices[MAX_DEVICES];
+std::mutex g_init_mutex;
+
+}  // namespace
+
+__device__ int g_error_word;          // set by a kernel whose bounded wait gave up; read by tf_device_error
+
+// ---------------------------------------------------------------------------------------------------------------------
+// repack: one thread per output word of the tiled tensor
+// ---------------------------------------------------------------------------------------------------------------------
+
+__global__ void pack_kernel(const uint32_t* __restrict__ words, const uint16_t* __restrict__ scales,
+                            const uint16_t* __restrict__ biases, int n, int k, int bits, int gs,
+                            uint32_t* __restrict__ tiled, int64_t total) {
+  const int wpl = words_per_lane(bits, gs), unitw = unit_words(bits, gs), kg = k / gs;
+  const int64_t wpr = static_cast<int64_t>(k) * bits / 32;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int wi_unit = static_cast<int>(i % unitw);
+    const int64_t unit = i / unitw;
+    const int g = static_cast<int>(unit % kg);
+    const int64_t sb = unit / kg;
+    const int code_words = TILE_PAIRS * 32 * wpl;
+    uint32_t value;
+    if (wi_unit < code_words) {
+      const int tp = wi_unit / (32 * wpl), lane = (wi_unit / wpl) % 32, wi = wi_unit % wpl;
+      auto code = [&](int col, int kk) -> uint32_t {
+        const int64_t row = sb * SB_COLS + col;
+        return row < n ? stored_code(words + row * wpr, static_cast<int64_t>(g) * gs + kk, bits, wpr) : 0u;
+      };
+      value = lane_word(bits, gs, tp, lane, wi, code);
+    } else {
+      const int ai = wi_unit - code_words;
+      const int tp = ai >> 5, gg = (ai >> 2) & 7, h = (ai >> 1) & 1, r8 = ai & 1;
+      const int64_t row = sb * SB_COLS + 32 * tp + 16 * h + 8 * r8 + gg;
+      value = row < n ? (static_cast<uint32_t>(scales[row * kg + g]) | (static_cast<uint32_t>(biases[row * kg + g]) << 16)) : 0u;
+    }
+    tiled[i] = value;
+  }
+}
+
+// inverse: one thread per (row, block of 32 codes) writes `bits` words; one thread per (row, group) writes the affine pair
+__global__ void unpack_kernel(const uint32_t* __restrict__ tiled, int n, int k, int bits, int gs,
+                              uint32_t* __restrict__ words, uint16_t* __restrict__ scales, uint16_t* __restrict__ biases) {
+  const int wpl = words_per_lane(bits, gs), unitw = unit_words(bits, gs), kg = k / gs, blocks = k / 32;
+  const int64_t total = static_cast<int64_t>(n) * blocks;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / blocks;
+    const int blk = static_cast<int>(i % blocks);
+    const int64_t sb = row / SB_COLS;
+    const int c = static_cast<int>(row % SB_COLS);
+    uint32_t outw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < 32; ++j) {
+      const int kk_all = blk * 32 + j, g = kk_all / gs, kk = kk_all % gs;
+      const CodeLoc loc = code_loc(c, kk, gs);
+      const uint32_t* lw = tiled + (sb * kg + g) * unitw + (loc.tp * 32 + loc.lane) * wpl;
+      const uint64_t code = lane_code(bits, gs, lw, loc.p, loc.half);
+      const int bit = j * bits;
+      const uint64_t shifted = code << (bit & 31);
+      outw[bit >> 5] |= static_cast<uint32_t>(shifted);
+      if ((bit & 31) + bits > 32) outw[(bit >> 5) + 1] |= static_cast<uint32_t>(shifted >> 32);
+    }
+    for (int w = 0; w < bits; ++w) words[row * (static_cast<int64_t>(k) * bits / 32) + blk * bits + w] = outw[w];
+    if (blk < kg) {                                   // kg <= blocks: reuse the first kg threads of a row
+      const int g = blk;
+      const uint32_t v = tiled[(sb * kg + g) * unitw + TILE_PAIRS * 32 * wpl + affine_index(c)];
+      scales[row * kg + g] = static_cast<uint16_t>(v & 0xFFFFu);
+      biases[row * kg + g] = static_cast<uint16_t>(v >> 16);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// group sums with the matmul kernel's own arithmetic: x against a tile of ones, one warp per (8 rows, group)
+// ---------------------------------------------------------------------------------------------------------------------
+
+__global__ void group_sums_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int m, int kg, int gs,
+                                  float* __restrict__ xs) {
+  const int lane = threadIdx.x & 31, g8 = lane >> 2, t = lane & 3;
+  const int group = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (group >= kg) return;
+  const int m0 = blockIdx.y * 8, row = m0 + g8;
+  const uint32_t ones[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};
+  float d[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(x + static_cast<int64_t>(row < m ? row : 0) * ldx + static_cast<int64_t>(group) * gs);
+  for (int s = 0; s < gs / 16; ++s) {
+    uint32_t b0 = 0, b1 = 0;
+    if (row < m) {
+      b0 = src[s * 8 + t];           // inputs 16 s + 2 t, + 1
+      b1 = src[s * 8 + 4 + t];       // inputs 16 s + 8 + 2 t, + 1
+    }
+    mma_bf16(d, ones, b0, b1);
+  }
+  if (lane < 4) {
+    const int r = m0 + 2 * lane;
+    if (r < m) xs[static_cast<int64_t>(r) * kg + group] = d[0];
+    if (r + 1 < m) xs[static_cast<int64_t>(r + 1) * kg + group] = d[1];
+  }
+}
+
+__global__ void reduce_slices_kernel(const float* __restrict__ part, int sk, int64_t total, void* out, int out_f32) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float acc = part[i];
+    for (int s = 1; s < sk; ++s) acc = acc + part[static_cast<int64_t>(s) * total + i];
+    if (out_f32) reinterpret_cast<float*>(out)[i] = acc;
+    else reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(acc);
+  }
+}
+
+namespace {
+
+int grid_for(int64_t total, int threads) {
+  const int64_t blocks = (total + threads - 1) / threads;
+  return static_cast<int>(blocks < 1 ? 1 : (blocks > 148 * 32 ? 148 * 32 : blocks));
+}
+
+int current_state(DeviceState** st) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= MAX_DEVICES || !g_devices[dev].ready)
+    return fail(TF_ERR_STATE, "tf_init(%d) has not been called for the current device", dev);
+  *st = &g_devices[dev];
+  return TF_OK;
+}
+
+}  // namespace
+
+}  // namespace tf
+
+using namespace tf;
+
+extern "C" {
+
+int tf_version(void) { return 100; }
+const char* tf_arch(void) { return "sm_100a"; }
+const char* tf_last_error(void) { return g_error; }
+
+int tf_init(int device) {
+  if (device < 0 || device >= MAX_DEVICES) return fail(TF_ERR_ARG, "device %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_init_mutex);
+  if (g_devices[device].ready) return TF_OK;
+  int prev = -1;
+  cudaError_t e = cudaGetDevice(&prev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  e = cudaSetDevice(device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, device);
+  if (e == cudaSuccess && prop.major != 10) {
+    cudaSetDevice(prev);
+    return fail(TF_ERR_UNSUPPORTED, "built for sm_100a; device %d is sm_%d%d", device, prop.major, prop.minor);
+  }
+  if (e == cudaSuccess) e = qmm_configure_b2();
+  if (e == cudaSuccess) e = qmm_configure_b3();
+  if (e == cudaSuccess) e = qmm_configure_b4();
+  if (e == cudaSuccess) e = qmm_configure_b5();
+  if (e == cudaSuccess) e = qmm_configure_b6();
+  if (e == cudaSuccess) e = qmm_configure_b8();
+  int* err = nullptr;
+  if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_error_word);
+  if (e == cudaSuccess) e = cudaMemset(err, 0, sizeof(int));
+  cudaSetDevice(prev);
+  if (e != cudaSuccess) return cuda_fail(e, "tf_init");
+  g_devices[device].err = err;
+  g_devices[device].ready = true;
+  return TF_OK;
+}
+
+int tf_device_error(int device, void* stream, int* code) {
+  if (device < 0 || device >= MAX_DEVICES || !g_devices[device].ready || code == nullptr)
+    return fail(TF_ERR_STATE, "tf_init(%d) has not been called", device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(code, g_devices[device].err, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess && *code != 0) e = cudaMemsetAsync(g_devices[device].err, 0, sizeof(int), s);
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_device_error");
+}
+
+int tf_split_k(int n, int k, int gs, int target) {
+  if (n < 1 || k < 1 || gs < 1) return TF_ERR_ARG;
+  const int tiles = (n + 63) / 64, groups = k / gs;
+  int sk = 1;
+  while (sk < 8 && tiles * sk < target && groups % (sk * 2) == 0 && groups / (sk * 2) >= 8) sk *= 2;
+  return sk;
+}
+
+int tf_bucket(int m) { return m < 1 ? TF_ERR_ARG : m <= 16 ? 16 : m <= 32 ? 32 : 64; }
+
+int tf_unit_words(int bits, int gs) { return format_ok(bits, gs) ? unit_words(bits, gs) : TF_ERR_ARG; }
+
+int64_t tf_tiled_words(int n, int k, int bits, int gs) {
+  if (!format_ok(bits, gs) || n < 1 || k < gs || k % gs) return TF_ERR_ARG;
+  return static_cast<int64_t>((n + SB_COLS - 1) / SB_COLS) * (k / gs) * unit_words(bits, gs);
+}
+
+int tf_pack(const void* words, const void* scales, const void* biases, int n, int k, int bits, int gs, void* tiled,
+            void* stream) {
+  if (!format_ok(bits, gs)) return fail(TF_ERR_ARG, "tf_pack: %d bits / groups of %d is not an affine format", bits, gs);
+  if (n < 1 || k < gs || k % gs || (static_cast<int64_t>(k) * bits) % 32)
+    return fail(TF_ERR_ARG, "tf_pack: (%d, %d) does not split into whole groups and words", n, k);
+  if (!words || !scales || !biases || !tiled) return fail(TF_ERR_ARG, "tf_pack: null pointer");
+  const int64_t total = tf_tiled_words(n, k, bits, gs);
+  pack_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(words), static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), n, k,
+      bits, gs, static_cast<uint32_t*>(tiled), total);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_pack");
+}
+
+int tf_unpack(const void* tiled, int n, int k, int bits, int gs, void* words, void* scales, void* biases, void* stream) {
+  if (!format_ok(bits, gs)) return fail(TF_ERR_ARG, "tf_unpack: %d bits / groups of %d is not an affine format", bits, gs);
+  if (n < 1 || k < gs || k % gs || (static_cast<int64_t>(k) * bits) % 32)
+    return fail(TF_ERR_ARG, "tf_unpack: (%d, %d) does not split into whole groups and words", n, k);
+  if (!words || !scales || !biases || !tiled) return fail(TF_ERR_ARG, "tf_unpack: null pointer");
+  unpack_kernel<<<grid_for(static_cast<int64_t>(n) * (k / 32), 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(tiled), n, k, bits, gs, static_cast<uint32_t*>(words), static_cast<uint16_t*>(scales),
+      static_cast<uint16_t*>(biases));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_unpack");
+}
+
+int tf_group_sums(const void* x, int64_t ldx, int m, int k, int gs, float* xs, void* stream) {
+  if (gs != 32 && gs != 64 && gs != 128) return fail(TF_ERR_ARG, "tf_group_sums: groups of 32, 64 or 128, not %d", gs);
+  if (m < 1 || k < gs || k % gs || !x || !xs) return fail(TF_ERR_ARG, "tf_group_sums: bad shape (%d, %d)", m, k);
+  if (reinterpret_cast<uintptr_t>(x) % 4 || (m > 1 && ldx % 2)) return fail(TF_ERR_ALIGN, "tf_group_sums: rows must be 4-byte aligned");
+  const int kg = k / gs;
+  dim3 grid((kg + 3) / 4, (m + 7) / 8);
+  group_sums_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x), ldx, m, kg, gs, xs);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_group_sums");
+}
+
+int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled, int64_t sb_stride, int n, int k, int bits,
+           int gs, int sk, void* out, int64_t ldo, int out_f32, float* part, int reduce, int pdl, void* stream) {
+  if (!format_ok(bits, gs)) return fail(TF_ERR_ARG, "tf_qmm: %d bits / groups of %d is not an affine format", bits, gs);
+  if (m < 1 || n < 1 || k < gs || k % gs) return fail(TF_ERR_ARG, "tf_qmm: bad shape m=%d n=%d k=%d", m, n, k);
+  const int kg = k / gs;
+  if (sk < 1 || kg % sk) return fail(TF_ERR_ARG, "tf_qmm: K must split into whole groups a slice (groups %d, slices %d)", kg, sk);
+  if (!x || !tiled) return fail(TF_ERR_ARG, "tf_qmm: null pointer");
+  if (reinterpret_cast<uintptr_t>(x) % 16 || (m > 1 && ldx % 8) || ldx < k)
+    return fail(TF_ERR_ALIGN, "tf_qmm: x rows must start on 16-byte boundaries (ldx %% 8 == 0, ldx >= k)");
+  if (reinterpret_cast<uintptr_t>(tiled) % 16) return fail(TF_ERR_ALIGN, "tf_qmm: tiled weights must be 16-byte aligned");
+  const bool slices_out = sk > 1 && (!reduce || sk > 8);
+  if (slices_out && !part) return fail(TF_ERR_ARG, "tf_qmm: part [sk, m, n] is required for %d slices with reduce=%d", sk, reduce);
+  if (!(slices_out && !reduce) && (!out || ldo < n)) return fail(TF_ERR_ARG, "tf_qmm: out must be [m, n] with ldo >= n");
+  if (slices_out && reduce && ldo != n) return fail(TF_ERR_ARG, "tf_qmm: more than 8 slices need a contiguous out (ldo == n)");
+  if (m > 65535 * 8) return fail(TF_ERR_ARG, "tf_qmm: too many rows");
+  DeviceState* st = nullptr;
+  if (int rc = current_state(&st)) return rc;
+
+  const int unitw = unit_words(bits, gs);
+  QmmParams p;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.ldx = ldx;
+  p.M = m;
+  p.xs = xs;
+  p.w = static_cast<const uint32_t*>(tiled);
+  p.sb_stride = sb_stride > 0 ? sb_stride : static_cast<int64_t>(kg) * unitw;
+  p.N = n, p.K = k, p.KG = kg, p.sk = sk;
+  p.out = out;
+  p.ldo = ldo;
+  p.out_f32 = out_f32;
+  const int esize = out_f32 ? 4 : 2;
+  p.out_vec = out && reinterpret_cast<uintptr_t>(out) % 16 == 0 && (ldo * esize) % 16 == 0;
+  p.part = part;
+  p.cluster = !slices_out;
+  p.err = st->err;
+  const int mt = mt_for_rows(m);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  switch (bits) {
+    case 2: e = qmm_launch_b2(p, gs, mt, s, pdl != 0); break;
+    case 3: e = qmm_launch_b3(p, gs, mt, s, pdl != 0); break;
+    case 4: e = qmm_launch_b4(p, gs, mt, s, pdl != 0); break;
+    case 5: e = qmm_launch_b5(p, gs, mt, s, pdl != 0); break;
+    case 6: e = qmm_launch_b6(p, gs, mt, s, pdl != 0); break;
+    default: e = qmm_launch_b8(p, gs, mt, s, pdl != 0); break;
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "tf_qmm launch");
+  if (slices_out && reduce) return tf_reduce_slices(part, sk, static_cast<int64_t>(m) * n, out, out_f32, stream);
+  return TF_OK;
+}
+
+int tf_reduce_slices(const float* part, int sk, int64_t total, void* out, int out_f32, void* stream) {
+  if (!part || !out || sk < 1 || total < 1) return fail(TF_ERR_ARG, "tf_reduce_slices: bad arguments");
+  reduce_slices_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(part, sk, total, out, out_f32);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_reduce_slices");
+}
+
+}  // extern "C"

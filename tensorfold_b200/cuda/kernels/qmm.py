@@ -1,0 +1,156 @@
+"""4-bit lane matmul: rows run the same groups and K slices at any row count, so no row affects another.
+
+Host-side mirror of the reference module ``tensorfold.cuda.kernels.qmm`` (cuda/kernels/qmm.py:24-171): same names,
+argument meaning and errors; the arithmetic runs in ``libtensorfold_b200.so``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ... import _lib
+
+BITS = (2, 3, 4, 5, 6, 8)
+GROUPS = (32, 64, 128)
+
+
+@dataclass
+class Q4:
+    """A packed (n, k) weight in the tiled layout: int32 units [ceil(n / 128), k / gs, unit words], each unit the codes
+    of 128 output columns for one group followed by their 128 (scale, bias) bf16 pairs.  ``scales`` and ``biases`` stay
+    None: the pairs live inside ``weight`` (``unpack`` returns them).  Field order follows cuda/kernels/qmm.py:24-35."""
+
+    weight: torch.Tensor
+    scales: torch.Tensor | None
+    biases: torch.Tensor | None
+    n: int
+    k: int
+    gs: int
+    bits: int = 4
+
+    def nbytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+
+def pack(weight: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, gs: int, chunk: int = 4096,
+         bits: int = 4) -> Q4:
+    """MLX (n, k * bits / 32) words, (n, k / gs) bf16 scales and biases -> ``Q4``.  ``chunk`` is accepted for
+    signature parity (cuda/kernels/qmm.py:55) and unused: the repack is one kernel."""
+
+    if bits not in BITS or gs not in GROUPS:
+        raise ValueError("affine weights require 2/3/4/5/6/8 bits and groups of 32/64/128")
+    if weight.dim() != 2 or weight.dtype not in (torch.int32, torch.uint32):
+        raise ValueError("pack: weight must be 2-D int32/uint32 MLX words")
+    if scales.dtype != torch.bfloat16 or biases.dtype != torch.bfloat16 or scales.shape != biases.shape:
+        raise ValueError("pack: scales and biases must be matching bf16 tensors")
+    n, words = weight.shape
+    k = words * 32 // bits
+    if scales.shape != (n, k // gs) or k % gs or (k * bits) % 32:
+        raise ValueError(f"pack: words {tuple(weight.shape)} do not match scales {tuple(scales.shape)} at {bits} bits")
+    stream = _lib.stream_of(weight)
+    weight, scales, biases = weight.contiguous(), scales.contiguous(), biases.contiguous()
+    lib = _lib.lib()
+    unit = lib.tf_unit_words(bits, gs)
+    out = torch.empty((-(-n // 128), k // gs, unit), dtype=torch.int32, device=weight.device)
+    _lib.check(lib.tf_pack(weight.data_ptr(), scales.data_ptr(), biases.data_ptr(), n, k, bits, gs, out.data_ptr(),
+                           stream), "pack")
+    return Q4(out, None, None, n, k, gs, bits)
+
+
+def unpack(q: Q4, chunk: int = 64) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The stored MLX layout again: (n, k * bits / 32) int32 words, (n, k / gs) bf16 scales and biases."""
+
+    stream = _lib.stream_of(q.weight)
+    dev = q.weight.device
+    words = torch.empty((q.n, q.k * q.bits // 32), dtype=torch.int32, device=dev)
+    scales = torch.empty((q.n, q.k // q.gs), dtype=torch.bfloat16, device=dev)
+    biases = torch.empty_like(scales)
+    tiled = q.weight if q.weight.is_contiguous() else q.weight.contiguous()
+    _lib.check(_lib.lib().tf_unpack(tiled.data_ptr(), q.n, q.k, q.bits, q.gs, words.data_ptr(), scales.data_ptr(),
+                                    biases.data_ptr(), stream), "unpack")
+    return words, scales, biases
+
+
+def split_k(n: int, k: int, gs: int = 64, target: int = 192) -> int:
+    """K slices for an (n, k) weight: a function of the shape only (never of the row count)."""
+
+    tiles, groups, sk = -(-n // 64), k // gs, 1
+    while sk < 8 and tiles * sk < target and groups % (sk * 2) == 0 and groups // (sk * 2) >= 8:
+        sk *= 2
+    return sk
+
+
+def bucket(m: int) -> int:
+    """The reference's row tile (16, 32, else 64); kept for callers that size buffers by it.  Tiles never change bits."""
+
+    if m < 1:
+        raise ValueError("the lane matmul takes at least one row")
+    return 16 if m <= 16 else 32 if m <= 32 else 64
+
+
+def group_sums(x: torch.Tensor, gs: int = 64) -> torch.Tensor:
+    """(M, K) bf16 (rows may be strided) -> (M, K/gs) fp32 sums of each group's inputs, with the matmul's own bits."""
+
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] % gs:
+        raise ValueError("group_sums: x must be (M, K) bf16 with K a multiple of the group")
+    if x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) % 2) or x.data_ptr() % 4:
+        x = x.clone(memory_format=torch.contiguous_format)
+    stream = _lib.stream_of(x)
+    m, k = x.shape
+    xs = torch.empty((m, k // gs), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().tf_group_sums(x.data_ptr(), x.stride(0), m, k, gs, xs.data_ptr(), stream), "group_sums")
+    return xs
+
+
+def _rows(x: torch.Tensor, k: int, who: str) -> torch.Tensor:
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != k:
+        raise ValueError(f"{who}: x must be (M, {k}) bf16")
+    if x.shape[0] < 1:
+        raise ValueError(f"{who}: x needs at least one row")
+    if x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) % 8) or x.data_ptr() % 16:
+        x = x.clone(memory_format=torch.contiguous_format)     # bulk copies read rows in 16-byte pieces
+    return x
+
+
+def matmul(x: torch.Tensor, q: Q4, xs: torch.Tensor | None = None, *, sk: int | None = None, f32: bool = False,
+           out: torch.Tensor | None = None, part: torch.Tensor | None = None, reduce: bool = True,
+           pdl: bool = False) -> torch.Tensor:
+    """x @ q.T as (M, n) bf16, or unrounded fp32 with ``f32``; ``reduce=False`` returns K slices to add in order.
+
+    ``pdl`` (not in the reference) launches with programmatic stream serialisation so the weight prefetch of this call
+    overlaps the end of the previous kernel in the stream."""
+
+    x = _rows(x, q.k, "matmul")
+    m = x.shape[0]
+    stream = _lib.stream_of(x)
+    if q.weight.device != x.device:
+        raise ValueError("matmul: x and the weight must share a CUDA device")
+    kg = q.k // q.gs
+    if xs is not None and (xs.dtype != torch.float32 or xs.shape != (m, kg) or not xs.is_contiguous()):
+        raise ValueError(f"matmul: xs must be contiguous ({m}, {kg}) fp32")
+    sk = sk or split_k(q.n, q.k, q.gs)
+    if sk < 1 or kg % sk:
+        raise ValueError("matmul: K must split into whole groups a slice")
+    slices = sk > 1 and not reduce
+    if out is None:
+        if not slices:
+            out = torch.empty((m, q.n), dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
+    elif out.shape != (m, q.n) or out.dtype != (torch.float32 if f32 else torch.bfloat16) or out.stride(1) != 1:
+        raise ValueError("matmul: out must be (M, n) of the requested dtype with unit-stride rows")
+    if sk > 1 and (not reduce or sk > 8):
+        if part is None:
+            part = torch.empty((sk, m, q.n), dtype=torch.float32, device=x.device)
+        elif part.dtype != torch.float32 or not part.is_contiguous() or part.numel() < sk * m * q.n:
+            raise ValueError("matmul: part must hold (SK, M, n) fp32")
+    if q.weight.dim() != 3 or q.weight.stride(2) != 1 or q.weight.stride(1) != q.weight.shape[2]:
+        raise ValueError("matmul: the tiled weight may be sliced by super-blocks of 128 columns only")
+    _lib.check(_lib.lib().tf_qmm(
+        x.data_ptr(), x.stride(0), m, xs.data_ptr() if xs is not None else None, q.weight.data_ptr(),
+        q.weight.stride(0), q.n, q.k, q.bits, q.gs, sk, out.data_ptr() if out is not None else None,
+        out.stride(0) if out is not None else 0, int(f32), part.data_ptr() if part is not None else None,
+        int(reduce), int(pdl), stream), "matmul")
+    if sk == 1 or reduce:
+        return out
+    return part.reshape(-1)[:sk * m * q.n].view(sk, m, q.n)
