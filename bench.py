@@ -214,10 +214,15 @@ def run_b200(args) -> None:
     host_y = {name: torch.empty((rows, n), dtype=torch.bfloat16).pin_memory() for name, (n, k) in shapes}
     torch.cuda.synchronize()
 
+    if args.lanes:
+        _lib.check(_lib.lib().tf_tune(b"qmm_lanes", args.lanes), "tune")
+    splits = {name: (qmm.split_k(n, k, GS, args.sk_target) if args.sk_target else qmm.default_split(n, k, GS))
+              for name, (n, k) in shapes}
+
     def step(i: int, pdl: bool) -> None:
         layer = layers[i % ring]
         for name, _ in shapes:
-            qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=pdl)
+            qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=pdl, sk=splits[name])
 
     def barrier():
         if world > 1:
@@ -313,7 +318,7 @@ def run_b200(args) -> None:
                        "l2": f"steps cycle a ring of {ring} distinct layers ({ring * layer_bytes / 1e6:.0f} MB of weights, "
                              "larger than the 126 MB L2), so no flush is needed",
                        "launch": "CUDA graph of the timed steps" + (", programmatic dependent launch" if pdl else ""),
-                       "replicas": world > 1},
+                       "replicas": world > 1, "k_slices": splits, "lanes": args.lanes},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "traffic": None, "kernel": "qmm_tiled_kernel<4,64,%d>" % (rows + 7 >> 3 if rows <= 16 else 8),
@@ -340,6 +345,8 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")
+    ap.add_argument("--sk-target", type=int, default=0, help="tuning: occupancy target of the K split (0 = default)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

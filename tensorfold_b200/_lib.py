@@ -17,6 +17,7 @@ SIGNATURES = {
     "tf_last_error": (ctypes.c_char_p, ()),
     "tf_init": (_i32, (_i32,)),
     "tf_device_error": (_i32, (_i32, _vp, ctypes.POINTER(_i32))),
+    "tf_tune": (_i32, (ctypes.c_char_p, _i32)),
     "tf_split_k": (_i32, (_i32, _i32, _i32, _i32)),
     "tf_bucket": (_i32, (_i32,)),
     "tf_tiled_words": (_i64, (_i32, _i32, _i32, _i32)),

@@ -1,4 +1,4 @@
-// Instantiates qmm_tiled_kernel for one bit width (TF_BITS) over every group size and row tile.
+// Instantiates qmm_tiled_kernel for one bit width (TF_BITS) over every group size, row tile and lane count.
 #include "qmm_launch.h"
 
 #ifndef TF_BITS
@@ -9,21 +9,22 @@ namespace tf {
 
 namespace {
 
-template <int GS, int MT>
+template <int GS, int MT, int KW>
 cudaError_t launch(const QmmParams& p, cudaStream_t stream, bool pdl) {
-  using Geo = QmmGeo<TF_BITS, GS, MT>;
+  using Geo = QmmGeo<TF_BITS, GS, MT, KW>;
+  const int nblocks = p.sk / KW;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((p.N + SB_COLS - 1) / SB_COLS, (p.M + Geo::ROWS - 1) / Geo::ROWS, p.sk);
-  cfg.blockDim = dim3(QMM_THREADS);
+  cfg.gridDim = dim3((p.N + SB_COLS - 1) / SB_COLS, (p.M + Geo::ROWS - 1) / Geo::ROWS, nblocks);
+  cfg.blockDim = dim3(Geo::THREADS);
   cfg.dynamicSmemBytes = Geo::SMEM;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
   int na = 0;
-  if (p.cluster && p.sk > 1) {
+  if (p.cluster && nblocks > 1) {
     attrs[na].id = cudaLaunchAttributeClusterDimension;
     attrs[na].val.clusterDim.x = 1;
     attrs[na].val.clusterDim.y = 1;
-    attrs[na].val.clusterDim.z = p.sk;
+    attrs[na].val.clusterDim.z = nblocks;
     ++na;
   }
   if (pdl) {
@@ -33,32 +34,42 @@ cudaError_t launch(const QmmParams& p, cudaStream_t stream, bool pdl) {
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  return cudaLaunchKernelEx(&cfg, qmm_tiled_kernel<TF_BITS, GS, MT>, p);
+  return cudaLaunchKernelEx(&cfg, qmm_tiled_kernel<TF_BITS, GS, MT, KW>, p);
 }
 
-template <int GS, int MT>
+template <int GS, int MT, int KW>
 cudaError_t configure() {
-  return cudaFuncSetAttribute(qmm_tiled_kernel<TF_BITS, GS, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              QmmGeo<TF_BITS, GS, MT>::SMEM);
+  return cudaFuncSetAttribute(qmm_tiled_kernel<TF_BITS, GS, MT, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              QmmGeo<TF_BITS, GS, MT, KW>::SMEM);
 }
 
 template <int GS>
-cudaError_t launch_gs(const QmmParams& p, int mt, cudaStream_t stream, bool pdl) {
-  switch (mt) {
-    case 1: return launch<GS, 1>(p, stream, pdl);
-    case 2: return launch<GS, 2>(p, stream, pdl);
-    case 4: return launch<GS, 4>(p, stream, pdl);
-    case 8: return launch<GS, 8>(p, stream, pdl);
+cudaError_t launch_gs(const QmmParams& p, int mt, int kw, cudaStream_t stream, bool pdl) {
+  switch (mt * 10 + kw) {
+    case 11: return launch<GS, 1, 1>(p, stream, pdl);
+    case 12: return launch<GS, 1, 2>(p, stream, pdl);
+    case 14: return launch<GS, 1, 4>(p, stream, pdl);
+    case 21: return launch<GS, 2, 1>(p, stream, pdl);
+    case 22: return launch<GS, 2, 2>(p, stream, pdl);
+    case 24: return launch<GS, 2, 4>(p, stream, pdl);
+    case 41: return launch<GS, 4, 1>(p, stream, pdl);
+    case 42: return launch<GS, 4, 2>(p, stream, pdl);
+    case 81: return launch<GS, 8, 1>(p, stream, pdl);
     default: return cudaErrorInvalidValue;
   }
 }
 
 template <int GS>
 cudaError_t configure_gs() {
-  cudaError_t e = configure<GS, 1>();
-  if (e == cudaSuccess) e = configure<GS, 2>();
-  if (e == cudaSuccess) e = configure<GS, 4>();
-  if (e == cudaSuccess) e = configure<GS, 8>();
+  cudaError_t e = configure<GS, 1, 1>();
+  if (e == cudaSuccess) e = configure<GS, 1, 2>();
+  if (e == cudaSuccess) e = configure<GS, 1, 4>();
+  if (e == cudaSuccess) e = configure<GS, 2, 1>();
+  if (e == cudaSuccess) e = configure<GS, 2, 2>();
+  if (e == cudaSuccess) e = configure<GS, 2, 4>();
+  if (e == cudaSuccess) e = configure<GS, 4, 1>();
+  if (e == cudaSuccess) e = configure<GS, 4, 2>();
+  if (e == cudaSuccess) e = configure<GS, 8, 1>();
   return e;
 }
 
@@ -67,11 +78,11 @@ cudaError_t configure_gs() {
 #define TF_CAT2(a, b) a##b
 #define TF_CAT(a, b) TF_CAT2(a, b)
 
-cudaError_t TF_CAT(qmm_launch_b, TF_BITS)(const QmmParams& p, int gs, int mt, cudaStream_t stream, bool pdl) {
+cudaError_t TF_CAT(qmm_launch_b, TF_BITS)(const QmmParams& p, int gs, int mt, int kw, cudaStream_t stream, bool pdl) {
   switch (gs) {
-    case 32: return launch_gs<32>(p, mt, stream, pdl);
-    case 64: return launch_gs<64>(p, mt, stream, pdl);
-    case 128: return launch_gs<128>(p, mt, stream, pdl);
+    case 32: return launch_gs<32>(p, mt, kw, stream, pdl);
+    case 64: return launch_gs<64>(p, mt, kw, stream, pdl);
+    case 128: return launch_gs<128>(p, mt, kw, stream, pdl);
     default: return cudaErrorInvalidValue;
   }
 }

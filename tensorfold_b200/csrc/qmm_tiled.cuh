@@ -11,10 +11,12 @@
 // so one to eight rows cost a single MMA per 256 weights.  An MMA output element depends only on its own A row and B
 // column, hence a row's bits never depend on the rows beside it.
 //
-// Block = 4 consumer warps (32 output columns each, all rows of the row tile) + 1 producer warp that issues the bulk
-// copies (one per stage for the packed weights, one per row of x) and computes the group sums of x for the consumers.
-// K slices of one column block run as one thread-block cluster and are summed in slice order through distributed
-// shared memory; with more than 8 slices, or when the caller wants the slices, they go to `part` in global memory.
+// Block = KW slice lanes x 4 consumer warps (a lane streams one K slice of the block's 128 output columns; each of its
+// warps owns 32 columns and all rows of the row tile) + a copy warp that issues the bulk copies (one per lane and stage
+// for the packed weights, one per row of x) + a sums warp that computes the group sums of x for the consumers.
+// The sk / KW blocks that hold the slices of one column block form a thread-block cluster; the slices are summed in
+// slice order through (distributed) shared memory.  When the caller wants the slices, or there are more than the
+// cluster can hold, they go to `part` in global memory.  How slices map to lanes and blocks never changes a bit.
 #pragma once
 
 #include <cooperative_groups.h>
@@ -40,17 +42,17 @@ struct QmmParams {
   int out_f32;
   int out_vec;                // rows of out allow 16-byte vector stores
   float* part;                // [sk, M, N] fp32 when the slices leave the kernel
-  int cluster;                // 1: slices form a cluster and are summed here
+  int cluster;                // 1: the blocks of a column block form a cluster and the slices are summed here
   int* err;                   // device error word (0 = none)
 };
 
-constexpr int QMM_THREADS = 160;
-constexpr int QMM_CONSUMERS = 128;
 constexpr int XROW_BYTES = 272;            // 128 inputs of bf16 + 16 bytes so ldmatrix rows fall in distinct banks
 constexpr int RED_STRIDE = 132;            // floats per row of the output staging tile (conflict-free fragment stores)
 
-template <int BITS, int GS, int MT>
+template <int BITS, int GS, int MT, int KW>
 struct QmmGeo {
+  static constexpr int CONSUMERS = 4 * KW;                  // consumer warps
+  static constexpr int THREADS = 32 * (CONSUMERS + 2);
   static constexpr int S = GS / 16;                         // MMA k-steps per group
   static constexpr int G = 128 / GS;                        // groups per stage (a stage covers 128 inputs)
   static constexpr int ROWS = 8 * MT;
@@ -59,9 +61,11 @@ struct QmmGeo {
   static constexpr int W_BYTES = G * UNITW * 4;
   static constexpr int X_BYTES = ROWS * XROW_BYTES;
   static constexpr int XS_BYTES = ROWS * G * 4;
-  static constexpr int STAGE = W_BYTES + X_BYTES + XS_BYTES;
-  static constexpr int RED_BYTES = ROWS * RED_STRIDE * 4;
-  static constexpr int NST_RAW = 98304 / STAGE;
+  static constexpr int LANE_STAGE = W_BYTES + X_BYTES + XS_BYTES;
+  static constexpr int STAGE = KW * LANE_STAGE;
+  static constexpr int RED_BYTES = KW * ROWS * RED_STRIDE * 4;
+  static constexpr int BUDGET = KW == 1 ? (MT <= 2 ? 73 * 1024 : 110 * 1024) : KW == 2 ? 110 * 1024 : 222 * 1024;
+  static constexpr int NST_RAW = BUDGET / STAGE;
   static constexpr int NST = NST_RAW < 2 ? 2 : (NST_RAW > 12 ? 12 : NST_RAW);
   static constexpr int BAR_BYTES = 3 * NST * 8 + 16;
   static constexpr int SMEM = NST * STAGE + BAR_BYTES;
@@ -84,10 +88,11 @@ __device__ __forceinline__ void ones_mma_group(float (&d)[4], uint32_t xaddr_lan
   }
 }
 
-template <int BITS, int GS, int MT>
-__global__ void __launch_bounds__(QMM_THREADS) qmm_tiled_kernel(const QmmParams p) {
-  using Geo = QmmGeo<BITS, GS, MT>;
+template <int BITS, int GS, int MT, int KW>
+__global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_kernel(const QmmParams p) {
+  using Geo = QmmGeo<BITS, GS, MT, KW>;
   constexpr int S = Geo::S, G = Geo::G, ROWS = Geo::ROWS, WPL = Geo::WPL, UNITW = Geo::UNITW, NST = Geo::NST;
+  constexpr int CONSUMERS = Geo::CONSUMERS, THREADS = Geo::THREADS;
   constexpr bool SPLIT = Fmt<BITS>::SPLIT;
 
   extern __shared__ __align__(128) uint8_t smem[];
@@ -97,16 +102,15 @@ __global__ void __launch_bounds__(QMM_THREADS) qmm_tiled_kernel(const QmmParams 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sums + NST);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int sb = blockIdx.x, m0 = blockIdx.y * ROWS, slice = blockIdx.z;
-  const int per = p.KG / p.sk;                              // groups of this slice
-  const int g_first = slice * per;
+  const int sb = blockIdx.x, m0 = blockIdx.y * ROWS;
+  const int per = p.KG / p.sk;                              // groups of a slice
   const int nstages = (per + G - 1) / G;
   const int rows_here = min(ROWS, p.M - m0);
 
   if (tid == 0) {
     for (int i = 0; i < NST; ++i) {
       mbar_init(full + i, 1);
-      mbar_init(empty + i, 4);
+      mbar_init(empty + i, CONSUMERS);
       mbar_init(sums + i, 1);
     }
     *abort_flag = 0;
@@ -115,10 +119,16 @@ __global__ void __launch_bounds__(QMM_THREADS) qmm_tiled_kernel(const QmmParams 
   __syncthreads();
   pdl_launch_dependents();
 
-  const uint32_t* wbase = p.w + static_cast<int64_t>(sb) * p.sb_stride + static_cast<int64_t>(g_first) * UNITW;
-
-  auto stage_ptr = [&](int slot) { return smem + slot * Geo::STAGE; };
+  // lane kw of this block streams slice blockIdx.z * KW + kw
+  auto slice_of = [&](int kw) { return static_cast<int>(blockIdx.z) * KW + kw; };
+  auto lane_ptr = [&](int slot, int kw) { return smem + slot * Geo::STAGE + kw * Geo::LANE_STAGE; };
   auto groups_of = [&](int st) { return min(G, per - st * G); };
+  auto give_up = [&](int code) {
+    if (lane == 0) {
+      *abort_flag = code;
+      atomicCAS(p.err, 0, code);
+    }
+  };
 
   float acc[2][MT][4];
 #pragma unroll
@@ -128,82 +138,85 @@ __global__ void __launch_bounds__(QMM_THREADS) qmm_tiled_kernel(const QmmParams 
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[h][mt][e] = 0.f;
 
-  if (warp == 4) {
-    // ------------------------------------------------------------------ producer: copies and group sums
+  if (warp == CONSUMERS) {
+    // ------------------------------------------------------------------ copy warp: weights and rows of x
+    const uint32_t* wsb = p.w + static_cast<int64_t>(sb) * p.sb_stride;
     auto issue_w = [&](int st, int slot) {
       if (lane == 0) {
         const int ng = groups_of(st);
-        const uint32_t bytes = ng * UNITW * 4 + rows_here * ng * GS * 2;
-        mbar_expect_tx(full + slot, bytes);
-        bulk_load(stage_ptr(slot), wbase + static_cast<int64_t>(st) * G * UNITW, ng * UNITW * 4, full + slot);
+        mbar_expect_tx(full + slot, KW * (ng * UNITW * 4 + rows_here * ng * GS * 2));
+#pragma unroll
+        for (int kw = 0; kw < KW; ++kw)
+          bulk_load(lane_ptr(slot, kw), wsb + (static_cast<int64_t>(slice_of(kw)) * per + st * G) * UNITW, ng * UNITW * 4,
+                    full + slot);
       }
     };
     auto issue_x = [&](int st, int slot) {
       const int ng = groups_of(st);
-      const int64_t k0 = static_cast<int64_t>(g_first + st * G) * GS;
-      for (int r = lane; r < rows_here; r += 32)
-        bulk_load(stage_ptr(slot) + Geo::W_BYTES + r * XROW_BYTES, p.x + (m0 + r) * p.ldx + k0, ng * GS * 2, full + slot);
+      for (int i = lane; i < KW * rows_here; i += 32) {
+        const int kw = i / rows_here, r = i % rows_here;
+        const int64_t k0 = (static_cast<int64_t>(slice_of(kw)) * per + st * G) * GS;
+        bulk_load(lane_ptr(slot, kw) + Geo::W_BYTES + r * XROW_BYTES, p.x + (m0 + r) * p.ldx + k0, ng * GS * 2,
+                  full + slot);
+      }
     };
     const int pro = min(NST, nstages);
     for (int st = 0; st < pro; ++st) issue_w(st, st);      // weights never depend on the previous kernel
     __syncwarp();
-    pdl_wait();                                            // x (and out) may be the previous kernel's
+    pdl_wait();                                            // x may be the previous kernel's output
     for (int st = 0; st < pro; ++st) issue_x(st, st);
-
     bool ok = true;
-    for (int st = 0; st < nstages && ok; ++st) {
+    for (int st = NST; st < nstages; ++st) {               // stage st goes where stage st - NST was
       const int slot = st % NST;
-      ok = mbar_wait(full + slot, (st / NST) & 1, abort_flag);
+      ok = mbar_wait(empty + slot, ((st - NST) / NST) & 1, abort_flag);
       if (!ok) {
-        if (lane == 0) {
-          *abort_flag = ERR_WAIT_FULL;
-          atomicCAS(p.err, 0, ERR_WAIT_FULL);
-        }
+        give_up(ERR_WAIT_EMPTY);
         break;
       }
-      const int ng = groups_of(st);
-      float* xs_s = reinterpret_cast<float*>(stage_ptr(slot) + Geo::W_BYTES + Geo::X_BYTES);
-      if (p.xs != nullptr) {
-        for (int i = lane; i < ng * ROWS; i += 32) {
-          const int u = i / ROWS, r = i % ROWS;
-          xs_s[u * ROWS + r] = r < rows_here ? p.xs[static_cast<int64_t>(m0 + r) * p.KG + g_first + st * G + u] : 0.f;
-        }
-      } else {
-        const uint32_t xs0 = smem_addr(stage_ptr(slot) + Geo::W_BYTES) + (lane & 7) * XROW_BYTES + (lane >> 3) * 16;
-        for (int u = 0; u < ng; ++u)
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            float d[4];
-            ones_mma_group<GS>(d, xs0 + mt * 8 * XROW_BYTES + u * GS * 2);
-            if (lane < 4) *reinterpret_cast<float2*>(xs_s + u * ROWS + mt * 8 + 2 * lane) = make_float2(d[0], d[1]);
-          }
-      }
+      issue_w(st, slot);
       __syncwarp();
-      if (lane == 0) mbar_arrive(sums + slot);
-      // refill the slot the consumers are about to finish: stage st - 1 + NST goes where stage st - 1 was
-      const int nst = st - 1 + NST;
-      if (st >= 1 && nst < nstages) {
-        const int slot2 = (st - 1) % NST;
-        ok = mbar_wait(empty + slot2, ((st - 1) / NST) & 1, abort_flag);
-        if (!ok) {
-          if (lane == 0) {
-            *abort_flag = ERR_WAIT_EMPTY;
-            atomicCAS(p.err, 0, ERR_WAIT_EMPTY);
-          }
-          break;
-        }
-        issue_w(nst, slot2);
-        __syncwarp();
-        issue_x(nst, slot2);
-      }
+      issue_x(st, slot);
     }
     if (!ok) {
       // give copies still in flight time to land before this block's shared memory is released
       for (int i = 0; i < 64; ++i) __nanosleep(20000);
     }
+  } else if (warp == CONSUMERS + 1) {
+    // ------------------------------------------------------------------ sums warp: group sums of x for every lane
+    pdl_wait();
+    for (int st = 0; st < nstages; ++st) {
+      const int slot = st % NST;
+      if (!mbar_wait(full + slot, (st / NST) & 1, abort_flag)) {
+        give_up(ERR_WAIT_FULL);
+        break;
+      }
+      const int ng = groups_of(st);
+#pragma unroll 1
+      for (int kw = 0; kw < KW; ++kw) {
+        float* xs_s = reinterpret_cast<float*>(lane_ptr(slot, kw) + Geo::W_BYTES + Geo::X_BYTES);
+        if (p.xs != nullptr) {
+          const int g0 = slice_of(kw) * per + st * G;
+          for (int i = lane; i < ng * ROWS; i += 32) {
+            const int u = i / ROWS, r = i % ROWS;
+            xs_s[u * ROWS + r] = r < rows_here ? p.xs[static_cast<int64_t>(m0 + r) * p.KG + g0 + u] : 0.f;
+          }
+        } else {
+          const uint32_t xs0 = smem_addr(lane_ptr(slot, kw) + Geo::W_BYTES) + (lane & 7) * XROW_BYTES + (lane >> 3) * 16;
+          for (int u = 0; u < ng; ++u)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              float d[4];
+              ones_mma_group<GS>(d, xs0 + mt * 8 * XROW_BYTES + u * GS * 2);
+              if (lane < 4) *reinterpret_cast<float2*>(xs_s + u * ROWS + mt * 8 + 2 * lane) = make_float2(d[0], d[1]);
+            }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sums + slot);
+    }
   } else {
     // ------------------------------------------------------------------ consumers: dequantise, MMA, affine epilogue
-    pdl_wait();
+    const int kw = warp >> 2, tp = warp & 3;
     const int g = lane >> 2, t = lane & 3;
     constexpr float OFFSET = code_offset(BITS);
     bool ok = true;
@@ -212,14 +225,11 @@ __global__ void __launch_bounds__(QMM_THREADS) qmm_tiled_kernel(const QmmParams 
       const uint32_t parity = (st / NST) & 1;
       ok = mbar_wait(full + slot, parity, abort_flag);
       if (!ok) {
-        if (lane == 0) {
-          *abort_flag = ERR_WAIT_FULL;
-          atomicCAS(p.err, 0, ERR_WAIT_FULL);
-        }
+        give_up(ERR_WAIT_FULL);
         break;
       }
       const int ng = groups_of(st);
-      const uint8_t* sp = stage_ptr(slot);
+      const uint8_t* sp = lane_ptr(slot, kw);
       const uint32_t* wst = reinterpret_cast<const uint32_t*>(sp);
       const uint32_t xaddr = smem_addr(sp + Geo::W_BYTES) + (lane & 7) * XROW_BYTES + (lane >> 3) * 16;
       const float* xs_s = reinterpret_cast<const float*>(sp + Geo::W_BYTES + Geo::X_BYTES);
@@ -228,7 +238,7 @@ __global__ void __launch_bounds__(QMM_THREADS) qmm_tiled_kernel(const QmmParams 
       for (int u = 0; u < ng; ++u) {
         uint32_t wd[WPL];
         {
-          const uint32_t* src = wst + u * UNITW + (warp * 32 + lane) * WPL;
+          const uint32_t* src = wst + u * UNITW + (tp * 32 + lane) * WPL;
           if constexpr (WPL % 4 == 0) {
 #pragma unroll
             for (int i = 0; i < WPL; i += 4) {
@@ -246,7 +256,7 @@ __global__ void __launch_bounds__(QMM_THREADS) qmm_tiled_kernel(const QmmParams 
             for (int i = 0; i < WPL; ++i) wd[i] = src[i];
           }
         }
-        const uint4 sbw = *reinterpret_cast<const uint4*>(wst + u * UNITW + TILE_PAIRS * 32 * WPL + warp * 32 + g * 4);
+        const uint4 sbw = *reinterpret_cast<const uint4*>(wst + u * UNITW + TILE_PAIRS * 32 * WPL + tp * 32 + g * 4);
 
         float P[2][MT][4];
 #pragma unroll
@@ -288,10 +298,7 @@ __global__ void __launch_bounds__(QMM_THREADS) qmm_tiled_kernel(const QmmParams 
         if (!sums_ready) {
           ok = mbar_wait(sums + slot, parity, abort_flag);
           if (!ok) {
-            if (lane == 0) {
-              *abort_flag = ERR_WAIT_SUMS;
-              atomicCAS(p.err, 0, ERR_WAIT_SUMS);
-            }
+            give_up(ERR_WAIT_SUMS);
             break;
           }
           sums_ready = true;
@@ -317,57 +324,64 @@ __global__ void __launch_bounds__(QMM_THREADS) qmm_tiled_kernel(const QmmParams 
   }
 
   // -------------------------------------------------------------------- output: stage, sum the slices in order, store
-  __syncthreads();                                          // every stage consumed: its memory becomes the staging tile
-  float* red = reinterpret_cast<float*>(smem);
-  if (warp < 4) {
-    const int g = lane >> 2, t = lane & 3;
+  __syncthreads();                                          // every stage consumed: its memory becomes the staging tiles
+  pdl_wait();                                               // nothing is written before the previous kernel is done
+  float* red = reinterpret_cast<float*>(smem);              // [KW][ROWS][RED_STRIDE]
+  constexpr int RED_TILE = ROWS * RED_STRIDE;
+  if (warp < CONSUMERS) {
+    const int kw = warp >> 2, tp = warp & 3, g = lane >> 2, t = lane & 3;
+    float* mine = red + kw * RED_TILE;
 #pragma unroll
     for (int h = 0; h < 2; ++h)
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        const int n = warp * 32 + h * 16 + g, m = mt * 8 + 2 * t;
-        red[m * RED_STRIDE + n] = acc[h][mt][0];
-        red[(m + 1) * RED_STRIDE + n] = acc[h][mt][1];
-        red[m * RED_STRIDE + n + 8] = acc[h][mt][2];
-        red[(m + 1) * RED_STRIDE + n + 8] = acc[h][mt][3];
+        const int n = tp * 32 + h * 16 + g, m = mt * 8 + 2 * t;
+        mine[m * RED_STRIDE + n] = acc[h][mt][0];
+        mine[(m + 1) * RED_STRIDE + n] = acc[h][mt][1];
+        mine[m * RED_STRIDE + n + 8] = acc[h][mt][2];
+        mine[(m + 1) * RED_STRIDE + n + 8] = acc[h][mt][3];
       }
   }
-  const bool clustered = p.cluster && p.sk > 1;
+  const int nblocks = p.sk / KW;                            // blocks holding the slices of this column block
+  const bool clustered = p.cluster && nblocks > 1;
   cg::cluster_group cluster = cg::this_cluster();
   if (clustered) cluster.sync(); else __syncthreads();
 
   const bool failed = *abort_flag != 0;
   const int n0 = sb * SB_COLS;
-  const int share = clustered ? p.sk : 1, mine = clustered ? slice : 0;
+  const bool summed = p.cluster != 0;                       // slices are summed here (else they go to part)
+  const int share = clustered ? nblocks : 1, mine_rank = clustered ? static_cast<int>(blockIdx.z) : 0;
   if (!failed) {
-    for (int idx = tid; idx < ROWS * 16; idx += QMM_THREADS) {
-      if (idx % share != mine) continue;
-      const int ml = idx >> 4, c8 = (idx & 15) * 8, m = m0 + ml, n = n0 + c8;
+    const int items = summed ? ROWS * 16 : KW * ROWS * 16;
+    for (int idx = tid; idx < items; idx += THREADS) {
+      if (idx % share != mine_rank) continue;
+      const int kw_item = idx / (ROWS * 16), rem = idx % (ROWS * 16);
+      const int ml = rem >> 4, c8 = (rem & 15) * 8, m = m0 + ml, n = n0 + c8;
       if (ml >= rows_here || n >= p.N) continue;
+      const int off = ml * RED_STRIDE + c8;
       float v[8];
-      {
-        const float4 a = *reinterpret_cast<const float4*>(red + ml * RED_STRIDE + c8);
-        const float4 b = *reinterpret_cast<const float4*>(red + ml * RED_STRIDE + c8 + 4);
-        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-      }
-      if (clustered) {
-        // slice order: ((s0 + s1) + s2) + ...; this block holds slice `slice`, the others are read remotely
-        float tot[8];
+      if (summed) {
+        // slice order ((s0 + s1) + s2) + ...: slice s is lane s % KW of block s / KW of the cluster
 #pragma unroll 1
-        for (int r = 0; r < p.sk; ++r) {
-          const float* src = r == slice ? red : cluster.map_shared_rank(red, r);
-          const float4 a = *reinterpret_cast<const float4*>(src + ml * RED_STRIDE + c8);
-          const float4 b = *reinterpret_cast<const float4*>(src + ml * RED_STRIDE + c8 + 4);
-          const float w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        for (int s = 0; s < p.sk; ++s) {
+          const int b = s / KW;
+          const float* tile = (b == mine_rank || !clustered) ? red : cluster.map_shared_rank(red, b);
+          const float* src = tile + (s % KW) * RED_TILE + off;
+          const float4 lo = *reinterpret_cast<const float4*>(src);
+          const float4 hi = *reinterpret_cast<const float4*>(src + 4);
+          const float w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
-          for (int e = 0; e < 8; ++e) tot[e] = r == 0 ? w[e] : tot[e] + w[e];
+          for (int e = 0; e < 8; ++e) v[e] = s == 0 ? w[e] : v[e] + w[e];
         }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = tot[e];
+      } else {
+        const float* src = red + kw_item * RED_TILE + off;
+        const float4 lo = *reinterpret_cast<const float4*>(src);
+        const float4 hi = *reinterpret_cast<const float4*>(src + 4);
+        v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
       }
       const int valid = min(8, p.N - n);
-      if (!clustered && p.sk > 1) {
-        float* dst = p.part + (static_cast<int64_t>(slice) * p.M + m) * p.N + n;
+      if (!summed) {
+        float* dst = p.part + (static_cast<int64_t>(slice_of(kw_item)) * p.M + m) * p.N + n;
         for (int e = 0; e < valid; ++e) dst[e] = v[e];
       } else if (p.out_f32) {
         float* dst = reinterpret_cast<float*>(p.out) + m * p.ldo + n;
@@ -392,7 +406,7 @@ __global__ void __launch_bounds__(QMM_THREADS) qmm_tiled_kernel(const QmmParams 
       }
     }
   }
-  if (clustered) cluster.sync();                            // peers may still be reading this block's tile
+  if (clustered) cluster.sync();                            // peers may still be reading this block's tiles
 }
 
 }  // namespace tf

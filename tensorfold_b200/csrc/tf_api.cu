@@ -3,6 +3,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
+#include <string>
 
 #include "../../include/tensorfold_b200.h"
 #include "qmm_launch.h"
@@ -36,6 +37,7 @@ struct DeviceState {
   int* err = nullptr;
 };
 DeviceState g_devices[MAX_DEVICES];
+int g_lanes_pref = 0;                 // tuning knob (tf_tune): preferred slice lanes per block, 0 = default
 std::mutex g_init_mutex;
 
 }  // namespace
@@ -216,6 +218,14 @@ int tf_device_error(int device, void* stream, int* code) {
   return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_device_error");
 }
 
+int tf_tune(const char* key, int value) {
+  if (key != nullptr && std::string(key) == "qmm_lanes" && (value == 0 || value == 1 || value == 2 || value == 4)) {
+    g_lanes_pref = value;
+    return TF_OK;
+  }
+  return fail(TF_ERR_ARG, "tf_tune: unknown key or value");
+}
+
 int tf_split_k(int n, int k, int gs, int target) {
   if (n < 1 || k < 1 || gs < 1) return TF_ERR_ARG;
   const int tiles = (n + 63) / 64, groups = k / gs;
@@ -280,9 +290,21 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
   if (reinterpret_cast<uintptr_t>(x) % 16 || (m > 1 && ldx % 8) || ldx < k)
     return fail(TF_ERR_ALIGN, "tf_qmm: x rows must start on 16-byte boundaries (ldx %% 8 == 0, ldx >= k)");
   if (reinterpret_cast<uintptr_t>(tiled) % 16) return fail(TF_ERR_ALIGN, "tf_qmm: tiled weights must be 16-byte aligned");
-  const bool slices_out = sk > 1 && (!reduce || sk > 8);
-  if (slices_out && !part) return fail(TF_ERR_ARG, "tf_qmm: part [sk, m, n] is required for %d slices with reduce=%d", sk, reduce);
-  if (!(slices_out && !reduce) && (!out || ldo < n)) return fail(TF_ERR_ARG, "tf_qmm: out must be [m, n] with ldo >= n");
+  // Slices map to (block, lane) pairs: kw lanes a block, sk / kw blocks a cluster (at most 8).  The mapping never
+  // changes a bit of the result; it is picked for occupancy and may depend on the row count.
+  const int mt = mt_for_rows(m);
+  int kw = 1;
+  {
+    int want = g_lanes_pref > 0 ? g_lanes_pref : 2;
+    if (want > max_lanes(mt)) want = max_lanes(mt);
+    for (int c = want; c >= 1; c >>= 1)
+      if (sk % c == 0) {
+        kw = c;
+        break;
+      }
+    while (sk / kw > 8 && kw * 2 <= max_lanes(mt) && sk % (kw * 2) == 0) kw *= 2;
+  }
+  const bool slices_out = sk > 1 && (!reduce || sk / kw > 8);
   if (slices_out && reduce && ldo != n) return fail(TF_ERR_ARG, "tf_qmm: more than 8 slices need a contiguous out (ldo == n)");
   if (m > 65535 * 8) return fail(TF_ERR_ARG, "tf_qmm: too many rows");
   DeviceState* st = nullptr;
@@ -305,16 +327,15 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
   p.part = part;
   p.cluster = !slices_out;
   p.err = st->err;
-  const int mt = mt_for_rows(m);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   switch (bits) {
-    case 2: e = qmm_launch_b2(p, gs, mt, s, pdl != 0); break;
-    case 3: e = qmm_launch_b3(p, gs, mt, s, pdl != 0); break;
-    case 4: e = qmm_launch_b4(p, gs, mt, s, pdl != 0); break;
-    case 5: e = qmm_launch_b5(p, gs, mt, s, pdl != 0); break;
-    case 6: e = qmm_launch_b6(p, gs, mt, s, pdl != 0); break;
-    default: e = qmm_launch_b8(p, gs, mt, s, pdl != 0); break;
+    case 2: e = qmm_launch_b2(p, gs, mt, kw, s, pdl != 0); break;
+    case 3: e = qmm_launch_b3(p, gs, mt, kw, s, pdl != 0); break;
+    case 4: e = qmm_launch_b4(p, gs, mt, kw, s, pdl != 0); break;
+    case 5: e = qmm_launch_b5(p, gs, mt, kw, s, pdl != 0); break;
+    case 6: e = qmm_launch_b6(p, gs, mt, kw, s, pdl != 0); break;
+    default: e = qmm_launch_b8(p, gs, mt, kw, s, pdl != 0); break;
   }
   if (e != cudaSuccess) return cuda_fail(e, "tf_qmm launch");
   if (slices_out && reduce) return tf_reduce_slices(part, sk, static_cast<int64_t>(m) * n, out, out_f32, stream);

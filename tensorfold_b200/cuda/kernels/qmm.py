@@ -82,6 +82,15 @@ def split_k(n: int, k: int, gs: int = 64, target: int = 192) -> int:
     return sk
 
 
+LANE_TARGET = 2048     # 64-column tiles x slices this build aims for: enough warps in flight to fill 148 SMs
+
+
+def default_split(n: int, k: int, gs: int = 64) -> int:
+    """The K slices ``matmul`` uses when it is given none: ``split_k`` with this build's occupancy target."""
+
+    return split_k(n, k, gs, LANE_TARGET)
+
+
 def bucket(m: int) -> int:
     """The reference's row tile (16, 32, else 64); kept for callers that size buffers by it.  Tiles never change bits."""
 
@@ -130,7 +139,7 @@ def matmul(x: torch.Tensor, q: Q4, xs: torch.Tensor | None = None, *, sk: int | 
     kg = q.k // q.gs
     if xs is not None and (xs.dtype != torch.float32 or xs.shape != (m, kg) or not xs.is_contiguous()):
         raise ValueError(f"matmul: xs must be contiguous ({m}, {kg}) fp32")
-    sk = sk or split_k(q.n, q.k, q.gs)
+    sk = sk or default_split(q.n, q.k, q.gs)
     if sk < 1 or kg % sk:
         raise ValueError("matmul: K must split into whole groups a slice")
     slices = sk > 1 and not reduce

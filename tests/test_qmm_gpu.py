@@ -99,7 +99,7 @@ def test_accuracy_every_format(bits, gs):
     ref = oracle_f64(x, words, scales, biases, gs, bits)
     for m in (1, 16):
         assert_close_bf16(qmm.matmul(x[:m].to(DEV), q), ref[:m], f"{bits}b/g{gs} M={m}")
-    for sk in (1, 2, 4):
+    for sk in (1, 2, 4, 16):
         assert_close_bf16(qmm.matmul(x.to(DEV), q, sk=sk), ref, f"{bits}b/g{gs} sk={sk}")
 
 
@@ -116,8 +116,8 @@ def test_config0_single_matmul():
 
 def test_split_depends_only_on_shape():
     for n, k in [(48, 5120), (1024, 5120), (5120, 6144), (17408, 5120), (5120, 17408), (248320, 5120)]:
-        sk = qmm.split_k(n, k)
-        assert sk == qmm.split_k(n, k) and (k // 64) % sk == 0
+        sk = qmm.default_split(n, k)
+        assert sk == qmm.default_split(n, k) and (k // 64) % sk == 0
 
 
 def test_strided_rows_buffers_and_unreduced_slices():
@@ -129,7 +129,7 @@ def test_strided_rows_buffers_and_unreduced_slices():
     assert torch.equal(qmm.matmul(x, q), want)
     out = torch.empty_like(want)
     assert qmm.matmul(x, q, out=out) is out and torch.equal(out, want)
-    sk = qmm.split_k(n, k)
+    sk = qmm.default_split(n, k)
     assert sk > 1
     slices = qmm.matmul(x, q, reduce=False, f32=True)
     assert slices.shape == (sk, 24, n)
@@ -161,10 +161,32 @@ def test_super_block_views_give_the_same_columns():
     n, k, gs = 1024, 2048, 64
     q, _ = packed(n, k, gs, 29)
     x = synthetic.activations(9, k, 4).to(DEV)
-    sk = qmm.split_k(n, k, gs)
+    sk = qmm.default_split(n, k, gs)
     full = qmm.matmul(x, q, sk=sk)
     part = qmm.Q4(q.weight[2:5], None, None, 384, k, gs)
     assert torch.equal(qmm.matmul(x, part, sk=sk), full[:, 256:640])
+
+
+def test_lane_mapping_never_changes_bits():
+    """How K slices map to blocks and lanes is a tuning knob; every setting gives the same bits."""
+
+    n, k, gs = 1024, 4096, 64
+    q, _ = packed(n, k, gs, 41)
+    x = synthetic.activations(33, k, 6).to(DEV)
+    lib = _lib.lib()
+    want = {m: qmm.matmul(x[:m], q, sk=8, f32=True) for m in (1, 16, 33)}
+    try:
+        for lanes in (1, 2, 4):
+            _lib.check(lib.tf_tune(b"qmm_lanes", lanes), "tune")
+            for m in (1, 16, 33):
+                assert torch.equal(qmm.matmul(x[:m], q, sk=8, f32=True), want[m]), (lanes, m)
+            sl = qmm.matmul(x[:16], q, sk=8, f32=True, reduce=False)
+            total = sl[0]
+            for s in range(1, 8):
+                total = total + sl[s]
+            assert torch.equal(total, want[16])
+    finally:
+        lib.tf_tune(b"qmm_lanes", 0)
 
 
 def test_no_wait_gave_up():
