@@ -40,8 +40,8 @@ int tf_init(int device);
  * Synchronises `stream`.  host: *code. */
 int tf_device_error(int device, void* stream, int* code);
 
-/* Performance knobs that never change a result bit.  key "qmm_lanes": K slices a thread block streams side by side
- * (1, 2 or 4; 0 = default).  No counterpart in the reference. */
+/* Performance knobs that never change a result bit.  key "qmm_lanes": 128-column super-blocks a thread block streams side
+ * by side (1, 2 or 4; 0 = default).  No counterpart in the reference. */
 int tf_tune(const char* key, int value);
 
 /* ---- shape-only planning (host functions) -------------------------------------------------------------------- */
@@ -78,8 +78,8 @@ int tf_group_sums(const void* x, int64_t ldx, int m, int k, int gs, float* xs, v
  *            (0: dense, (k / gs) * tf_unit_words)
  *   sk       K slices (>= 1, divides k / gs); sums are added in slice order
  *   out      [m, n] bf16 (out_f32 = 0) or fp32, row stride ldo elements; ignored when reduce = 0 and sk > 1
- *   part     [sk, m, n] fp32, required when reduce = 0 with sk > 1, or when sk > 8 (up to 32 slices are summed on
- *            chip for m <= 16, 16 for m <= 32; beyond that they pass through part), else may be NULL
+ *   part     [sk, m, n] fp32, required when reduce = 0 with sk > 1, or when sk > 8 (up to 8 slices are summed on
+ *            chip; more pass through part), else may be NULL
  *   reduce   1: out receives the sum of the slices; 0: the slices stay in part (out untouched)
  *   pdl      1: launch with programmatic stream serialisation, so this call's weight prefetch overlaps the tail of the
  *            previous kernel in the stream (it still waits for that kernel before reading x or writing out)

@@ -6,7 +6,9 @@ import ctypes
 from functools import lru_cache
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libtensorfold_b200.so"
+import os
+
+LIB_PATH = Path(os.environ.get("TENSORFOLD_B200_LIB") or Path(__file__).resolve().parent / "libtensorfold_b200.so")
 
 _vp, _i32, _i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
 

@@ -12,9 +12,10 @@ namespace {
 template <int GS, int MT, int KW>
 cudaError_t launch(const QmmParams& p, cudaStream_t stream, bool pdl) {
   using Geo = QmmGeo<TF_BITS, GS, MT, KW>;
-  const int nblocks = p.sk / KW;
+  const int nblocks = p.sk;
+  const int nsb = (p.N + SB_COLS - 1) / SB_COLS;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((p.N + SB_COLS - 1) / SB_COLS, (p.M + Geo::ROWS - 1) / Geo::ROWS, nblocks);
+  cfg.gridDim = dim3((nsb + KW - 1) / KW, (p.M + Geo::ROWS - 1) / Geo::ROWS, nblocks);
   cfg.blockDim = dim3(Geo::THREADS);
   cfg.dynamicSmemBytes = Geo::SMEM;
   cfg.stream = stream;

@@ -11,12 +11,12 @@
 // so one to eight rows cost a single MMA per 256 weights.  An MMA output element depends only on its own A row and B
 // column, hence a row's bits never depend on the rows beside it.
 //
-// Block = KW slice lanes x 4 consumer warps (a lane streams one K slice of the block's 128 output columns; each of its
-// warps owns 32 columns and all rows of the row tile) + a copy warp that issues the bulk copies (one per lane and stage
-// for the packed weights, one per row of x) + a sums warp that computes the group sums of x for the consumers.
-// The sk / KW blocks that hold the slices of one column block form a thread-block cluster; the slices are summed in
-// slice order through (distributed) shared memory.  When the caller wants the slices, or there are more than the
-// cluster can hold, they go to `part` in global memory.  How slices map to lanes and blocks never changes a bit.
+// Block = KW column lanes x 4 consumer warps (a lane streams one 128-column super-block over the block's K slice; each
+// of its warps owns 32 columns and all rows of the row tile) + a copy warp (one bulk copy per lane and stage for the
+// packed weights, 16-byte asynchronous copies for the rows of x, which all lanes share) + a sums warp that computes the
+// group sums of x once for the whole block.  The blocks that hold the K slices of the same columns form a thread-block
+// cluster; the slices are summed in slice order through distributed shared memory.  When the caller wants the slices,
+// or there are more than a cluster can hold, they go to `part` in global memory.  Geometry never changes a bit.
 #pragma once
 
 #include <cooperative_groups.h>
@@ -27,6 +27,20 @@
 namespace tf {
 
 namespace cg = cooperative_groups;
+
+#ifdef TF_TRACE
+// debug build only: block (0, 0, 0) logs (event, stage, clock) into shared memory, dumped to p.part when it ends
+#define TF_TRACE_EVENTS 200
+#define TF_MARK(ev, st)                                                                    \
+  do {                                                                                     \
+    if (tf_trace_on && lane == 0 && tf_tr < TF_TRACE_EVENTS) {                             \
+      tf_trace[warp][tf_tr] = (static_cast<long long>((ev) * 1000 + (st)) << 40) | (clock64() & 0xFFFFFFFFFFLL); \
+      ++tf_tr;                                                                             \
+    }                                                                                      \
+  } while (0)
+#else
+#define TF_MARK(ev, st) do {} while (0)
+#endif
 
 struct QmmParams {
   const __nv_bfloat16* x;     // [M, K] bf16, row stride ldx elements, rows 16-byte aligned
@@ -42,12 +56,22 @@ struct QmmParams {
   int out_f32;
   int out_vec;                // rows of out allow 16-byte vector stores
   float* part;                // [sk, M, N] fp32 when the slices leave the kernel
-  int cluster;                // 1: the blocks of a column block form a cluster and the slices are summed here
+  int cluster;                // 1: the sk blocks of a column block form a cluster and the slices are summed here
   int* err;                   // device error word (0 = none)
 };
 
 constexpr int XROW_BYTES = 272;            // 128 inputs of bf16 + 16 bytes so ldmatrix rows fall in distinct banks
 constexpr int RED_STRIDE = 132;            // floats per row of the output staging tile (conflict-free fragment stores)
+
+#ifndef TF_BUDGET1_KB
+#define TF_BUDGET1_KB 73
+#endif
+#ifndef TF_BUDGET2_KB
+#define TF_BUDGET2_KB 110
+#endif
+#ifndef TF_BUDGET4_KB
+#define TF_BUDGET4_KB 222
+#endif
 
 template <int BITS, int GS, int MT, int KW>
 struct QmmGeo {
@@ -58,17 +82,22 @@ struct QmmGeo {
   static constexpr int ROWS = 8 * MT;
   static constexpr int WPL = words_per_lane(BITS, GS);
   static constexpr int UNITW = unit_words(BITS, GS);
-  static constexpr int W_BYTES = G * UNITW * 4;
+  static constexpr int W_BYTES = G * UNITW * 4;             // one lane's weights of a stage
   static constexpr int X_BYTES = ROWS * XROW_BYTES;
   static constexpr int XS_BYTES = ROWS * G * 4;
-  static constexpr int LANE_STAGE = W_BYTES + X_BYTES + XS_BYTES;
-  static constexpr int STAGE = KW * LANE_STAGE;
+  static constexpr int X_OFF = KW * W_BYTES;
+  static constexpr int XS_OFF = X_OFF + X_BYTES;
+  static constexpr int STAGE = XS_OFF + XS_BYTES;
   static constexpr int RED_BYTES = KW * ROWS * RED_STRIDE * 4;
-  static constexpr int BUDGET = KW == 1 ? (MT <= 2 ? 73 * 1024 : 110 * 1024) : KW == 2 ? 110 * 1024 : 222 * 1024;
-  static constexpr int NST_RAW = BUDGET / STAGE;
-  static constexpr int NST = NST_RAW < 2 ? 2 : (NST_RAW > 12 ? 12 : NST_RAW);
+  static constexpr int BUDGET = (MT > 2 ? 110 : KW == 1 ? TF_BUDGET1_KB : KW == 2 ? TF_BUDGET2_KB : TF_BUDGET4_KB) * 1024;
+  static constexpr int NST_A = BUDGET / STAGE, NST_B = (RED_BYTES + STAGE - 1) / STAGE;
+  static constexpr int NST_C = NST_A < 2 ? 2 : (NST_A > 12 ? 12 : NST_A);
+  static constexpr int NST = NST_C < NST_B ? NST_B : NST_C;
   static constexpr int BAR_BYTES = 3 * NST * 8 + 16;
   static constexpr int SMEM = NST * STAGE + BAR_BYTES;
+  // blocks per SM the register file should allow (64 registers a thread is the floor the kernel needs)
+  static constexpr int BY_SMEM = (227 * 1024) / (SMEM + 1024), BY_REGS = 65536 / (THREADS * 64);
+  static constexpr int MINB = MT > 2 ? 1 : (BY_SMEM < BY_REGS ? BY_SMEM : BY_REGS) < 1 ? 1 : (BY_SMEM < BY_REGS ? BY_SMEM : BY_REGS);
   static_assert(STAGE % 16 == 0 && W_BYTES % 16 == 0 && X_BYTES % 16 == 0, "stage parts stay 16-byte aligned");
   static_assert(NST * STAGE >= RED_BYTES, "the output staging tile reuses the stage memory");
   static_assert(SMEM <= 227 * 1024, "fits the shared memory of an SM");
@@ -89,27 +118,44 @@ __device__ __forceinline__ void ones_mma_group(float (&d)[4], uint32_t xaddr_lan
 }
 
 template <int BITS, int GS, int MT, int KW>
-__global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_kernel(const QmmParams p) {
+__global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS, QmmGeo<BITS, GS, MT, KW>::MINB)
+qmm_tiled_kernel(const QmmParams p) {
   using Geo = QmmGeo<BITS, GS, MT, KW>;
   constexpr int S = Geo::S, G = Geo::G, ROWS = Geo::ROWS, WPL = Geo::WPL, UNITW = Geo::UNITW, NST = Geo::NST;
   constexpr int CONSUMERS = Geo::CONSUMERS, THREADS = Geo::THREADS;
   constexpr bool SPLIT = Fmt<BITS>::SPLIT;
 
   extern __shared__ __align__(128) uint8_t smem[];
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + NST * Geo::STAGE);
-  uint64_t* empty = full + NST;
-  uint64_t* sums = empty + NST;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + NST * Geo::STAGE);   // weights and x of a stage have landed
+  uint64_t* empty = full + NST;                                           // every consumer warp is done with a stage
+  uint64_t* sums = empty + NST;                                           // the stage's group sums are written
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sums + NST);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int sb = blockIdx.x, m0 = blockIdx.y * ROWS;
+#ifdef TF_TRACE
+  __shared__ long long tf_trace[6][TF_TRACE_EVENTS];
+  int tf_tr = 0;
+  const bool tf_trace_on = blockIdx.x == TF_TRACE_BX && blockIdx.y == 0 && blockIdx.z == 0 && warp < 6;
+  unsigned long long tf_t_start;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tf_t_start));
+  unsigned int tf_smid;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(tf_smid));
+  unsigned long long tf_t1 = 0, tf_t2 = 0, tf_t3 = 0;
+#define TF_STAMP(v) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v))
+  for (int i = tid; i < 6 * TF_TRACE_EVENTS; i += blockDim.x) (&tf_trace[0][0])[i] = 0;
+#endif
+  const int nsb = (p.N + SB_COLS - 1) / SB_COLS;
+  const int sb0 = blockIdx.x * KW;                          // lane kw streams super-block sb0 + kw (if it exists)
+  const int lanes_here = min(KW, nsb - sb0);
+  const int m0 = blockIdx.y * ROWS, slice = blockIdx.z;
   const int per = p.KG / p.sk;                              // groups of a slice
+  const int g_first = slice * per;
   const int nstages = (per + G - 1) / G;
   const int rows_here = min(ROWS, p.M - m0);
 
   if (tid == 0) {
     for (int i = 0; i < NST; ++i) {
-      mbar_init(full + i, 1);
+      mbar_init(full + i, 1 + 32);                          // the expect_tx arrive + each copy-warp lane's cp.async arrive
       mbar_init(empty + i, CONSUMERS);
       mbar_init(sums + i, 1);
     }
@@ -117,11 +163,12 @@ __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_k
     mbar_fence_init();
   }
   __syncthreads();
+#ifdef TF_TRACE
+  TF_STAMP(tf_t1);
+#endif
   pdl_launch_dependents();
 
-  // lane kw of this block streams slice blockIdx.z * KW + kw
-  auto slice_of = [&](int kw) { return static_cast<int>(blockIdx.z) * KW + kw; };
-  auto lane_ptr = [&](int slot, int kw) { return smem + slot * Geo::STAGE + kw * Geo::LANE_STAGE; };
+  auto stage_ptr = [&](int slot) { return smem + slot * Geo::STAGE; };
   auto groups_of = [&](int st) { return min(G, per - st * G); };
   auto give_up = [&](int code) {
     if (lane == 0) {
@@ -139,30 +186,29 @@ __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_k
       for (int e = 0; e < 4; ++e) acc[h][mt][e] = 0.f;
 
   if (warp == CONSUMERS) {
-    // ------------------------------------------------------------------ copy warp: weights and rows of x
-    const uint32_t* wsb = p.w + static_cast<int64_t>(sb) * p.sb_stride;
+    // ------------------------------------------------------------------ copy warp: weights (bulk) and rows of x (16 B)
+    const uint32_t* wbase = p.w + static_cast<int64_t>(sb0) * p.sb_stride + static_cast<int64_t>(g_first) * UNITW;
     auto issue_w = [&](int st, int slot) {
       if (lane == 0) {
         const int ng = groups_of(st);
-        mbar_expect_tx(full + slot, KW * (ng * UNITW * 4 + rows_here * ng * GS * 2));
-#pragma unroll
-        for (int kw = 0; kw < KW; ++kw)
-          bulk_load(lane_ptr(slot, kw), wsb + (static_cast<int64_t>(slice_of(kw)) * per + st * G) * UNITW, ng * UNITW * 4,
-                    full + slot);
+        mbar_expect_tx(full + slot, lanes_here * ng * UNITW * 4);
+        for (int kw = 0; kw < lanes_here; ++kw)
+          bulk_load(stage_ptr(slot) + kw * Geo::W_BYTES, wbase + kw * p.sb_stride + static_cast<int64_t>(st) * G * UNITW,
+                    ng * UNITW * 4, full + slot);
       }
     };
     auto issue_x = [&](int st, int slot) {
-      const int ng = groups_of(st);
-      for (int i = lane; i < KW * rows_here; i += 32) {
-        const int kw = i / rows_here, r = i % rows_here;
-        const int64_t k0 = (static_cast<int64_t>(slice_of(kw)) * per + st * G) * GS;
-        bulk_load(lane_ptr(slot, kw) + Geo::W_BYTES + r * XROW_BYTES, p.x + (m0 + r) * p.ldx + k0, ng * GS * 2,
-                  full + slot);
+      const int cpr = groups_of(st) * GS / 8;               // 16-byte chunks a row
+      const __nv_bfloat16* src = p.x + static_cast<int64_t>(m0) * p.ldx + static_cast<int64_t>(g_first + st * G) * GS;
+      uint8_t* dst = stage_ptr(slot) + Geo::X_OFF;
+      for (int c = lane; c < rows_here * cpr; c += 32) {
+        const int r = c / cpr, q = c - r * cpr;
+        cp_async16(dst + r * XROW_BYTES + q * 16, src + r * p.ldx + q * 8);
       }
+      cp_async_arrive(full + slot);
     };
     const int pro = min(NST, nstages);
     for (int st = 0; st < pro; ++st) issue_w(st, st);      // weights never depend on the previous kernel
-    __syncwarp();
     pdl_wait();                                            // x may be the previous kernel's output
     for (int st = 0; st < pro; ++st) issue_x(st, st);
     bool ok = true;
@@ -173,16 +219,17 @@ __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_k
         give_up(ERR_WAIT_EMPTY);
         break;
       }
+      TF_MARK(10, st);
       issue_w(st, slot);
-      __syncwarp();
       issue_x(st, slot);
+      TF_MARK(11, st);
     }
     if (!ok) {
       // give copies still in flight time to land before this block's shared memory is released
       for (int i = 0; i < 64; ++i) __nanosleep(20000);
     }
   } else if (warp == CONSUMERS + 1) {
-    // ------------------------------------------------------------------ sums warp: group sums of x for every lane
+    // ------------------------------------------------------------------ sums warp: group sums of x, once per block
     pdl_wait();
     for (int st = 0; st < nstages; ++st) {
       const int slot = st % NST;
@@ -191,51 +238,60 @@ __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_k
         break;
       }
       const int ng = groups_of(st);
-#pragma unroll 1
-      for (int kw = 0; kw < KW; ++kw) {
-        float* xs_s = reinterpret_cast<float*>(lane_ptr(slot, kw) + Geo::W_BYTES + Geo::X_BYTES);
-        if (p.xs != nullptr) {
-          const int g0 = slice_of(kw) * per + st * G;
-          for (int i = lane; i < ng * ROWS; i += 32) {
-            const int u = i / ROWS, r = i % ROWS;
-            xs_s[u * ROWS + r] = r < rows_here ? p.xs[static_cast<int64_t>(m0 + r) * p.KG + g0 + u] : 0.f;
-          }
-        } else {
-          const uint32_t xs0 = smem_addr(lane_ptr(slot, kw) + Geo::W_BYTES) + (lane & 7) * XROW_BYTES + (lane >> 3) * 16;
-          for (int u = 0; u < ng; ++u)
+      TF_MARK(20, st);
+      float* xs_s = reinterpret_cast<float*>(stage_ptr(slot) + Geo::XS_OFF);
+      if (p.xs != nullptr) {
+        const int g0 = g_first + st * G;
+        for (int i = lane; i < ng * ROWS; i += 32) {
+          const int u = i / ROWS, r = i % ROWS;
+          xs_s[u * ROWS + r] = r < rows_here ? p.xs[static_cast<int64_t>(m0 + r) * p.KG + g0 + u] : 0.f;
+        }
+      } else {
+        const uint32_t xs0 = smem_addr(stage_ptr(slot) + Geo::X_OFF) + (lane & 7) * XROW_BYTES + (lane >> 3) * 16;
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-              float d[4];
-              ones_mma_group<GS>(d, xs0 + mt * 8 * XROW_BYTES + u * GS * 2);
-              if (lane < 4) *reinterpret_cast<float2*>(xs_s + u * ROWS + mt * 8 + 2 * lane) = make_float2(d[0], d[1]);
-            }
+        for (int u = 0; u < G; ++u) {
+          if (u >= ng) break;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            float d[4];
+            ones_mma_group<GS>(d, xs0 + mt * 8 * XROW_BYTES + u * GS * 2);
+            if (lane < 4) *reinterpret_cast<float2*>(xs_s + u * ROWS + mt * 8 + 2 * lane) = make_float2(d[0], d[1]);
+          }
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(sums + slot);
+      if (lane == 0) mbar_arrive(sums + slot);               // also tells the consumers that the stage has landed
+      TF_MARK(21, st);
     }
   } else {
     // ------------------------------------------------------------------ consumers: dequantise, MMA, affine epilogue
     const int kw = warp >> 2, tp = warp & 3;
     const int g = lane >> 2, t = lane & 3;
+    const bool active = kw < lanes_here;
     constexpr float OFFSET = code_offset(BITS);
     bool ok = true;
+    bool ready = mbar_try_wait(sums + 0, 0);                // probe early: the answer is needed only after the loop head
     for (int st = 0; st < nstages && ok; ++st) {
       const int slot = st % NST;
       const uint32_t parity = (st / NST) & 1;
-      ok = mbar_wait(full + slot, parity, abort_flag);
+      TF_MARK(0, st);
+      ok = mbar_wait_probed(ready, sums + slot, parity, abort_flag);
+      TF_MARK(1, st);
       if (!ok) {
-        give_up(ERR_WAIT_FULL);
+        give_up(ERR_WAIT_SUMS);
         break;
       }
       const int ng = groups_of(st);
-      const uint8_t* sp = lane_ptr(slot, kw);
-      const uint32_t* wst = reinterpret_cast<const uint32_t*>(sp);
-      const uint32_t xaddr = smem_addr(sp + Geo::W_BYTES) + (lane & 7) * XROW_BYTES + (lane >> 3) * 16;
-      const float* xs_s = reinterpret_cast<const float*>(sp + Geo::W_BYTES + Geo::X_BYTES);
-      bool sums_ready = false;
-#pragma unroll 1
-      for (int u = 0; u < ng; ++u) {
+      const uint8_t* sp = stage_ptr(slot);
+      const uint32_t* wst = reinterpret_cast<const uint32_t*>(sp + kw * Geo::W_BYTES);
+      const uint32_t xaddr = smem_addr(sp + Geo::X_OFF) + (lane & 7) * XROW_BYTES + (lane >> 3) * 16;
+      const float* xs_s = reinterpret_cast<const float*>(sp + Geo::XS_OFF);
+#pragma unroll
+      for (int u = 0; u < G; ++u) {
+        if (u >= ng) break;
+        if (u == ng - 1 && st + 1 < nstages)               // probe the next stage while this group computes
+          ready = mbar_try_wait(sums + (st + 1) % NST, ((st + 1) / NST) & 1);
+        if (!active) continue;
         uint32_t wd[WPL];
         {
           const uint32_t* src = wst + u * UNITW + (tp * 32 + lane) * WPL;
@@ -259,13 +315,6 @@ __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_k
         const uint4 sbw = *reinterpret_cast<const uint4*>(wst + u * UNITW + TILE_PAIRS * 32 * WPL + tp * 32 + g * 4);
 
         float P[2][MT][4];
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) P[h][mt][e] = 0.f;
-
         uint32_t bf[MT][4];
 #pragma unroll
         for (int s = 0; s < S; ++s) {
@@ -279,7 +328,10 @@ __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_k
 #pragma unroll
             for (int j = 0; j < 4; ++j) a[j] = pair_reg<BITS, GS, false>(wd, (h * S + s) * 4 + j);
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) mma_bf16(P[h][mt], a, bf[mt][2 * (s & 1)], bf[mt][2 * (s & 1) + 1]);
+            for (int mt = 0; mt < MT; ++mt) {
+              if (s == 0) mma_bf16_zero(P[h][mt], a, bf[mt][0], bf[mt][1]);
+              else mma_bf16(P[h][mt], a, bf[mt][2 * (s & 1)], bf[mt][2 * (s & 1) + 1]);
+            }
             if constexpr (SPLIT) {
               uint32_t ah[4];
 #pragma unroll
@@ -295,14 +347,7 @@ __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_k
           }
         }
 
-        if (!sums_ready) {
-          ok = mbar_wait(sums + slot, parity, abort_flag);
-          if (!ok) {
-            give_up(ERR_WAIT_SUMS);
-            break;
-          }
-          sums_ready = true;
-        }
+        TF_MARK(5 + 2 * u, st);
         const uint32_t sbv[4] = {sbw.x, sbw.y, sbw.z, sbw.w};       // (tile 0, col g), (0, g + 8), (1, g), (1, g + 8)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -311,19 +356,24 @@ __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_k
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             const float2 xv = *reinterpret_cast<const float2*>(xs_s + u * ROWS + mt * 8 + 2 * t);
-            fma2(acc[h][mt][0], acc[h][mt][1], P[h][mt][0], P[h][mt][1], s0);
-            fma2(acc[h][mt][0], acc[h][mt][1], xv.x, xv.y, c0);
-            fma2(acc[h][mt][2], acc[h][mt][3], P[h][mt][2], P[h][mt][3], s1);
-            fma2(acc[h][mt][2], acc[h][mt][3], xv.x, xv.y, c1);
+            acc[h][mt][0] = fmaf(xv.x, c0, fmaf(P[h][mt][0], s0, acc[h][mt][0]));
+            acc[h][mt][1] = fmaf(xv.y, c0, fmaf(P[h][mt][1], s0, acc[h][mt][1]));
+            acc[h][mt][2] = fmaf(xv.x, c1, fmaf(P[h][mt][2], s1, acc[h][mt][2]));
+            acc[h][mt][3] = fmaf(xv.y, c1, fmaf(P[h][mt][3], s1, acc[h][mt][3]));
           }
         }
+        TF_MARK(6 + 2 * u, st);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty + slot);
+      TF_MARK(4, st);
     }
   }
 
   // -------------------------------------------------------------------- output: stage, sum the slices in order, store
+#ifdef TF_TRACE
+  TF_STAMP(tf_t2);
+#endif
   __syncthreads();                                          // every stage consumed: its memory becomes the staging tiles
   pdl_wait();                                               // nothing is written before the previous kernel is done
   float* red = reinterpret_cast<float*>(smem);              // [KW][ROWS][RED_STRIDE]
@@ -342,46 +392,50 @@ __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_k
         mine[(m + 1) * RED_STRIDE + n + 8] = acc[h][mt][3];
       }
   }
-  const int nblocks = p.sk / KW;                            // blocks holding the slices of this column block
-  const bool clustered = p.cluster && nblocks > 1;
+  const bool clustered = p.cluster && p.sk > 1;
   cg::cluster_group cluster = cg::this_cluster();
   if (clustered) cluster.sync(); else __syncthreads();
+#ifdef TF_TRACE
+  TF_STAMP(tf_t3);
+#endif
 
   const bool failed = *abort_flag != 0;
-  const int n0 = sb * SB_COLS;
-  const bool summed = p.cluster != 0;                       // slices are summed here (else they go to part)
-  const int share = clustered ? nblocks : 1, mine_rank = clustered ? static_cast<int>(blockIdx.z) : 0;
+  const int share = clustered ? p.sk : 1, mine_rank = clustered ? slice : 0;
   if (!failed) {
-    const int items = summed ? ROWS * 16 : KW * ROWS * 16;
-    for (int idx = tid; idx < items; idx += THREADS) {
+    for (int idx = tid; idx < lanes_here * ROWS * 16; idx += THREADS) {
       if (idx % share != mine_rank) continue;
-      const int kw_item = idx / (ROWS * 16), rem = idx % (ROWS * 16);
-      const int ml = rem >> 4, c8 = (rem & 15) * 8, m = m0 + ml, n = n0 + c8;
+      const int kw = idx / (ROWS * 16), rem = idx % (ROWS * 16);
+      const int ml = rem >> 4, c8 = (rem & 15) * 8, m = m0 + ml, n = (sb0 + kw) * SB_COLS + c8;
       if (ml >= rows_here || n >= p.N) continue;
-      const int off = ml * RED_STRIDE + c8;
+      const int off = kw * RED_TILE + ml * RED_STRIDE + c8;
       float v[8];
-      if (summed) {
-        // slice order ((s0 + s1) + s2) + ...: slice s is lane s % KW of block s / KW of the cluster
-#pragma unroll 1
-        for (int s = 0; s < p.sk; ++s) {
-          const int b = s / KW;
-          const float* tile = (b == mine_rank || !clustered) ? red : cluster.map_shared_rank(red, b);
-          const float* src = tile + (s % KW) * RED_TILE + off;
-          const float4 lo = *reinterpret_cast<const float4*>(src);
-          const float4 hi = *reinterpret_cast<const float4*>(src + 4);
-          const float w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+      if (clustered) {
+        // slice order ((s0 + s1) + s2) + ...: slice s is block s of the cluster.  All remote loads are issued before
+        // the first add so their latencies overlap (a cluster holds at most 8 slices).
+        float4 lo[8], hi[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = s == 0 ? w[e] : v[e] + w[e];
-        }
+        for (int s = 0; s < 8; ++s)
+          if (s < p.sk) {
+            const float* src = (s == slice ? red : cluster.map_shared_rank(red, s)) + off;
+            lo[s] = *reinterpret_cast<const float4*>(src);
+            hi[s] = *reinterpret_cast<const float4*>(src + 4);
+          }
+        v[0] = lo[0].x, v[1] = lo[0].y, v[2] = lo[0].z, v[3] = lo[0].w;
+        v[4] = hi[0].x, v[5] = hi[0].y, v[6] = hi[0].z, v[7] = hi[0].w;
+#pragma unroll
+        for (int s = 1; s < 8; ++s)
+          if (s < p.sk) {
+            v[0] += lo[s].x, v[1] += lo[s].y, v[2] += lo[s].z, v[3] += lo[s].w;
+            v[4] += hi[s].x, v[5] += hi[s].y, v[6] += hi[s].z, v[7] += hi[s].w;
+          }
       } else {
-        const float* src = red + kw_item * RED_TILE + off;
-        const float4 lo = *reinterpret_cast<const float4*>(src);
-        const float4 hi = *reinterpret_cast<const float4*>(src + 4);
+        const float4 lo = *reinterpret_cast<const float4*>(red + off);
+        const float4 hi = *reinterpret_cast<const float4*>(red + off + 4);
         v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
       }
       const int valid = min(8, p.N - n);
-      if (!summed) {
-        float* dst = p.part + (static_cast<int64_t>(slice_of(kw_item)) * p.M + m) * p.N + n;
+      if (!p.cluster && p.sk > 1) {
+        float* dst = p.part + (static_cast<int64_t>(slice) * p.M + m) * p.N + n;
         for (int e = 0; e < valid; ++e) dst[e] = v[e];
       } else if (p.out_f32) {
         float* dst = reinterpret_cast<float*>(p.out) + m * p.ldo + n;
@@ -407,6 +461,20 @@ __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS) qmm_tiled_k
     }
   }
   if (clustered) cluster.sync();                            // peers may still be reading this block's tiles
+#ifdef TF_TRACE
+  __syncthreads();
+  if (tid == 0 && p.xs == nullptr && p.part != nullptr && p.cluster) {
+    unsigned long long tf_t_end;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tf_t_end));
+    const long long cta = (static_cast<long long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    long long* rec = reinterpret_cast<long long*>(p.part) + 2048 + cta * 6;
+    rec[0] = static_cast<long long>(tf_t_start), rec[1] = static_cast<long long>(tf_t_end), rec[2] = tf_smid;
+    rec[3] = static_cast<long long>(tf_t1), rec[4] = static_cast<long long>(tf_t2), rec[5] = static_cast<long long>(tf_t3);
+  }
+  if (blockIdx.x == TF_TRACE_BX && blockIdx.y == 0 && blockIdx.z == 0 && p.xs == nullptr && p.part != nullptr && p.cluster)
+    for (int i = tid; i < 6 * TF_TRACE_EVENTS; i += blockDim.x)
+      reinterpret_cast<long long*>(p.part)[i] = (&tf_trace[0][0])[i];
+#endif
 }
 
 }  // namespace tf

@@ -290,21 +290,13 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
   if (reinterpret_cast<uintptr_t>(x) % 16 || (m > 1 && ldx % 8) || ldx < k)
     return fail(TF_ERR_ALIGN, "tf_qmm: x rows must start on 16-byte boundaries (ldx %% 8 == 0, ldx >= k)");
   if (reinterpret_cast<uintptr_t>(tiled) % 16) return fail(TF_ERR_ALIGN, "tf_qmm: tiled weights must be 16-byte aligned");
-  // Slices map to (block, lane) pairs: kw lanes a block, sk / kw blocks a cluster (at most 8).  The mapping never
-  // changes a bit of the result; it is picked for occupancy and may depend on the row count.
+  // A block streams kw super-blocks of 128 columns side by side (they share the rows of x); the sk blocks of the same
+  // columns form a cluster (at most 8).  The geometry never changes a bit of the result; it is picked for occupancy.
   const int mt = mt_for_rows(m);
-  int kw = 1;
-  {
-    int want = g_lanes_pref > 0 ? g_lanes_pref : 2;
-    if (want > max_lanes(mt)) want = max_lanes(mt);
-    for (int c = want; c >= 1; c >>= 1)
-      if (sk % c == 0) {
-        kw = c;
-        break;
-      }
-    while (sk / kw > 8 && kw * 2 <= max_lanes(mt) && sk % (kw * 2) == 0) kw *= 2;
-  }
-  const bool slices_out = sk > 1 && (!reduce || sk / kw > 8);
+  const int nsb = (n + SB_COLS - 1) / SB_COLS;
+  int kw = g_lanes_pref > 0 ? g_lanes_pref : (((nsb + 1) / 2) * sk >= 256 ? 2 : 1);    // measured on B200
+  if (kw > max_lanes(mt)) kw = max_lanes(mt);
+  const bool slices_out = sk > 1 && (!reduce || sk > 8);
   if (slices_out && reduce && ldo != n) return fail(TF_ERR_ARG, "tf_qmm: more than 8 slices need a contiguous out (ldo == n)");
   if (m > 65535 * 8) return fail(TF_ERR_ARG, "tf_qmm: too many rows");
   DeviceState* st = nullptr;

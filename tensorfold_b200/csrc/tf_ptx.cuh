@@ -8,7 +8,7 @@
 
 namespace tf {
 
-constexpr uint32_t WAIT_POLLS = 1u << 22;      // ~ a second of try_wait polls before a wait is declared lost
+constexpr uint32_t WAIT_POLLS = 1u << 16;      // try_wait polls of up to 20 us each (about a second) before a wait is lost
 
 enum ErrorCode : int {
   ERR_NONE = 0,
@@ -39,18 +39,35 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint (nanoseconds): the thread may sleep in hardware that long before it reports "not
+// yet", so a waiting warp does not burn issue slots polling.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait by a whole warp (every lane calls it): false, for all lanes alike, when the barrier did not flip within
 // WAIT_POLLS polls or another warp already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
   bool ok = false;
   for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
-    if (mbar_try_wait(bar, parity)) {
+    if (mbar_try_wait_sleep(bar, parity, 20000u)) {
       ok = true;
       break;
     }
-    if ((i & 1023u) == 1023u && *abort_flag) break;
+    if ((i & 255u) == 255u && *abort_flag) break;
   }
   return __all_sync(0xFFFFFFFFu, ok);
+}
+
+// Bounded wait for a lane that already probed once: loops only if `ready` is false; uniform result across the warp.
+__device__ __forceinline__ bool mbar_wait_probed(bool ready, uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
+  if (__all_sync(0xFFFFFFFFu, ready)) return true;
+  return mbar_wait(bar, parity, abort_flag);
 }
 
 // Bulk asynchronous copy global -> shared of `bytes` (a multiple of 16; both addresses 16-byte aligned),
@@ -62,6 +79,15 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                : "memory");
 }
 
+// 16-byte asynchronous copy global -> shared through the load/store unit (rows of x: any 16-byte aligned placement).
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+// The executing thread's earlier cp.async copies arrive on `bar` when they land (the barrier's count includes them).
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -71,11 +97,19 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
 // D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col).  Each D element is the dot of one A row with one B
 // column; it does not depend on the other rows or columns of the operands.
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
       "{%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// The same with a zero accumulator input: D = A * B (the first k-step of a group needs no cleared registers).
+__device__ __forceinline__ void mma_bf16_zero(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%10, %10, %10, %10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 // (d0, d1) = (a0 * b + c0, a1 * b + c1), two IEEE fp32 fmas in one sm_100 instruction.
