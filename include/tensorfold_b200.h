@@ -61,6 +61,12 @@ int tf_unit_words(int bits, int gs);
  * Replaces the torch-indexing repack of cuda/kernels/qmm.py:55-82 (pack). */
 int tf_pack(const void* words, const void* scales, const void* biases, int n, int k, int bits, int gs, void* tiled,
             void* stream);
+/* Two projections of the same input packed as one weight of 2 * n_each rows that interleaves 16 rows of the first
+ * (gate) with 16 rows of the second (up), so one matmul tile pair holds both halves of a SwiGLU output.  n_each % 16 == 0.
+ * tiled: tf_tiled_words(2 * n_each, k, bits, gs).  Replaces the M = 2 (gate, up) interleave of cuda/experts.py:84-92 and
+ * cuda/experts_pack.cu:21-41. */
+int tf_pack_pair(const void* words_a, const void* scales_a, const void* biases_a, const void* words_b, const void* scales_b,
+                 const void* biases_b, int n_each, int k, int bits, int gs, void* tiled, void* stream);
 /* Exact inverse of tf_pack: cuda/kernels/qmm.py:85-102 (unpack). */
 int tf_unpack(const void* tiled, int n, int k, int bits, int gs, void* words, void* scales, void* biases, void* stream);
 
@@ -88,6 +94,42 @@ int tf_group_sums(const void* x, int64_t ldx, int m, int k, int gs, float* xs, v
 int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled, int64_t sb_stride, int n, int k,
            int bits, int gs, int sk, void* out, int64_t ldo, int out_f32, float* part, int reduce, int pdl,
            void* stream);
+
+/* Dense projection with an activation epilogue (one K slice): epi 1 = bf16(relu(bf16 v)^2); epi 2 = SwiGLU over a
+ * tf_pack_pair weight, bf16(bf16(silu(bf16 gate)) * bf16 up) with both clipped first when limit > 0 (out then has n / 2
+ * columns).  out: bf16.  The dense form of the expert epilogues of cuda/experts.cuh:57-103 (shared experts wider than the
+ * routed ones run through it). */
+int tf_qmm_act(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int bits, int gs,
+               void* out, int64_t ldo, int epi, float limit, int pdl, void* stream);
+
+/* ---- routed mixture of experts --------------------------------------------------------------------------------- */
+
+/* Blocks of 1024 pairs a plan of `pairs` ranks: sizes the hist scratch (blocks * experts ints). */
+int tf_moe_plan_blocks(int pairs);
+/* Stable counting sort of the pairs by expert.  picks: [pairs] int32 expert ids; members: [pairs] pair ids grouped by
+ * expert in pair order; items: [max_items][3] = (expert, first, count <= tile); counts: [2] = (items, distinct experts);
+ * scratch rank: [pairs], hist: [tf_moe_plan_blocks(pairs) * experts].  Every buffer is the caller's, so a CUDA graph
+ * replays it on new picks.  Replaces the pybind `plan` of cuda/experts.cpp:43-55 (cuda/experts.cu:157-334). */
+int tf_moe_plan(const int* picks, int pairs, int experts, int tile, int* members, int* items, int* counts, int* rank,
+                int* hist, int max_items, void* stream);
+/* Grouped expert projection over a plan: item y = (expert, first, count) multiplies rows members[first .. first+count)
+ * (row pair / slots of x when slots > 0: the token gather; row pair when slots == 0) by that expert's weight and writes
+ * row `pair` of out.  tiled: [experts][ceil(n / 128)][k / gs][unit] 4-bit units, expert_stride words apart.
+ * epi 0: out fp32 (out_f32 = 1) or bf16; 1: relu^2 (bf16); 2: SwiGLU over gate/up-interleaved rows (bf16, n / 2 columns).
+ * tile = pairs an item may hold (8, 16, 32, 64).  Replaces the pybind `run` and `prefill` of cuda/experts.cpp:57-82. */
+int tf_moe_experts(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int n, int k, int gs,
+                   const int* items, const int* counts, const int* members, int max_items, int tile, void* out, int64_t ldo,
+                   int out_f32, int epi, float limit, void* stream);
+/* logits[r, e] = fp32 dot of bf16 rows x[r] and w[e].  Replaces the Triton `_router` of cuda/moe.py:23-55. */
+int tf_moe_router(const void* x, int64_t ldx, int rows, int d, const void* w, int ne, float* out, int64_t ldo, void* stream);
+/* Per row: top `topk` experts by fp32 logit (ties to the lower id), weights bf16(exp(l_k - l_0) / sum); with `shared`
+ * one more slot, expert id `experts`, weight bf16(sigmoid(bf16(logit[experts]))).  pick, wts: [rows, topk + shared].
+ * Replaces the Triton `_topk_rows` of cuda/moe.py:58-85. */
+int tf_moe_topk(const float* logits, int64_t ldl, int rows, int experts, int topk, int shared, int* pick, float* wts,
+                void* stream);
+/* out[r, :] = bf16(sum over slots, in slot order, of wts[r, k] * y[r, k, :]) in fp32; y fp32 or bf16 (y_bf16).
+ * Replaces the Triton `_combine` of cuda/moe.py:130-150. */
+int tf_moe_combine(const void* y, int y_bf16, const float* wts, int rows, int slots, int d, void* out, void* stream);
 
 /* out[i] = round(part[0][i] + part[1][i] + ...), slices added in order: cuda/kernels/qmm.cu:235-243 (reduce_kernel).
  * part: [sk, total] fp32; out: [total] bf16 or fp32. */

@@ -40,7 +40,7 @@ def select_rows(logits, top_k: int, experts: int, shared: bool = True):
         if shared:
             sg = bf16_round(logits[i, experts:experts + 1])[0]
             picks[i, top_k] = experts
-            wts[i, top_k] = bf16_round(np.float32(1.0) / (np.float32(1.0) + np.exp(np.float32(-sg))))[()]
+            wts[i, top_k] = bf16_round(np.asarray([1.0 / (1.0 + np.exp(-np.float64(sg)))], dtype=np.float32))[0]
     return picks, wts
 
 
@@ -108,6 +108,37 @@ def expert_pairs(x, picks, gate, up, down, gs: int, limit: float = 0.0, weight_b
         act[p] = a
         y[p] = wd @ bf16_round(a.astype(np.float32)).astype(np.float64)
     return act, y
+
+
+def down_pairs(act, picks, down, gs: int) -> np.ndarray:
+    """float64 down projection of given (bf16-valued) activations, pair p using expert picks[p]."""
+
+    act = np.asarray(act, dtype=np.float64)
+    pe = np.asarray(picks).reshape(-1)
+    y = np.zeros((act.shape[0], down[0].shape[1]))
+    cache: dict[int, np.ndarray] = {}
+    for p, e in enumerate(pe):
+        e = int(e)
+        if e not in cache:
+            cache[e] = dequantize(down[0][e], down[1][e], down[2][e], 4, gs)
+        y[p] = cache[e] @ act[p]
+    return y
+
+
+def expert_pairs_relu2(x, picks, up, down, gs: int):
+    """The relu^2 form: act = relu(bf16(up x))^2 (before its bf16 rounding), then the down projection.
+    Follows cuda/experts.cuh:67-70 and tests/cuda/test_experts.py:157-158."""
+
+    x = np.asarray(x, dtype=np.float64)
+    picks = np.asarray(picks)
+    rows, slots = picks.shape
+    pe = picks.reshape(-1)
+    act = np.zeros((rows * slots, up[0].shape[1]))
+    for p, e in enumerate(pe):
+        w = dequantize(up[0][int(e)], up[1][int(e)], up[2][int(e)], 4, gs)
+        v = bf16_round((w @ x[p // slots]).astype(np.float32)).astype(np.float64)
+        act[p] = np.maximum(v, 0.0) ** 2
+    return act, down_pairs(bf16_round(act.astype(np.float32)), picks, down, gs)
 
 
 def combine(y, wts) -> np.ndarray:

@@ -29,6 +29,15 @@ SIGNATURES = {
     "tf_group_sums": (_i32, (_vp, _i64, _i32, _i32, _i32, _vp, _vp)),
     "tf_qmm": (_i32, (_vp, _i64, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i32, _vp, _i32, _i32,
                       _vp)),
+    "tf_pack_pair": (_i32, (_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp)),
+    "tf_qmm_act": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _i64, _i32, ctypes.c_float, _i32, _vp)),
+    "tf_moe_plan_blocks": (_i32, (_i32,)),
+    "tf_moe_plan": (_i32, (_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp)),
+    "tf_moe_experts": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _i64, _i32, _i32,
+                              ctypes.c_float, _vp)),
+    "tf_moe_router": (_i32, (_vp, _i64, _i32, _i32, _vp, _i32, _vp, _i64, _vp)),
+    "tf_moe_topk": (_i32, (_vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp)),
+    "tf_moe_combine": (_i32, (_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp)),
     "tf_reduce_slices": (_i32, (_vp, _i32, _i64, _vp, _i32, _vp)),
 }
 

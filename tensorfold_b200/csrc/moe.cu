@@ -1,0 +1,302 @@
+// Routed mixture-of-experts plumbing around the grouped matmul: router logits, top-k selection with renormalised
+// weights, the plan (a stable counting sort of the (row, slot) pairs by expert) and the slot-ordered combine.
+// Every kernel computes a row from that row alone, so a row's bits never depend on how many rows share the call.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdio>
+
+#include "../../include/tensorfold_b200.h"
+
+namespace tf {
+
+int fail_moe(int code, const char* msg);          // defined in tf_api.cu (sets the thread's error text)
+int cuda_fail_moe(cudaError_t e, const char* what);
+
+namespace {
+
+constexpr int PLAN_BLOCK = 1024;                  // pairs a plan block ranks
+constexpr int PLAN_MAX_EXPERTS = 4096;
+
+// ---------------------------------------------------------------------------------------------------------------------
+// plan
+// ---------------------------------------------------------------------------------------------------------------------
+
+// Phase A: block b ranks pairs [1024 b, 1024 b + 1024): rank[i] = number of earlier pairs of the block with the same
+// expert; hist[b][e] = pairs of expert e in the block.  Warps take turns so ranks follow pair order (a stable sort).
+__device__ void plan_rank_block(const int* __restrict__ picks, int pairs, int experts, int* __restrict__ rank,
+                                int* __restrict__ hist, int blk, int* cnt /* shared [experts] */) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int e = tid; e < experts; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  const int i = blk * PLAN_BLOCK + tid;
+  int e = i < pairs ? picks[i] : -1;
+  const bool valid = e >= 0 && e < experts;
+  for (int turn = 0; turn < PLAN_BLOCK / 32; ++turn) {
+    if (warp == turn) {
+      const unsigned act = __ballot_sync(0xFFFFFFFFu, valid);
+      if (valid) {
+        const unsigned same = __match_any_sync(act, e);
+        const int base = cnt[e];
+        __syncwarp(act);
+        rank[i] = base + __popc(same & ((1u << lane) - 1u));
+        if (lane == __ffs(same) - 1) cnt[e] = base + __popc(same);
+      }
+    }
+    __syncthreads();
+  }
+  for (int x = tid; x < experts; x += blockDim.x) hist[blk * experts + x] = cnt[x];
+}
+
+// Phase B (one block): turn hist[b][e] into the offset in `members` of block b's first pair of expert e, and write the
+// items (expert, first, count <= tile) in expert order plus counts = (items, distinct experts).
+__device__ void plan_offsets_block(int* __restrict__ hist, int nblk, int experts, int tile, int* __restrict__ items,
+                                   int* __restrict__ counts, int max_items, int* scan /* shared [2 * 1024 + 64] */) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ept = (experts + blockDim.x - 1) / blockDim.x;       // experts a thread owns (consecutive)
+  int tot[4], nit[4];
+  int sum_t = 0, sum_i = 0, distinct = 0;
+  for (int j = 0; j < ept; ++j) {
+    const int e = tid * ept + j;
+    int t = 0;
+    if (e < experts)
+      for (int b = 0; b < nblk; ++b) {
+        const int c = hist[b * experts + e];
+        hist[b * experts + e] = t;                               // exclusive over blocks
+        t += c;
+      }
+    tot[j] = t, nit[j] = (t + tile - 1) / tile;
+    sum_t += t, sum_i += nit[j], distinct += t > 0;
+  }
+  // block-wide exclusive scans of (sum_t, sum_i) and the total of `distinct`
+  int inc_t = sum_t, inc_i = sum_i, dis = distinct;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xFFFFFFFFu, inc_t, o), b = __shfl_up_sync(0xFFFFFFFFu, inc_i, o);
+    if (lane >= o) inc_t += a, inc_i += b;
+  }
+  for (int o = 16; o > 0; o >>= 1) dis += __shfl_xor_sync(0xFFFFFFFFu, dis, o);
+  int* wt = scan;
+  int* wi = scan + 32;
+  int* wd = scan + 64;
+  if (lane == 31) wt[warp] = inc_t, wi[warp] = inc_i;
+  if (lane == 0) wd[warp] = dis;
+  __syncthreads();
+  int base_t = 0, base_i = 0;
+  for (int w = 0; w < warp; ++w) base_t += wt[w], base_i += wi[w];
+  int start = base_t + inc_t - sum_t, ibase = base_i + inc_i - sum_i;
+  for (int j = 0; j < ept; ++j) {
+    const int e = tid * ept + j;
+    if (e < experts) {
+      for (int b = 0; b < nblk; ++b) hist[b * experts + e] += start;
+      for (int q = 0; q < nit[j]; ++q)
+        if (ibase + q < max_items) {
+          items[3 * (ibase + q)] = e;
+          items[3 * (ibase + q) + 1] = start + q * tile;
+          items[3 * (ibase + q) + 2] = min(tile, tot[j] - q * tile);
+        }
+    }
+    start += tot[j], ibase += nit[j];
+  }
+  if (tid == blockDim.x - 1) {
+    int d = 0;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) d += wd[w];
+    counts[0] = min(ibase, max_items);
+    counts[1] = d;
+  }
+}
+
+__device__ void plan_scatter_block(const int* __restrict__ picks, int pairs, int experts, const int* __restrict__ rank,
+                                   const int* __restrict__ hist, int* __restrict__ members, int blk) {
+  const int i = blk * PLAN_BLOCK + threadIdx.x;
+  if (i >= pairs) return;
+  const int e = picks[i];
+  if (e < 0 || e >= experts) return;
+  members[hist[blk * experts + e] + rank[i]] = i;
+}
+
+// phase 0: rank (grid = blocks), 1: offsets (one block), 2: scatter (grid = blocks), -1: all three in one block
+__global__ void __launch_bounds__(PLAN_BLOCK) plan_kernel(const int* __restrict__ picks, int pairs, int experts, int tile,
+                                                         int* members, int* items, int* counts, int* rank, int* hist,
+                                                         int max_items, int nblk, int phase) {
+  __shared__ int shared[PLAN_MAX_EXPERTS + 128];
+  if (phase == 0) {
+    plan_rank_block(picks, pairs, experts, rank, hist, blockIdx.x, shared);
+  } else if (phase == 1) {
+    plan_offsets_block(hist, nblk, experts, tile, items, counts, max_items, shared);
+  } else if (phase == 2) {
+    plan_scatter_block(picks, pairs, experts, rank, hist, members, blockIdx.x);
+  } else {
+    plan_rank_block(picks, pairs, experts, rank, hist, 0, shared);
+    __syncthreads();
+    plan_offsets_block(hist, 1, experts, tile, items, counts, max_items, shared);
+    __syncthreads();
+    plan_scatter_block(picks, pairs, experts, rank, hist, members, 0);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// router: logits[r, e] = fp32 dot of bf16 rows x[r] and w[e]; one warp per (row, expert), fixed order
+// ---------------------------------------------------------------------------------------------------------------------
+
+__global__ void router_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int rows, int d,
+                              const __nv_bfloat16* __restrict__ w, int ne, float* __restrict__ out, int64_t ldo) {
+  const int lane = threadIdx.x & 31, e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), r = blockIdx.y;
+  if (e >= ne || r >= rows) return;
+  const __nv_bfloat16* xr = x + r * ldx;
+  const __nv_bfloat16* wr = w + static_cast<int64_t>(e) * d;
+  float acc = 0.f;
+  const int vec = (d % 8 == 0 && (reinterpret_cast<uintptr_t>(xr) % 16 == 0) && (reinterpret_cast<uintptr_t>(wr) % 16 == 0)) ? d / 8 : 0;
+  for (int v = lane; v < vec; v += 32) {
+    const uint4 a = reinterpret_cast<const uint4*>(xr)[v], b = reinterpret_cast<const uint4*>(wr)[v];
+    const uint32_t aa[4] = {a.x, a.y, a.z, a.w}, bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc = fmaf(__uint_as_float(aa[i] << 16), __uint_as_float(bb[i] << 16), acc);
+      acc = fmaf(__uint_as_float(aa[i] & 0xFFFF0000u), __uint_as_float(bb[i] & 0xFFFF0000u), acc);
+    }
+  }
+  for (int k = vec * 8 + lane; k < d; k += 32) acc = fmaf(__bfloat162float(xr[k]), __bfloat162float(wr[k]), acc);
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+  if (lane == 0) out[r * ldo + e] = acc;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// top-k: one warp per row
+// ---------------------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__global__ void topk_kernel(const float* __restrict__ logits, int64_t ldl, int rows, int experts, int topk, int shared,
+                            int* __restrict__ pick, float* __restrict__ wts) {
+  const int lane = threadIdx.x & 31, r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const float* l = logits + r * ldl;
+  const int slots = topk + (shared ? 1 : 0);
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = (lane + 32 * j) < experts ? l[lane + 32 * j] : -INFINITY;
+  float top = 0.f, total = 0.f, mine_ex = 0.f;
+  int mine_id = 0;
+  for (int k = 0; k < topk; ++k) {
+    float best = -INFINITY;
+    int id = 0x7FFFFFFF;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (v[j] > best) best = v[j], id = lane + 32 * j;           // ascending ids: the first maximum is the lowest id
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+      const int oi = __shfl_xor_sync(0xFFFFFFFFu, id, o);
+      if (ob > best || (ob == best && oi < id)) best = ob, id = oi;
+    }
+    if (k == 0) top = best;
+    const float ex = expf(best - top);
+    total += ex;
+    if (lane == k % 32) mine_ex = ex, mine_id = id;              // lane k keeps slot k (topk <= 32)
+    if ((id & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j == (id >> 5)) v[j] = -INFINITY;
+    }
+  }
+  if (lane < topk) {
+    pick[r * slots + lane] = mine_id;
+    wts[r * slots + lane] = bf16r(mine_ex / total);
+  }
+  if (shared && lane == 0) {
+    const float sg = bf16r(l[experts]);
+    pick[r * slots + topk] = experts;
+    wts[r * slots + topk] = bf16r(1.f / (1.f + expf(-sg)));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// combine: out[r, d] = bf16(sum over slots in slot order of w[r, k] * y[r, k, d]) in fp32
+// ---------------------------------------------------------------------------------------------------------------------
+
+template <bool YBF16>
+__global__ void combine_kernel(const void* __restrict__ y, const float* __restrict__ wts, int rows, int slots, int d,
+                               __nv_bfloat16* __restrict__ out) {
+  const int r = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (r >= rows || c >= d) return;
+  float a0 = 0.f, a1 = 0.f;
+  for (int k = 0; k < slots; ++k) {
+    const float w = wts[r * slots + k];
+    const int64_t off = (static_cast<int64_t>(r) * slots + k) * d + c;
+    float y0, y1 = 0.f;
+    if (YBF16) {
+      const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(y) + off;
+      y0 = __bfloat162float(p[0]);
+      if (c + 1 < d) y1 = __bfloat162float(p[1]);
+    } else {
+      const float* p = reinterpret_cast<const float*>(y) + off;
+      y0 = p[0];
+      if (c + 1 < d) y1 = p[1];
+    }
+    a0 = fmaf(w, y0, a0);
+    a1 = fmaf(w, y1, a1);
+  }
+  out[static_cast<int64_t>(r) * d + c] = __float2bfloat16_rn(a0);
+  if (c + 1 < d) out[static_cast<int64_t>(r) * d + c + 1] = __float2bfloat16_rn(a1);
+}
+
+}  // namespace
+
+}  // namespace tf
+
+using namespace tf;
+
+extern "C" {
+
+int tf_moe_plan_blocks(int pairs) { return pairs < 1 ? TF_ERR_ARG : (pairs + PLAN_BLOCK - 1) / PLAN_BLOCK; }
+
+int tf_moe_plan(const int* picks, int pairs, int experts, int tile, int* members, int* items, int* counts, int* rank,
+                int* hist, int max_items, void* stream) {
+  if (pairs < 1 || experts < 1 || experts > PLAN_MAX_EXPERTS || tile < 1 || max_items < 1)
+    return fail_moe(TF_ERR_ARG, "tf_moe_plan: bad sizes (at most 4096 experts)");
+  if (!picks || !members || !items || !counts || !rank || !hist) return fail_moe(TF_ERR_ARG, "tf_moe_plan: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int nblk = (pairs + PLAN_BLOCK - 1) / PLAN_BLOCK;
+  if (nblk == 1) {
+    plan_kernel<<<1, PLAN_BLOCK, 0, s>>>(picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, 1, -1);
+  } else {
+    plan_kernel<<<nblk, PLAN_BLOCK, 0, s>>>(picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, nblk, 0);
+    plan_kernel<<<1, PLAN_BLOCK, 0, s>>>(picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, nblk, 1);
+    plan_kernel<<<nblk, PLAN_BLOCK, 0, s>>>(picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, nblk, 2);
+  }
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_plan");
+}
+
+int tf_moe_router(const void* x, int64_t ldx, int rows, int d, const void* w, int ne, float* out, int64_t ldo, void* stream) {
+  if (rows < 1 || d < 1 || ne < 1 || !x || !w || !out || ldx < d || ldo < ne) return fail_moe(TF_ERR_ARG, "tf_moe_router: bad arguments");
+  if (rows > 65535) return fail_moe(TF_ERR_ARG, "tf_moe_router: too many rows");
+  dim3 grid((ne + 7) / 8, rows);
+  router_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x), ldx, rows, d,
+                                                                     static_cast<const __nv_bfloat16*>(w), ne, out, ldo);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_router");
+}
+
+int tf_moe_topk(const float* logits, int64_t ldl, int rows, int experts, int topk, int shared, int* pick, float* wts,
+                void* stream) {
+  if (rows < 1 || experts < 1 || experts > 1024 || topk < 1 || topk > 32 || topk > experts || !logits || !pick || !wts ||
+      ldl < experts + (shared ? 1 : 0))
+    return fail_moe(TF_ERR_ARG, "tf_moe_topk: bad arguments (at most 1024 experts, top 32)");
+  topk_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, ldl, rows, experts, topk, shared, pick, wts);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_topk");
+}
+
+int tf_moe_combine(const void* y, int y_bf16, const float* wts, int rows, int slots, int d, void* out, void* stream) {
+  if (rows < 1 || slots < 1 || d < 1 || !y || !wts || !out || rows > 65535) return fail_moe(TF_ERR_ARG, "tf_moe_combine: bad arguments");
+  dim3 grid((d / 2 + 127) / 128 + 1, rows);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (y_bf16) combine_kernel<true><<<grid, 128, 0, s>>>(y, wts, rows, slots, d, static_cast<__nv_bfloat16*>(out));
+  else combine_kernel<false><<<grid, 128, 0, s>>>(y, wts, rows, slots, d, static_cast<__nv_bfloat16*>(out));
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_combine");
+}
+
+}  // extern "C"

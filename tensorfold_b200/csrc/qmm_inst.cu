@@ -15,7 +15,7 @@ cudaError_t launch(const QmmParams& p, cudaStream_t stream, bool pdl) {
   const int nblocks = p.sk;
   const int nsb = (p.N + SB_COLS - 1) / SB_COLS;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((nsb + KW - 1) / KW, (p.M + Geo::ROWS - 1) / Geo::ROWS, nblocks);
+  cfg.gridDim = dim3((nsb + KW - 1) / KW, p.items != nullptr ? p.M : (p.M + Geo::ROWS - 1) / Geo::ROWS, nblocks);   // grouped: M = plan capacity in items
   cfg.blockDim = dim3(Geo::THREADS);
   cfg.dynamicSmemBytes = Geo::SMEM;
   cfg.stream = stream;

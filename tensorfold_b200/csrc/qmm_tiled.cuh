@@ -58,7 +58,34 @@ struct QmmParams {
   float* part;                // [sk, M, N] fp32 when the slices leave the kernel
   int cluster;                // 1: the sk blocks of a column block form a cluster and the slices are summed here
   int* err;                   // device error word (0 = none)
+  // grouped (mixture-of-experts) mode, items != null: block (x, y) runs plan item y = (expert, first, count <= ROWS):
+  // its rows are pairs members[first .. first + count), read from row pair / slots of x (slots > 0) or row pair of x
+  // (slots == 0), against expert `expert`'s weights, written to row `pair` of out.  sk must be 1.
+  const int* items;           // [max items][3]
+  const int* counts;          // [0] = items in use; blocks past it leave at once
+  const int* members;         // pair ids grouped by expert
+  int slots;
+  int64_t expert_stride;      // words from one expert's units to the next
+  // epilogue: 0 store as is; 1 bf16(relu(bf16 v)^2); 2 SwiGLU over column pairs: the weight rows interleave 16 gate
+  // columns with 16 up columns, so a tile pair holds both halves and out has N / 2 columns.
+  int epi;
+  float limit;                // SwiGLU clip (0: none)
 };
+
+// SwiGLU as the families define it: bf16(bf16(silu(bf16 g)) * bf16 u), clipped first when limit > 0.
+__device__ __forceinline__ float bf16_round_f(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float swiglu_f(float g, float u, float limit) {
+  float gv = bf16_round_f(g), uv = bf16_round_f(u);
+  if (limit > 0.f) {
+    gv = fminf(gv, limit);
+    uv = fminf(fmaxf(uv, -limit), limit);
+  }
+  return bf16_round_f(gv / (1.f + expf(-gv))) * uv;
+}
+__device__ __forceinline__ float relu2_f(float v) {
+  const float u = fmaxf(bf16_round_f(v), 0.f);
+  return u * u;
+}
 
 constexpr int XROW_BYTES = 272;            // 128 inputs of bf16 + 16 bytes so ldmatrix rows fall in distinct banks
 constexpr int RED_STRIDE = 132;            // floats per row of the output staging tile (conflict-free fragment stores)
@@ -147,11 +174,29 @@ qmm_tiled_kernel(const QmmParams p) {
   const int nsb = (p.N + SB_COLS - 1) / SB_COLS;
   const int sb0 = blockIdx.x * KW;                          // lane kw streams super-block sb0 + kw (if it exists)
   const int lanes_here = min(KW, nsb - sb0);
-  const int m0 = blockIdx.y * ROWS, slice = blockIdx.z;
+  const int slice = blockIdx.z;
   const int per = p.KG / p.sk;                              // groups of a slice
   const int g_first = slice * per;
   const int nstages = (per + G - 1) / G;
-  const int rows_here = min(ROWS, p.M - m0);
+  const bool grouped = p.items != nullptr;
+  int m0 = blockIdx.y * ROWS, rows_here, first = 0;
+  const uint32_t* wroot = p.w;
+  if (grouped) {
+    pdl_wait();                                             // the plan may be the previous kernel's output
+    if (static_cast<int>(blockIdx.y) >= p.counts[0]) return;
+    const int* item = p.items + 3 * blockIdx.y;
+    wroot += static_cast<int64_t>(item[0]) * p.expert_stride;
+    first = item[1];
+    rows_here = min(ROWS, item[2]);
+    m0 = 0;
+  } else {
+    rows_here = min(ROWS, p.M - m0);
+  }
+  auto row_of = [&](int r) -> int64_t {                      // the row of x that row r of this block reads
+    if (!grouped) return m0 + r;
+    const int pair = p.members[first + r];
+    return p.slots > 0 ? pair / p.slots : pair;
+  };
 
   if (tid == 0) {
     for (int i = 0; i < NST; ++i) {
@@ -187,7 +232,7 @@ qmm_tiled_kernel(const QmmParams p) {
 
   if (warp == CONSUMERS) {
     // ------------------------------------------------------------------ copy warp: weights (bulk) and rows of x (16 B)
-    const uint32_t* wbase = p.w + static_cast<int64_t>(sb0) * p.sb_stride + static_cast<int64_t>(g_first) * UNITW;
+    const uint32_t* wbase = wroot + static_cast<int64_t>(sb0) * p.sb_stride + static_cast<int64_t>(g_first) * UNITW;
     auto issue_w = [&](int st, int slot) {
       if (lane == 0) {
         const int ng = groups_of(st);
@@ -199,11 +244,11 @@ qmm_tiled_kernel(const QmmParams p) {
     };
     auto issue_x = [&](int st, int slot) {
       const int cpr = groups_of(st) * GS / 8;               // 16-byte chunks a row
-      const __nv_bfloat16* src = p.x + static_cast<int64_t>(m0) * p.ldx + static_cast<int64_t>(g_first + st * G) * GS;
+      const __nv_bfloat16* src = p.x + static_cast<int64_t>(g_first + st * G) * GS;
       uint8_t* dst = stage_ptr(slot) + Geo::X_OFF;
       for (int c = lane; c < rows_here * cpr; c += 32) {
         const int r = c / cpr, q = c - r * cpr;
-        cp_async16(dst + r * XROW_BYTES + q * 16, src + r * p.ldx + q * 8);
+        cp_async16(dst + r * XROW_BYTES + q * 16, src + row_of(r) * p.ldx + q * 8);
       }
       cp_async_arrive(full + slot);
     };
@@ -244,7 +289,7 @@ qmm_tiled_kernel(const QmmParams p) {
         const int g0 = g_first + st * G;
         for (int i = lane; i < ng * ROWS; i += 32) {
           const int u = i / ROWS, r = i % ROWS;
-          xs_s[u * ROWS + r] = r < rows_here ? p.xs[static_cast<int64_t>(m0 + r) * p.KG + g0 + u] : 0.f;
+          xs_s[u * ROWS + r] = r < rows_here ? p.xs[row_of(r) * p.KG + g0 + u] : 0.f;
         }
       } else {
         const uint32_t xs0 = smem_addr(stage_ptr(slot) + Geo::X_OFF) + (lane & 7) * XROW_BYTES + (lane >> 3) * 16;
@@ -401,12 +446,26 @@ qmm_tiled_kernel(const QmmParams p) {
 
   const bool failed = *abort_flag != 0;
   const int share = clustered ? p.sk : 1, mine_rank = clustered ? slice : 0;
-  if (!failed) {
+  if (!failed && p.epi == 2) {
+    // SwiGLU: a tile pair holds 16 gate columns then the 16 up columns of the same outputs; out has N / 2 columns (bf16)
+    const int nout = p.N / 2;
+    for (int idx = tid; idx < lanes_here * ROWS * 8; idx += THREADS) {
+      const int kw = idx / (ROWS * 8), rem = idx % (ROWS * 8);
+      const int ml = rem >> 3, j8 = rem & 7, n = (sb0 + kw) * (SB_COLS / 2) + j8 * 8;
+      if (ml >= rows_here || n >= nout) continue;
+      const float* src = red + kw * RED_TILE + ml * RED_STRIDE + 32 * (j8 >> 1) + 8 * (j8 & 1);
+      const int64_t m = grouped ? p.members[first + ml] : m0 + ml;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + m * p.ldo + n;
+      const int valid = min(8, nout - n);
+      for (int e = 0; e < valid; ++e) dst[e] = __float2bfloat16_rn(swiglu_f(src[e], src[16 + e], p.limit));
+    }
+  } else if (!failed) {
     for (int idx = tid; idx < lanes_here * ROWS * 16; idx += THREADS) {
       if (idx % share != mine_rank) continue;
       const int kw = idx / (ROWS * 16), rem = idx % (ROWS * 16);
-      const int ml = rem >> 4, c8 = (rem & 15) * 8, m = m0 + ml, n = (sb0 + kw) * SB_COLS + c8;
+      const int ml = rem >> 4, c8 = (rem & 15) * 8, n = (sb0 + kw) * SB_COLS + c8;
       if (ml >= rows_here || n >= p.N) continue;
+      const int64_t m = grouped ? p.members[first + ml] : m0 + ml;
       const int off = kw * RED_TILE + ml * RED_STRIDE + c8;
       float v[8];
       if (clustered) {
@@ -434,6 +493,10 @@ qmm_tiled_kernel(const QmmParams p) {
         v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
       }
       const int valid = min(8, p.N - n);
+      if (p.epi == 1) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = relu2_f(v[e]);
+      }
       if (!p.cluster && p.sk > 1) {
         float* dst = p.part + (static_cast<int64_t>(slice) * p.M + m) * p.N + n;
         for (int e = 0; e < valid; ++e) dst[e] = v[e];

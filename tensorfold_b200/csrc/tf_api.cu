@@ -42,15 +42,21 @@ std::mutex g_init_mutex;
 
 }  // namespace
 
+int fail_moe(int code, const char* msg) { return fail(code, "%s", msg); }
+int cuda_fail_moe(cudaError_t e, const char* what) { return cuda_fail(e, what); }
+
 __device__ int g_error_word;          // set by a kernel whose bounded wait gave up; read by tf_device_error
 
 // ---------------------------------------------------------------------------------------------------------------------
 // repack: one thread per output word of the tiled tensor
 // ---------------------------------------------------------------------------------------------------------------------
 
+// With a second source (words2 != null) the packed rows interleave 16 rows of the first with 16 rows of the second
+// (gate and up projections of an expert): packed row r comes from source (r / 16) % 2, row (r / 32) * 16 + r % 16.
 __global__ void pack_kernel(const uint32_t* __restrict__ words, const uint16_t* __restrict__ scales,
-                            const uint16_t* __restrict__ biases, int n, int k, int bits, int gs,
-                            uint32_t* __restrict__ tiled, int64_t total) {
+                            const uint16_t* __restrict__ biases, const uint32_t* __restrict__ words2,
+                            const uint16_t* __restrict__ scales2, const uint16_t* __restrict__ biases2, int n, int k,
+                            int bits, int gs, uint32_t* __restrict__ tiled, int64_t total) {
   const int wpl = words_per_lane(bits, gs), unitw = unit_words(bits, gs), kg = k / gs;
   const int64_t wpr = static_cast<int64_t>(k) * bits / 32;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -64,15 +70,29 @@ __global__ void pack_kernel(const uint32_t* __restrict__ words, const uint16_t* 
     if (wi_unit < code_words) {
       const int tp = wi_unit / (32 * wpl), lane = (wi_unit / wpl) % 32, wi = wi_unit % wpl;
       auto code = [&](int col, int kk) -> uint32_t {
-        const int64_t row = sb * SB_COLS + col;
-        return row < n ? stored_code(words + row * wpr, static_cast<int64_t>(g) * gs + kk, bits, wpr) : 0u;
+        int64_t row = sb * SB_COLS + col;
+        if (row >= n) return 0u;
+        const uint32_t* src = words;
+        if (words2 != nullptr) {
+          if ((row >> 4) & 1) src = words2;
+          row = (row >> 5) * 16 + (row & 15);
+        }
+        return stored_code(src + row * wpr, static_cast<int64_t>(g) * gs + kk, bits, wpr);
       };
       value = lane_word(bits, gs, tp, lane, wi, code);
     } else {
       const int ai = wi_unit - code_words;
       const int tp = ai >> 5, gg = (ai >> 2) & 7, h = (ai >> 1) & 1, r8 = ai & 1;
-      const int64_t row = sb * SB_COLS + 32 * tp + 16 * h + 8 * r8 + gg;
-      value = row < n ? (static_cast<uint32_t>(scales[row * kg + g]) | (static_cast<uint32_t>(biases[row * kg + g]) << 16)) : 0u;
+      int64_t row = sb * SB_COLS + 32 * tp + 16 * h + 8 * r8 + gg;
+      value = 0u;
+      if (row < n) {
+        const uint16_t *sc = scales, *bi = biases;
+        if (words2 != nullptr) {
+          if ((row >> 4) & 1) sc = scales2, bi = biases2;
+          row = (row >> 5) * 16 + (row & 15);
+        }
+        value = static_cast<uint32_t>(sc[row * kg + g]) | (static_cast<uint32_t>(bi[row * kg + g]) << 16);
+      }
     }
     tiled[i] = value;
   }
@@ -149,6 +169,17 @@ __global__ void reduce_slices_kernel(const float* __restrict__ part, int sk, int
 }
 
 namespace {
+
+cudaError_t launch_bits(const QmmParams& p, int bits, int gs, int mt, int kw, cudaStream_t s, bool pdl) {
+  switch (bits) {
+    case 2: return qmm_launch_b2(p, gs, mt, kw, s, pdl);
+    case 3: return qmm_launch_b3(p, gs, mt, kw, s, pdl);
+    case 4: return qmm_launch_b4(p, gs, mt, kw, s, pdl);
+    case 5: return qmm_launch_b5(p, gs, mt, kw, s, pdl);
+    case 6: return qmm_launch_b6(p, gs, mt, kw, s, pdl);
+    default: return qmm_launch_b8(p, gs, mt, kw, s, pdl);
+  }
+}
 
 int grid_for(int64_t total, int threads) {
   const int64_t blocks = (total + threads - 1) / threads;
@@ -251,10 +282,26 @@ int tf_pack(const void* words, const void* scales, const void* biases, int n, in
   if (!words || !scales || !biases || !tiled) return fail(TF_ERR_ARG, "tf_pack: null pointer");
   const int64_t total = tf_tiled_words(n, k, bits, gs);
   pack_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint32_t*>(words), static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), n, k,
-      bits, gs, static_cast<uint32_t*>(tiled), total);
+      static_cast<const uint32_t*>(words), static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), nullptr,
+      nullptr, nullptr, n, k, bits, gs, static_cast<uint32_t*>(tiled), total);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_pack");
+}
+
+int tf_pack_pair(const void* words_a, const void* scales_a, const void* biases_a, const void* words_b, const void* scales_b,
+                 const void* biases_b, int n_each, int k, int bits, int gs, void* tiled, void* stream) {
+  if (!format_ok(bits, gs)) return fail(TF_ERR_ARG, "tf_pack_pair: %d bits / groups of %d is not an affine format", bits, gs);
+  if (n_each < 16 || n_each % 16 || k < gs || k % gs || (static_cast<int64_t>(k) * bits) % 32)
+    return fail(TF_ERR_ARG, "tf_pack_pair: (%d, %d) needs rows in whole 16-row tiles and whole groups and words", n_each, k);
+  if (!words_a || !scales_a || !biases_a || !words_b || !scales_b || !biases_b || !tiled)
+    return fail(TF_ERR_ARG, "tf_pack_pair: null pointer");
+  const int64_t total = tf_tiled_words(2 * n_each, k, bits, gs);
+  pack_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(words_a), static_cast<const uint16_t*>(scales_a), static_cast<const uint16_t*>(biases_a),
+      static_cast<const uint32_t*>(words_b), static_cast<const uint16_t*>(scales_b), static_cast<const uint16_t*>(biases_b),
+      2 * n_each, k, bits, gs, static_cast<uint32_t*>(tiled), total);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_pack_pair");
 }
 
 int tf_unpack(const void* tiled, int n, int k, int bits, int gs, void* words, void* scales, void* biases, void* stream) {
@@ -303,7 +350,7 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
   if (int rc = current_state(&st)) return rc;
 
   const int unitw = unit_words(bits, gs);
-  QmmParams p;
+  QmmParams p = {};
   p.x = static_cast<const __nv_bfloat16*>(x);
   p.ldx = ldx;
   p.M = m;
@@ -319,19 +366,69 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
   p.part = part;
   p.cluster = !slices_out;
   p.err = st->err;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaError_t e;
-  switch (bits) {
-    case 2: e = qmm_launch_b2(p, gs, mt, kw, s, pdl != 0); break;
-    case 3: e = qmm_launch_b3(p, gs, mt, kw, s, pdl != 0); break;
-    case 4: e = qmm_launch_b4(p, gs, mt, kw, s, pdl != 0); break;
-    case 5: e = qmm_launch_b5(p, gs, mt, kw, s, pdl != 0); break;
-    case 6: e = qmm_launch_b6(p, gs, mt, kw, s, pdl != 0); break;
-    default: e = qmm_launch_b8(p, gs, mt, kw, s, pdl != 0); break;
-  }
+  const cudaError_t e = launch_bits(p, bits, gs, mt, kw, static_cast<cudaStream_t>(stream), pdl != 0);
   if (e != cudaSuccess) return cuda_fail(e, "tf_qmm launch");
   if (slices_out && reduce) return tf_reduce_slices(part, sk, static_cast<int64_t>(m) * n, out, out_f32, stream);
   return TF_OK;
+}
+
+int tf_qmm_act(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int bits, int gs,
+               void* out, int64_t ldo, int epi, float limit, int pdl, void* stream) {
+  if (!format_ok(bits, gs)) return fail(TF_ERR_ARG, "tf_qmm_act: %d bits / groups of %d is not an affine format", bits, gs);
+  if (m < 1 || n < 1 || k < gs || k % gs) return fail(TF_ERR_ARG, "tf_qmm_act: bad shape m=%d n=%d k=%d", m, n, k);
+  if (epi != 1 && epi != 2) return fail(TF_ERR_ARG, "tf_qmm_act: epilogue 1 (relu^2) or 2 (SwiGLU)");
+  if (epi == 2 && n % 32) return fail(TF_ERR_ARG, "tf_qmm_act: SwiGLU rows interleave gate and up in tiles of 16");
+  const int ncols = epi == 2 ? n / 2 : n;
+  if (!x || !tiled || !out || ldo < ncols) return fail(TF_ERR_ARG, "tf_qmm_act: null pointer or short out rows");
+  if (reinterpret_cast<uintptr_t>(x) % 16 || (m > 1 && ldx % 8) || ldx < k)
+    return fail(TF_ERR_ALIGN, "tf_qmm_act: x rows must start on 16-byte boundaries");
+  DeviceState* st = nullptr;
+  if (int rc = current_state(&st)) return rc;
+  QmmParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.ldx = ldx, p.M = m;
+  p.w = static_cast<const uint32_t*>(tiled);
+  p.sb_stride = sb_stride > 0 ? sb_stride : static_cast<int64_t>(k / gs) * unit_words(bits, gs);
+  p.N = n, p.K = k, p.KG = k / gs, p.sk = 1;
+  p.out = out, p.ldo = ldo, p.out_f32 = 0;
+  p.out_vec = reinterpret_cast<uintptr_t>(out) % 16 == 0 && (ldo * 2) % 16 == 0;
+  p.cluster = 1;
+  p.err = st->err;
+  p.epi = epi, p.limit = limit;
+  const cudaError_t e = launch_bits(p, bits, gs, mt_for_rows(m), 1, static_cast<cudaStream_t>(stream), pdl != 0);
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_qmm_act launch");
+}
+
+int tf_moe_experts(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int n, int k, int gs,
+                   const int* items, const int* counts, const int* members, int max_items, int tile, void* out, int64_t ldo,
+                   int out_f32, int epi, float limit, void* stream) {
+  if (!format_ok(4, gs)) return fail(TF_ERR_ARG, "tf_moe_experts: groups of 32, 64 or 128, not %d", gs);
+  if (n < 1 || k < gs || k % gs || max_items < 1) return fail(TF_ERR_ARG, "tf_moe_experts: bad shape n=%d k=%d items=%d", n, k, max_items);
+  if (tile != 8 && tile != 16 && tile != 32 && tile != 64) return fail(TF_ERR_ARG, "tf_moe_experts: items of 8, 16, 32 or 64 pairs");
+  if (epi < 0 || epi > 2 || (epi == 2 && n % 32)) return fail(TF_ERR_ARG, "tf_moe_experts: bad epilogue for %d columns", n);
+  if (epi != 0 && out_f32) return fail(TF_ERR_ARG, "tf_moe_experts: activations are written as bf16");
+  const int ncols = epi == 2 ? n / 2 : n;
+  if (!x || !tiled || !items || !counts || !members || !out || ldo < ncols || slots < 0)
+    return fail(TF_ERR_ARG, "tf_moe_experts: null pointer or short out rows");
+  if (reinterpret_cast<uintptr_t>(x) % 16 || ldx % 8 || ldx < k) return fail(TF_ERR_ALIGN, "tf_moe_experts: x rows must start on 16-byte boundaries");
+  if (max_items > 65535) return fail(TF_ERR_ARG, "tf_moe_experts: too many items");
+  DeviceState* st = nullptr;
+  if (int rc = current_state(&st)) return rc;
+  QmmParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.ldx = ldx, p.M = max_items;
+  p.w = static_cast<const uint32_t*>(tiled);
+  p.sb_stride = static_cast<int64_t>(k / gs) * unit_words(4, gs);
+  p.N = n, p.K = k, p.KG = k / gs, p.sk = 1;
+  p.out = out, p.ldo = ldo, p.out_f32 = out_f32;
+  p.out_vec = reinterpret_cast<uintptr_t>(out) % 16 == 0 && (ldo * (out_f32 ? 4 : 2)) % 16 == 0;
+  p.cluster = 1;
+  p.err = st->err;
+  p.items = items, p.counts = counts, p.members = members, p.slots = slots;
+  p.expert_stride = expert_stride;
+  p.epi = epi, p.limit = limit;
+  const cudaError_t e = launch_bits(p, 4, gs, tile / 8, 1, static_cast<cudaStream_t>(stream), false);
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_moe_experts launch");
 }
 
 int tf_reduce_slices(const float* part, int sk, int64_t total, void* out, int out_f32, void* stream) {

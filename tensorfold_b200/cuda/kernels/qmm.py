@@ -163,3 +163,43 @@ def matmul(x: torch.Tensor, q: Q4, xs: torch.Tensor | None = None, *, sk: int | 
     if sk == 1 or reduce:
         return out
     return part.reshape(-1)[:sk * m * q.n].view(sk, m, q.n)
+
+
+def pack_pair(gate: tuple, up: tuple, gs: int, bits: int = 4) -> Q4:
+    """Gate and up projections (each MLX words, scales, biases of n rows) as ONE weight of 2 n rows that interleaves 16
+    gate rows with 16 up rows, so a matmul tile pair holds both halves of every SwiGLU output (see ``matmul_act``)."""
+
+    (wg, sg, bg), (wu, su, bu) = gate, up
+    if wg.shape != wu.shape or sg.shape != su.shape or wg.dim() != 2:
+        raise ValueError("pack_pair: gate and up must have the same 2-D shapes")
+    n, words = wg.shape
+    k = words * 32 // bits
+    if n % 16 or k % gs or any(t.dtype != torch.bfloat16 for t in (sg, bg, su, bu)):
+        raise ValueError("pack_pair: rows in whole 16-row tiles, bf16 scales and biases")
+    stream = _lib.stream_of(wg)
+    ts = [t.contiguous() for t in (wg, sg, bg, wu, su, bu)]
+    lib = _lib.lib()
+    out = torch.empty((-(-2 * n // 128), k // gs, lib.tf_unit_words(bits, gs)), dtype=torch.int32, device=wg.device)
+    _lib.check(lib.tf_pack_pair(*[t.data_ptr() for t in ts], n, k, bits, gs, out.data_ptr(), stream), "pack_pair")
+    return Q4(out, None, None, 2 * n, k, gs, bits)
+
+
+def matmul_act(x: torch.Tensor, q: Q4, *, act: str = "swiglu", limit: float = 0.0, out: torch.Tensor | None = None,
+               pdl: bool = False) -> torch.Tensor:
+    """Projection with the experts' activation epilogue, dense form: ``act="swiglu"`` on a ``pack_pair`` weight gives
+    bf16(bf16(silu(bf16 gate)) * bf16 up) as (M, n / 2); ``act="relu2"`` gives bf16(relu(bf16 v)^2) as (M, n)."""
+
+    x = _rows(x, q.k, "matmul_act")
+    if act not in ("swiglu", "relu2"):
+        raise ValueError("matmul_act: act is 'swiglu' or 'relu2'")
+    m = x.shape[0]
+    stream = _lib.stream_of(x)
+    ncols = q.n // 2 if act == "swiglu" else q.n
+    if out is None:
+        out = torch.empty((m, ncols), dtype=torch.bfloat16, device=x.device)
+    elif out.shape != (m, ncols) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise ValueError("matmul_act: out must be (M, columns) bf16 with unit-stride rows")
+    _lib.check(_lib.lib().tf_qmm_act(x.data_ptr(), x.stride(0), m, q.weight.data_ptr(), q.weight.stride(0), q.n, q.k, q.bits,
+                                     q.gs, out.data_ptr(), out.stride(0), 2 if act == "swiglu" else 1, float(limit), int(pdl),
+                                     stream), "matmul_act")
+    return out
