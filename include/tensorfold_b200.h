@@ -131,6 +131,19 @@ int tf_moe_topk(const float* logits, int64_t ldl, int rows, int experts, int top
  * Replaces the Triton `_combine` of cuda/moe.py:130-150. */
 int tf_moe_combine(const void* y, int y_bf16, const float* wts, int rows, int slots, int d, void* out, void* stream);
 
+/* ---- stored (MLX) layout helpers and the tensor-parallel reduction ------------------------------------------------ */
+
+/* out[r, :] = q[row, :] * scale + bias in fp32 (rounded once when out is bf16) over the stored MLX words, row = ids[r]
+ * (int32, or int64 with ids64) or r when ids is NULL.  meta: dtype of scales and biases, 0 bf16, 1 fp16, 2 fp32.
+ * Replaces the Triton `embed` of cuda/kernels/affine_kernels.py:49-60 (cuda/kernels/affine.py:71-87) and, without ids
+ * and with fp32 output, the diagnostic `dequantize` of families/qwen3_5/cuda/qmm.py:132-149. */
+int tf_affine_rows(const void* ids, int ids64, int rows, const void* words, const void* scales, const void* biases, int meta,
+                   int n, int k, int bits, int gs, void* out, int out_f32, void* stream);
+/* out[i] = round(((p[0][i] + p[1][i]) + p[2][i]) + ...): the rank-ordered sum of `world` gathered partials (fp32, or
+ * bf16 with parts_bf16), one rounding, so every rank ends with the same bits.  Generalises the two-rank
+ * rank0.float() + rank1.float() of families/qwen3_5/cuda/distributed.py:281-284. */
+int tf_sum_ranks(const void* parts, int world, int64_t total, int parts_bf16, void* out, int out_f32, void* stream);
+
 /* out[i] = round(part[0][i] + part[1][i] + ...), slices added in order: cuda/kernels/qmm.cu:235-243 (reduce_kernel).
  * part: [sk, total] fp32; out: [total] bf16 or fp32. */
 int tf_reduce_slices(const float* part, int sk, int64_t total, void* out, int out_f32, void* stream);

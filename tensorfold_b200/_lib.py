@@ -38,6 +38,8 @@ SIGNATURES = {
     "tf_moe_router": (_i32, (_vp, _i64, _i32, _i32, _vp, _i32, _vp, _i64, _vp)),
     "tf_moe_topk": (_i32, (_vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp)),
     "tf_moe_combine": (_i32, (_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp)),
+    "tf_affine_rows": (_i32, (_vp, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp)),
+    "tf_sum_ranks": (_i32, (_vp, _i32, _i64, _i32, _vp, _i32, _vp)),
     "tf_reduce_slices": (_i32, (_vp, _i32, _i64, _vp, _i32, _vp)),
 }
 

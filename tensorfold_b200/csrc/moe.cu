@@ -223,6 +223,7 @@ __global__ void combine_kernel(const void* __restrict__ y, const float* __restri
   float a0 = 0.f, a1 = 0.f;
   for (int k = 0; k < slots; ++k) {
     const float w = wts[r * slots + k];
+    if (w == 0.f) continue;                                      // a slot another rank owns: its y is never read
     const int64_t off = (static_cast<int64_t>(r) * slots + k) * d + c;
     float y0, y1 = 0.f;
     if (YBF16) {

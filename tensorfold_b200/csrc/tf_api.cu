@@ -1,5 +1,7 @@
 // extern "C" entry points (include/tensorfold_b200.h), argument checks, and the small kernels around the matmul:
 // load-time repack and its inverse, group sums, slice reduction.
+#include <cuda_fp16.h>
+
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
@@ -165,6 +167,51 @@ __global__ void reduce_slices_kernel(const float* __restrict__ part, int sk, int
     for (int s = 1; s < sk; ++s) acc = acc + part[static_cast<int64_t>(s) * total + i];
     if (out_f32) reinterpret_cast<float*>(out)[i] = acc;
     else reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(acc);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// stored-layout helpers: dequantised rows (embedding gather, diagnostics) and the rank-ordered sum of partials
+// ---------------------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float meta_value(const void* p, int64_t i, int dtype) {      // 0 bf16, 1 fp16, 2 fp32
+  if (dtype == 0) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  if (dtype == 1) return __half2float(static_cast<const __half*>(p)[i]);
+  return static_cast<const float*>(p)[i];
+}
+
+// out[r, k] = q[row(r), k] * scale + bias in fp32 (one rounding when out is bf16); row(r) = ids[r], or r without ids.
+__global__ void affine_rows_kernel(const void* __restrict__ ids, int ids64, int rows, const uint32_t* __restrict__ words,
+                                   const void* __restrict__ scales, const void* __restrict__ biases, int meta, int n, int k,
+                                   int bits, int gs, void* __restrict__ out, int out_f32) {
+  const int r = blockIdx.y;
+  const int kk = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows || kk >= k) return;
+  int64_t row = r;
+  if (ids != nullptr) row = ids64 ? static_cast<const int64_t*>(ids)[r] : static_cast<const int*>(ids)[r];
+  float v = 0.f;
+  if (row >= 0 && row < n) {                                   // ids outside the table give zeros, never a fault
+    const int64_t wpr = static_cast<int64_t>(k) * bits / 32, kg = k / gs;
+    const float q = static_cast<float>(stored_code(words + row * wpr, kk, bits, wpr));
+    v = q * meta_value(scales, row * kg + kk / gs, meta) + meta_value(biases, row * kg + kk / gs, meta);
+  }
+  if (out_f32) static_cast<float*>(out)[static_cast<int64_t>(r) * k + kk] = v;
+  else static_cast<__nv_bfloat16*>(out)[static_cast<int64_t>(r) * k + kk] = __float2bfloat16_rn(v);
+}
+
+// out[i] = round(((p[0][i] + p[1][i]) + p[2][i]) + ...) in fp32, rank order; partials fp32 or bf16.
+__global__ void sum_ranks_kernel(const void* __restrict__ parts, int world, int64_t total, int parts_bf16, void* out,
+                                 int out_f32) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < world; ++r) {
+      const float v = parts_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(parts)[r * total + i])
+                                 : static_cast<const float*>(parts)[r * total + i];
+      acc = r == 0 ? v : acc + v;
+    }
+    if (out_f32) static_cast<float*>(out)[i] = acc;
+    else static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -429,6 +476,27 @@ int tf_moe_experts(const void* x, int64_t ldx, int slots, const void* tiled, int
   p.epi = epi, p.limit = limit;
   const cudaError_t e = launch_bits(p, 4, gs, tile / 8, 1, static_cast<cudaStream_t>(stream), false);
   return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_moe_experts launch");
+}
+
+int tf_affine_rows(const void* ids, int ids64, int rows, const void* words, const void* scales, const void* biases, int meta,
+                   int n, int k, int bits, int gs, void* out, int out_f32, void* stream) {
+  if (!format_ok(bits, gs)) return fail(TF_ERR_ARG, "tf_affine_rows: %d bits / groups of %d is not an affine format", bits, gs);
+  if (rows < 1 || rows > 65535 * 32 || n < 1 || k < gs || k % gs || (static_cast<int64_t>(k) * bits) % 32 || meta < 0 || meta > 2)
+    return fail(TF_ERR_ARG, "tf_affine_rows: bad shape rows=%d n=%d k=%d", rows, n, k);
+  if (!words || !scales || !biases || !out) return fail(TF_ERR_ARG, "tf_affine_rows: null pointer");
+  if (rows > 65535) return fail(TF_ERR_ARG, "tf_affine_rows: at most 65535 rows a call");
+  dim3 grid((k + 255) / 256, rows);
+  affine_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ids, ids64, rows, static_cast<const uint32_t*>(words),
+                                                                         scales, biases, meta, n, k, bits, gs, out, out_f32);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_affine_rows");
+}
+
+int tf_sum_ranks(const void* parts, int world, int64_t total, int parts_bf16, void* out, int out_f32, void* stream) {
+  if (!parts || !out || world < 1 || total < 1) return fail(TF_ERR_ARG, "tf_sum_ranks: bad arguments");
+  sum_ranks_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(parts, world, total, parts_bf16, out, out_f32);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_sum_ranks");
 }
 
 int tf_reduce_slices(const float* part, int sk, int64_t total, void* out, int out_f32, void* stream) {

@@ -1,0 +1,84 @@
+"""Host-side logic without a GPU: shard maps on CPU tensors, refusals, and the rank-ordered reduction over a
+two-process gloo group (the N > 1 path of the tensor-parallel layers)."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import affine as oaff
+from tensorfold_b200 import synthetic
+from tensorfold_b200.cuda.kernels import affine
+from tensorfold_b200.families.qwen3_5.cuda import distributed
+from tensorfold_b200.families.qwen3_5.cuda.weights import QLinear
+
+
+def test_shapes_and_slices_match_the_oracle(golden):
+    for bits, gs, rank, a, b, g0, g1 in golden["input_slice"].tolist():
+        assert affine.input_slice(gs * 4, bits, gs, rank) == ((a, b), (g0, g1))
+    with pytest.raises(ValueError):
+        affine.input_slice(384, 5, 128, 0)
+    for bits, gs, shape in [(1, 64, (4, 16)), (8, 16, (4, 64)), (3, 32, (4, 4))]:
+        with pytest.raises(ValueError):
+            affine.packed_shape(shape, (4, 2), (4, 2), bits, gs)
+    assert affine.packed_shape((5, 24), (5, 4), (5, 4), 3, 64) == (5, 256)
+    for world in (4, 8):
+        for rank in range(world):
+            assert affine.input_slice(8192, 4, 64, rank, world) == oaff.input_slice(8192, 4, 64, rank, world)
+
+
+def test_partition_map_on_cpu_tensors(golden):
+    assert distributed.output_rows(16, 1).tolist() == golden["rows_plain_r1"].tolist()
+    assert distributed.output_rows(40, 0, segments=(8, 8, 24)).tolist() == golden["rows_seg_r0"].tolist()
+    assert distributed.output_rows(32, 1, block=8).tolist() == golden["rows_block_r1"].tolist()
+    words, scales, biases = synthetic.raw_weight(64, 512, 4, 64, 3)
+    q = QLinear(words, scales, biases)
+    for world in (2, 4, 8):
+        cols = [distributed.split_output(q, r, world) for r in range(world)]
+        assert torch.equal(torch.cat([c.weight for c in cols]), words)
+        rows = [distributed.split_input(q, r, world) for r in range(world)]
+        assert torch.equal(torch.cat([c.weight for c in rows], dim=1), words)
+        assert torch.equal(torch.cat([c.scales for c in rows], dim=1), scales)
+        full = oaff.dequantize(words.numpy(), scales.float().numpy(), biases.float().numpy(), 4, 64)
+        part = oaff.dequantize(rows[1].weight.numpy(), rows[1].scales.float().numpy(), rows[1].biases.float().numpy(), 4, 64)
+        np.testing.assert_array_equal(part, full[:, 512 // world:2 * 512 // world])     # values never change
+    x = torch.arange(2 * 512, dtype=torch.float32).view(2, 512)
+    assert torch.equal(distributed.local_input(x, 3, 4), x[:, 384:512])
+    with pytest.raises(ValueError):
+        distributed.split_output(q, 0, 3)
+    with pytest.raises(ValueError):
+        distributed.local_input(x, 0, 3)
+
+
+def test_rank_sum_rounds_after_the_fp32_add(golden):
+    p0, p1 = torch.from_numpy(golden["rank_p0"]), torch.from_numpy(golden["rank_p1"])
+    got = distributed.sum_rank_partials([p0, p1])
+    assert synthetic.bf16_bits(got).tolist() == golden["rank_sum_bf16"].tolist()
+    four = [p0, p1, p0 * 0.5, p1 * 0.25]
+    want = oaff.sum_rank_partials([p.numpy() for p in four])
+    assert torch.equal(distributed.sum_rank_partials(four).float(), torch.from_numpy(want))
+
+
+def _worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(100 + rank)
+        local = torch.randn((5, 33), generator=g) * 3
+        summed = distributed.gather_rank_partials(local)
+        torch.save((local, summed), f"{out}/r{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gloo_ranks_agree_bit_for_bit_and_sum_in_rank_order(tmp_path, world):
+    port = 29600 + world + os.getpid() % 200
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    got = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
+    want = oaff.sum_rank_partials([g[0].numpy() for g in got])
+    for local, summed in got:
+        assert torch.equal(summed.float(), torch.from_numpy(want))
