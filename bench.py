@@ -25,6 +25,7 @@ if str(ROOT) not in sys.path:
 BITS, GS = 4, 64
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126 * 2 ** 20
+TRAFFIC_PER_LAUNCH = None          # dram bytes per launch of the dominant kernel from the ncu capture under profiles/
 
 
 def weight_bytes(n: int, k: int, bits: int = BITS, gs: int = GS) -> int:
@@ -180,12 +181,175 @@ def run_reference(args) -> None:
 # the B200 arm
 # ----------------------------------------------------------------------------------------------------------------------
 
+def graph_time(fn, steps: int, stream, reps: int = 5):
+    """Capture `steps` calls of fn(i) in one CUDA graph on `stream`; returns (graph, [ms per replay])."""
+
+    import torch
+
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(steps):
+                fn(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            graph.replay()
+            b.record(stream)
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+    return graph, times
+
+
+def rolled_experts(e: int, n: int, k: int, seed: int):
+    """E distinct expert weights from one seeded draw (rows rolled per expert): cheap to make, same distributions."""
+
+    import torch
+
+    from tensorfold_b200 import synthetic
+
+    w = synthetic.affine_weight(n, k, BITS, GS, seed=seed)
+    return tuple(torch.stack([torch.roll(t, 7 * i + 1, 0) for i in range(e)]) for t in w)
+
+
+def moe_layer_bench(dev, rows_list=(16, 2048)) -> dict:
+    """The routed-MoE layer: hidden 2688, 128 experts of width 1856, top 6, one shared expert of width 3712."""
+
+    import torch
+
+    from tensorfold_b200 import synthetic
+    from tensorfold_b200.cuda import experts, moe
+    from tensorfold_b200.cuda.kernels import qmm
+
+    d, e, ni, sni, top_k = 2688, 128, 1856, 3712, 6
+    g = torch.Generator().manual_seed(11)
+    todev = lambda m: tuple(t.to(dev) for t in m)
+    ex = experts.make([todev(rolled_experts(e, ni, d, 1)), todev(rolled_experts(e, ni, d, 2))], todev(rolled_experts(e, d, ni, 3)), GS)
+    shared = moe.SharedExpert(qmm.pack_pair(todev(synthetic.affine_weight(sni, d, BITS, GS, seed=4)),
+                                            todev(synthetic.affine_weight(sni, d, BITS, GS, seed=5)), GS),
+                              qmm.pack(*todev(synthetic.affine_weight(d, sni, BITS, GS, seed=6)), GS))
+    wr = (torch.randn((e + 1, d), generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    layer = moe.Routed(wr, ex, top_k, shared)
+    out = {}
+    stream = torch.cuda.Stream()
+    per_expert = 3 * weight_bytes(ni, d)
+    for rows in rows_list:
+        xs = [synthetic.activations(rows, d, 40 + i).to(dev) for i in range(4)]       # different routings in turn
+        prefill = rows > 128
+        for x in xs:
+            moe.run(x, layer, prefill=prefill)
+        torch.cuda.synchronize()
+        steps = 8
+        _, times = graph_time(lambda i: moe.run(xs[i % 4], layer, prefill=prefill), steps, stream)
+        us = sorted(times)[len(times) // 2] * 1e3 / steps
+        buf = next(b for k, b in moe._scratch.items() if k[0] >= rows and k[5] == prefill)
+        moe.run(xs[0], layer, prefill=prefill)
+        distinct = int(torch.unique(buf.pick[:rows, :top_k]).numel())
+        algo = distinct * per_expert + 3 * weight_bytes(sni, d) + 2 * (e + 1) * d + 2 * rows * d * 2
+        flops = 2 * rows * (top_k * 3 * ni * d + 3 * sni * d + (e + 1) * d)
+        out[f"M{rows}"] = {"us": us, "distinct_experts": distinct, "algorithmic_gb_s": algo / us / 1e3,
+                           "tflops": flops / us / 1e6}
+    return out
+
+
+def dense_rows_bench(dev, layers, shapes, ring, splits) -> dict:
+    """The same layer at other row counts: weight GB/s at M = 1, 4, 16 and TFLOP/s at M = 2048 (through ``matmul``)."""
+
+    import torch
+
+    from tensorfold_b200 import synthetic
+    from tensorfold_b200.cuda.kernels import qmm
+
+    layer_bytes = sum(weight_bytes(n, k) for _, (n, k) in shapes)
+    stream = torch.cuda.Stream()
+    out = {}
+    for rows in (1, 4, 16, 2048):
+        xs = {name: synthetic.activations(rows, k, 3).to(dev) for name, (n, k) in shapes}
+        ys = {name: torch.empty((rows, n), dtype=torch.bfloat16, device=dev) for name, (n, k) in shapes}
+
+        def fn(i):
+            for name, _ in shapes:
+                qmm.matmul(xs[name], layers[i % ring][name], out=ys[name], pdl=True, sk=splits[name])
+
+        for i in range(2):
+            fn(i)
+        torch.cuda.synchronize()
+        steps = 2 * ring if rows <= 16 else 2
+        _, times = graph_time(fn, steps, stream)
+        us = sorted(times)[len(times) // 2] * 1e3 / steps
+        entry = {"us_per_layer": us, "weight_gb_s": layer_bytes / us / 1e3}
+        if rows >= 256:
+            entry["tflops"] = 2 * rows * sum(n * k for _, (n, k) in shapes) / us / 1e6
+        out[f"M{rows}"] = entry
+    return out
+
+
+def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict:
+    """Tensor-parallel MoE decoder block: hidden 6144, 160 experts top 8 of width 1536 split by expert across the ranks,
+    attention o_proj 8192 -> 6144 row-parallel; both bf16 partials [M, 6144] are reduced in rank order over NVLink."""
+
+    import torch
+    import torch.distributed as dist
+
+    from tensorfold_b200 import synthetic
+    from tensorfold_b200.cuda import experts, tp
+    from tensorfold_b200.cuda.kernels import qmm
+
+    d, e, ni, top_k, ko = 6144, 160, 1536, 8, 8192
+    local_e = e // world
+    g = torch.Generator().manual_seed(21)
+    todev = lambda m: tuple(t.to(dev) for t in m)
+
+    def local_experts(n, k, seed):
+        w = synthetic.affine_weight(n, k, BITS, GS, seed=seed)
+        return tuple(torch.stack([torch.roll(t, 7 * (rank * local_e + i) + 1, 0) for i in range(local_e)]) for t in w)
+
+    ex = experts.make([todev(local_experts(ni, d, 1)), todev(local_experts(ni, d, 2))], todev(local_experts(d, ni, 3)), GS)
+    wr = (torch.randn((e, d), generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    layer = tp.ExpertParallelMoE(wr, ex, top_k, rank * local_e, e)
+    wo = synthetic.affine_weight(d, ko // world, BITS, GS, seed=30 + rank)
+    o_proj = qmm.pack(*todev(wo), GS)
+    out = {}
+    for rows in rows_list:
+        prefill = rows > 128
+        buf = layer.buffers(rows, dev, prefill=prefill)
+        attn = synthetic.activations(rows, ko // world, 50 + rank).to(dev)
+
+        def block():
+            h = tp.ordered_all_reduce(qmm.matmul(attn, o_proj))
+            return layer.run(h, buf)
+
+        for _ in range(3):
+            block()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        iters = 20
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            block()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) * 1e3 / iters], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[f"M{rows}"] = {"us": float(t.item()), "timing": "eager launches, CUDA events, max over ranks"}
+    return out
+
+
 def run_b200(args) -> None:
     import torch
     import torch.distributed as dist
 
     from tensorfold_b200 import _lib, synthetic
+    from tensorfold_b200.cuda import tp
     from tensorfold_b200.cuda.kernels import qmm
+    from tensorfold_b200.families.qwen3_5.cuda import distributed
+    from tensorfold_b200.families.qwen3_5.cuda.weights import QLinear
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -200,29 +364,41 @@ def run_b200(args) -> None:
     rows = args.rows
     shapes = layer_shapes()
     layer_bytes = sum(weight_bytes(n, k) for _, (n, k) in shapes)
-    ring = max(2, -(-4 * L2_BYTES // layer_bytes))          # distinct layers: the ring holds > 4x L2 of weights
+    ring = max(2, -(-4 * L2_BYTES * world // layer_bytes))   # distinct layers: each rank's ring holds > 4x L2 of weights
+    column = ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj")          # output rows split across ranks
     layers = []
     for li in range(ring):
         packed = {}
         for pi, (name, (n, k)) in enumerate(shapes):
             w = synthetic.affine_weight(n, k, BITS, GS, seed=1000 * li + pi)
-            packed[name] = qmm.pack(w[0].to(dev), w[1].to(dev), w[2].to(dev), GS)
+            q = QLinear(w[0].to(dev), w[1].to(dev), w[2].to(dev), gs=GS, bits=BITS)
+            if world > 1:
+                q = distributed.split_output(q, rank, world) if name in column else distributed.split_input(q, rank, world)
+            packed[name] = qmm.pack(q.weight, q.scales, q.biases, GS)
+            del q
         layers.append(packed)
-    host_x = {name: synthetic.activations(rows, k, 31 + i).pin_memory() for i, (name, (n, k)) in enumerate(shapes)}
+    kin = {name: (k if name in column or world == 1 else k // world) for name, (n, k) in shapes}
+    nout = {name: (n // world if name in column and world > 1 else n) for name, (n, k) in shapes}
+    host_x = {name: synthetic.activations(rows, kin[name], 31 + i).pin_memory() for i, (name, _) in enumerate(shapes)}
     dev_x = {name: t.to(dev) for name, t in host_x.items()}
-    dev_y = {name: torch.empty((rows, n), dtype=torch.bfloat16, device=dev) for name, (n, k) in shapes}
-    host_y = {name: torch.empty((rows, n), dtype=torch.bfloat16).pin_memory() for name, (n, k) in shapes}
+    dev_y = {name: torch.empty((rows, nout[name]), dtype=torch.bfloat16, device=dev) for name, _ in shapes}
+    host_y = {name: torch.empty((rows, nout[name]), dtype=torch.bfloat16).pin_memory() for name, _ in shapes}
     torch.cuda.synchronize()
 
     if args.lanes:
         _lib.check(_lib.lib().tf_tune(b"qmm_lanes", args.lanes), "tune")
-    splits = {name: (qmm.split_k(n, k, GS, args.sk_target) if args.sk_target else qmm.default_split(n, k, GS))
-              for name, (n, k) in shapes}
+    splits = {name: (qmm.split_k(nout[name], kin[name], GS, args.sk_target) if args.sk_target
+                     else qmm.default_split(nout[name], kin[name], GS)) for name, _ in shapes}
+    reduced = {}
 
     def step(i: int, pdl: bool) -> None:
         layer = layers[i % ring]
         for name, _ in shapes:
-            qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=pdl, sk=splits[name])
+            if world > 1 and name not in column:            # row-parallel: bf16 partial, rank-ordered reduction
+                qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=False, sk=splits[name])
+                reduced[name] = tp.ordered_all_reduce(dev_y[name])
+            else:
+                qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=pdl and world == 1, sk=splits[name])
 
     def barrier():
         if world > 1:
@@ -231,12 +407,12 @@ def run_b200(args) -> None:
 
     for i in range(max(args.warmup, 3)):                     # eager warm-up (also the first, configuring, calls)
         step(i, False)
-    torch.cuda.synchronize()
+    barrier()
 
     stream = torch.cuda.Stream()
-    pdl = not args.no_pdl
+    pdl = not args.no_pdl and world == 1
 
-    def capture(first: int, count: int, with_copies: bool):
+    def capture(first: int, count: int, with_copies: bool, use_pdl: bool):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(stream):
             with torch.cuda.graph(graph, stream=stream):
@@ -244,18 +420,18 @@ def run_b200(args) -> None:
                     if with_copies:
                         for name, _ in shapes:
                             dev_x[name].copy_(host_x[name], non_blocking=True)
-                    step(i, pdl)
+                    step(i, use_pdl)
                     if with_copies:
                         for name, _ in shapes:
                             host_y[name].copy_(dev_y[name], non_blocking=True)
         return graph
 
     try:
-        timed = capture(0, args.steps, False)
+        timed = capture(0, args.steps, False, pdl)
     except RuntimeError:
         pdl = False
         torch.cuda.synchronize()
-        timed = capture(0, args.steps, False)
+        timed = capture(0, args.steps, False, False)
 
     clocks = ClockSampler(local)
     with clocks:
@@ -282,10 +458,9 @@ def run_b200(args) -> None:
                 trials.append(s.elapsed_time(e))
 
             # end to end: host activations in, host results out, one graph replay (copies included) and a sync per step
-            e2e_graphs = [capture(i, 1, True) for i in range(ring)]
+            e2e_graphs = [capture(i, 1, True, False) for i in range(ring)]
             for g in e2e_graphs:
                 g.replay()
-            torch.cuda.synchronize()
             barrier()
             t0 = time.perf_counter()
             for i in range(args.steps):
@@ -300,39 +475,52 @@ def run_b200(args) -> None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = times.tolist()
 
-    launches = args.steps * len(shapes)
+    extras = {}
+    if not args.no_extras:
+        if world == 1:
+            extras["moe_layer"] = moe_layer_bench(dev)
+            extras["dense_rows"] = dense_rows_bench(dev, layers, shapes, ring, splits)
+        extras["moe_block"] = moe_block_tp_bench(dev, rank, world)
+
+    launches = args.steps * (len(shapes) + (2 if world > 1 else 0))
     io_bytes = sum(2 * rows * (n + k) for _, (n, k) in shapes)
     algo_bytes_step = layer_bytes + io_bytes
-    value = world * layer_bytes * args.steps / (ms * 1e-3) / 1e9
+    value = layer_bytes * args.steps / (ms * 1e-3) / 1e9     # the whole layer's weights, all ranks together
     peak, peak_kind = measured_peaks()
-    achieved = algo_bytes_step * args.steps / (ms * 1e-3) / 1e9
+    achieved = (layer_bytes / world + io_bytes) * args.steps / (ms * 1e-3) / 1e9      # per GPU
     med = sorted(trials)[len(trials) // 2]
     if rank == 0:
         line = {
             "metric": "affine_4bit_g64_qmm_weight_gbps", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"dense27b_layer_projections_4bit_g64_M{rows}", "rows": rows, "bits": BITS,
                        "group": GS, "projections": {name: list(shape) for name, shape in shapes},
                        "weight_bytes_per_step": layer_bytes, "ring_layers": ring,
-                       "l2": f"steps cycle a ring of {ring} distinct layers ({ring * layer_bytes / 1e6:.0f} MB of weights, "
-                             "larger than the 126 MB L2), so no flush is needed",
+                       "l2": f"steps cycle a ring of {ring} distinct layers ({ring * layer_bytes / world / 1e6:.0f} MB of weights "
+                             "a GPU, larger than the 126 MB L2), so no flush is needed",
                        "launch": "CUDA graph of the timed steps" + (", programmatic dependent launch" if pdl else ""),
-                       "replicas": world > 1, "k_slices": splits, "lanes": args.lanes},
+                       "parallelism": "single GPU" if world == 1 else
+                       f"tp{world}: q/k/v/gate/up column-parallel, o/down row-parallel with a rank-ordered bf16 reduction",
+                       "k_slices": splits, "lanes": args.lanes},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "traffic": None, "kernel": "qmm_tiled_kernel<4,64,%d>" % (rows + 7 >> 3 if rows <= 16 else 8),
-                         "bytes_per_launch": algo_bytes_step / len(shapes), "us_per_launch": ms * 1e3 / launches},
-            "median_of_9": {"ms_per_step": med / args.steps, "value": world * layer_bytes * args.steps / (med * 1e-3) / 1e9},
-            "e2e": {"value": world * layer_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-                    "h2d_bytes_per_step": sum(2 * rows * k for _, (n, k) in shapes),
-                    "d2h_bytes_per_step": sum(2 * rows * n for _, (n, k) in shapes), "ms_per_step": e2e_ms / args.steps},
+                         "peak_kind": peak_kind, "traffic": TRAFFIC_PER_LAUNCH if world == 1 and rows == 16 else None,
+                         "kernel": "qmm_tiled_kernel<4,64,%d,*>" % (1 if rows <= 8 else 2 if rows <= 16 else 4 if rows <= 32 else 8),
+                         "bytes_per_launch": (layer_bytes / world + io_bytes) / len(shapes),
+                         "us_per_launch": ms * 1e3 / (args.steps * len(shapes)), "per": "GPU"},
+            "median_of_9": {"ms_per_step": med / args.steps, "value": layer_bytes * args.steps / (med * 1e-3) / 1e9},
+            "e2e": {"value": layer_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": sum(2 * rows * kin[name] for name, _ in shapes),
+                    "d2h_bytes_per_step": sum(2 * rows * nout[name] for name, _ in shapes), "ms_per_step": e2e_ms / args.steps},
             "clocks": clocks.summary(),
         }
+        line.update(extras)
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(rows)
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -345,6 +533,7 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the MoE layer / row-count sweeps reported beside the headline")
     ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")
     ap.add_argument("--sk-target", type=int, default=0, help="tuning: occupancy target of the K split (0 = default)")
     args = ap.parse_args()

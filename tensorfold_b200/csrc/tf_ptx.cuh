@@ -71,7 +71,7 @@ __device__ __forceinline__ bool mbar_wait_probed(bool ready, uint64_t* bar, uint
 }
 
 // Bulk asynchronous copy global -> shared of `bytes` (a multiple of 16; both addresses 16-byte aligned),
-// completing on an mbarrier.  No multicast: every CTA fetches its own data.
+// completing on an mbarrier.  Every CTA fetches its own data.
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_addr(dst)),
