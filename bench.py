@@ -359,7 +359,9 @@ def run_b200(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        from datetime import timedelta
+
+        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=180))
 
     rows = args.rows
     shapes = layer_shapes()
@@ -438,8 +440,15 @@ def run_b200(args) -> None:
         with torch.cuda.stream(stream):
             timed.replay()                                   # untimed replay: graph upload, instruction caches
             torch.cuda.synchronize()
+            # keep the GPU under this load while clocks are sampled.  The count is agreed across ranks: every replay
+            # holds collectives, so all ranks must issue the same number of them.
             t_load = time.perf_counter()
-            while time.perf_counter() - t_load < 1.5:        # keep the GPU under this load while clocks are sampled
+            timed.replay()
+            torch.cuda.synchronize()
+            once = torch.tensor([time.perf_counter() - t_load], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(once, op=dist.ReduceOp.MAX)
+            for _ in range(max(1, min(2000, int(1.5 / max(once.item(), 1e-5))))):
                 timed.replay()
             barrier()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -520,8 +529,13 @@ def run_b200(args) -> None:
             line["cpu_baseline"] = cpu_baseline(rows)
         print(json.dumps(line))
     if world > 1:
+        # CUDA graphs that hold NCCL nodes keep the communicator busy: tearing the process group down under them can
+        # block for ever, so the graphs go first and the process leaves without the (optional) group teardown.
+        del timed, e2e_graphs
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def main() -> None:
@@ -537,6 +551,10 @@ def main() -> None:
     ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")
     ap.add_argument("--sk-target", type=int, default=0, help="tuning: occupancy target of the K split (0 = default)")
     args = ap.parse_args()
+    if os.environ.get("TF_BENCH_WATCHDOG"):                  # debugging aid: dump every thread's stack and exit if stuck
+        import faulthandler
+
+        faulthandler.dump_traceback_later(int(os.environ["TF_BENCH_WATCHDOG"]), exit=True)
     if args.impl == "reference":
         run_reference(args)
     else:
