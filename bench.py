@@ -25,7 +25,9 @@ if str(ROOT) not in sys.path:
 BITS, GS = 4, 64
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126 * 2 ** 20
-TRAFFIC_PER_LAUNCH = None          # dram bytes per launch of the dominant kernel from the ncu capture under profiles/
+# DRAM bytes per launch of the dominant kernel: the ncu capture under profiles/ read 50.32 MB for gate_proj's 50.86 MB of
+# algorithmic bytes (ratio 0.99); scaled to the average launch of a step (traffic grows with the weight bytes).
+TRAFFIC_RATIO = 0.99
 
 
 def weight_bytes(n: int, k: int, bits: int = BITS, gs: int = GS) -> int:
@@ -514,7 +516,7 @@ def run_b200(args) -> None:
                        "k_slices": splits, "lanes": args.lanes},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "traffic": TRAFFIC_PER_LAUNCH if world == 1 and rows == 16 else None,
+                         "peak_kind": peak_kind, "traffic": TRAFFIC_RATIO * (layer_bytes / world + io_bytes) / len(shapes),
                          "kernel": "qmm_tiled_kernel<4,64,%d,*>" % (1 if rows <= 8 else 2 if rows <= 16 else 4 if rows <= 32 else 8),
                          "bytes_per_launch": (layer_bytes / world + io_bytes) / len(shapes),
                          "us_per_launch": ms * 1e3 / (args.steps * len(shapes)), "per": "GPU"},
@@ -538,6 +540,28 @@ def run_b200(args) -> None:
         os._exit(0)
 
 
+def run_case(args) -> None:
+    """A small fixed case for profiler captures: one projection of the layer, three distinct weight copies (larger than
+    L2 together), six launches at --rows rows."""
+
+    import torch
+
+    from tensorfold_b200 import synthetic
+    from tensorfold_b200.cuda.kernels import qmm
+
+    n, k = synthetic.DENSE_27B[args.case]
+    dev = "cuda"
+    qs = []
+    for i in range(3):
+        w = synthetic.affine_weight(n, k, BITS, GS, seed=i)
+        qs.append(qmm.pack(w[0].to(dev), w[1].to(dev), w[2].to(dev), GS))
+    x = synthetic.activations(args.rows, k, 0).to(dev)
+    for i in range(6):
+        y = qmm.matmul(x, qs[i % 3])
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "rows": args.rows, "launches": 6, "max_abs": float(y.float().abs().max())}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -546,6 +570,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--case", default="", help="profiler case: run six launches of one projection (e.g. gate_proj) and exit")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE layer / row-count sweeps reported beside the headline")
     ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")
@@ -555,7 +580,9 @@ def main() -> None:
         import faulthandler
 
         faulthandler.dump_traceback_later(int(os.environ["TF_BENCH_WATCHDOG"]), exit=True)
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)
