@@ -112,6 +112,21 @@ int tf_moe_plan_blocks(int pairs);
  * replays it on new picks.  Replaces the pybind `plan` of cuda/experts.cpp:43-55 (cuda/experts.cu:157-334). */
 int tf_moe_plan(const int* picks, int pairs, int experts, int tile, int* members, int* items, int* counts, int* rank,
                 int* hist, int max_items, void* stream);
+/* tf_moe_plan for callers that cannot provide scratch: same result, but rank and hist live in a 320 KB array built
+ * into the library (every GPU that loads it holds that array until the process exits).  It is meant for hosts that have
+ * no way to allocate at the point of the call: a serving process that has already handed all of HBM to its own pools,
+ * so a late cudaMalloc would fail, or a plugin that is only given the buffers of the tensors it was called with.  This
+ * entry point calls no cudaMalloc, cudaFree or any allocating library routine.
+ *   limits   pairs <= 16384 and ceil(pairs / 1024) * experts <= 65536; anything larger is refused with TF_ERR_ARG and
+ *            nothing is launched (use tf_moe_plan with your own scratch)
+ *   set-up   the first call on each device looks up the array's device address (that device must be current); make that
+ *            first call before starting a stream capture
+ *   sharing  all calls on a device use the one array and it keeps the last call's contents; nothing in it has to start
+ *            at zero (every counter a call reads is written by that call first).  Two calls that overlap on the GPU
+ *            (different streams, or two host threads) race on it: keep calls on a device ordered.
+ * It has no counterpart in the reference, whose plan always takes caller tensors (cuda/experts.py:101-124). */
+int tf_moe_plan_static(const int* picks, int pairs, int experts, int tile, int* members, int* items, int* counts,
+                       int max_items, void* stream);
 /* Grouped expert projection over a plan: item y = (expert, first, count) multiplies rows members[first .. first+count)
  * (row pair / slots of x when slots > 0: the token gather; row pair when slots == 0) by that expert's weight and writes
  * row `pair` of out.  tiled: [experts][ceil(n / 128)][k / gs][unit] 4-bit units, expert_stride words apart.

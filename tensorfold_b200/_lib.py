@@ -33,6 +33,7 @@ SIGNATURES = {
     "tf_qmm_act": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _i64, _i32, ctypes.c_float, _i32, _vp)),
     "tf_moe_plan_blocks": (_i32, (_i32,)),
     "tf_moe_plan": (_i32, (_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp)),
+    "tf_moe_plan_static": (_i32, (_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp)),
     "tf_moe_experts": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _i64, _i32, _i32,
                               ctypes.c_float, _vp)),
     "tf_moe_router": (_i32, (_vp, _i64, _i32, _i32, _vp, _i32, _vp, _i64, _vp)),

@@ -270,6 +270,55 @@ int tf_moe_plan(const int* picks, int pairs, int experts, int tile, int* members
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_plan");
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// plan without caller scratch
+// ---------------------------------------------------------------------------------------------------------------------
+
+}  // extern "C"
+
+namespace tf {
+namespace {
+
+constexpr int STATIC_PLAN_PAIRS = 16384;              // pairs a tf_moe_plan_static call may sort
+constexpr int STATIC_PLAN_HIST = 65536;               // blocks * experts it may count (16 blocks of up to 4096 experts)
+
+// The plan's working memory for callers that own none: ranks of the pairs, then the per-block expert counts.  Every
+// GPU that loads the library holds these 320 KB until the process exits.
+static __device__ __align__(256) int g_plan_scratch[STATIC_PLAN_PAIRS + STATIC_PLAN_HIST];
+
+int* g_plan_scratch_ptr[64] = {};                     // device address of the array, per device, resolved on first use
+
+}  // namespace
+}  // namespace tf
+
+extern "C" {
+
+int tf_moe_plan_static(const int* picks, int pairs, int experts, int tile, int* members, int* items, int* counts,
+                       int max_items, void* stream) {
+  if (pairs < 1 || experts < 1) return fail_moe(TF_ERR_ARG, "tf_moe_plan_static: bad sizes");
+  const int nblk = (pairs + PLAN_BLOCK - 1) / PLAN_BLOCK;
+  if (pairs > STATIC_PLAN_PAIRS || static_cast<int64_t>(nblk) * experts > STATIC_PLAN_HIST) {
+    char msg[200];
+    snprintf(msg, sizeof msg,
+             "tf_moe_plan_static: %d pairs x %d experts exceed the built-in scratch (at most %d pairs and %d block-expert "
+             "counters); use tf_moe_plan with caller scratch", pairs, experts, STATIC_PLAN_PAIRS, STATIC_PLAN_HIST);
+    return fail_moe(TF_ERR_ARG, msg);
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail_moe(e, "tf_moe_plan_static: cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail_moe(TF_ERR_ARG, "tf_moe_plan_static: device index out of range");
+  if (g_plan_scratch_ptr[dev] == nullptr) {
+    // The array's name is only a host-side handle; the kernel needs its address on the current device.
+    int* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_plan_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return cuda_fail_moe(e, "tf_moe_plan_static: cudaGetSymbolAddress");
+    g_plan_scratch_ptr[dev] = ptr;
+  }
+  int* rank = g_plan_scratch_ptr[dev];
+  return tf_moe_plan(picks, pairs, experts, tile, members, items, counts, rank, rank + STATIC_PLAN_PAIRS, max_items, stream);
+}
+
 int tf_moe_router(const void* x, int64_t ldx, int rows, int d, const void* w, int ne, float* out, int64_t ldo, void* stream) {
   if (rows < 1 || d < 1 || ne < 1 || !x || !w || !out || ldx < d || ldo < ne) return fail_moe(TF_ERR_ARG, "tf_moe_router: bad arguments");
   if (rows > 65535) return fail_moe(TF_ERR_ARG, "tf_moe_router: too many rows");
