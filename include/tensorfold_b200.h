@@ -159,6 +159,14 @@ int tf_affine_rows(const void* ids, int ids64, int rows, const void* words, cons
  * rank0.float() + rank1.float() of families/qwen3_5/cuda/distributed.py:281-284. */
 int tf_sum_ranks(const void* parts, int world, int64_t total, int parts_bf16, void* out, int out_f32, void* stream);
 
+/* Prefill matmul on tcgen05 / tensor memory: every weight rounded once to bf16, w = bf16(fma(q, s, b)), then one fp32
+ * accumulation chain over K; any chunking of the rows gives the same bits (not the bits of tf_qmm).  4-bit weights,
+ * groups of 32 or 64, k % 64 == 0.  x: [m, k] bf16, 16-byte aligned rows (ldx % 8 == 0); out: [m, n] bf16 or fp32.
+ * Replaces the pybind function qmm_prefill(x, w, scales, biases, out, n, gs, f32, tile) of cuda/kernels/qmm.cpp:47-66
+ * (cuda/kernels/qmm_prefill.cu:36-191). */
+int tf_qmm_prefill(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int gs, void* out,
+                   int64_t ldo, int out_f32, void* stream);
+
 /* out[i] = round(part[0][i] + part[1][i] + ...), slices added in order: cuda/kernels/qmm.cu:235-243 (reduce_kernel).
  * part: [sk, total] fp32; out: [total] bf16 or fp32. */
 int tf_reduce_slices(const float* part, int sk, int64_t total, void* out, int out_f32, void* stream);

@@ -1,0 +1,338 @@
+// Prefill matmul on the 5th-generation tensor cores: out[m, n] = sum_k x[m, k] * bf16(q[n, k] * s + b).
+//
+// Arithmetic contract (the reference's prefill form, cuda/kernels/qmm_prefill.cu:1,115-118): every weight is rounded once
+// to bf16, w = bf16(fma(q, s, b)) with q exact, then ONE fp32 accumulation chain runs over all of K in 16-input steps
+// (tcgen05.mma, accumulator in tensor memory).  Any chunking of the rows gives the same bits; they are not the decode
+// kernel's bits (that one keeps the affine terms in fp32).
+//
+// Block tile = 128 output columns x 256 rows of x, "swap-AB": the dequantised weights are the MMA's A operand (M = 128),
+// the rows of x its B operand (N = 256), so every dequantised weight feeds 256 rows and the conversion (CUDA cores)
+// keeps pace with the tensor pipe.  Roles: warp 0 loads (a 2-D tensor-map copy of the x tile with the 128-byte swizzle
+// and a bulk copy of the packed units, per 64-input stage), warp 1 owns tensor memory and issues the MMAs, warps 2-9
+// turn packed codes into the swizzled bf16 A tile and afterwards drain the accumulator to global memory.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "../../include/tensorfold_b200.h"
+#include "tf_layout.h"
+#include "tf_ptx.cuh"
+
+namespace tf {
+
+int fail_moe(int code, const char* msg);
+int cuda_fail_moe(cudaError_t e, const char* what);
+int* device_error_word();          // tf_api.cu: the current device's error word (null before tf_init)
+
+namespace {
+
+constexpr int PF_COLS = 128;       // output columns of a block tile (MMA M)
+constexpr int PF_ROWS = 256;       // rows of x of a block tile (MMA N)
+constexpr int PF_STAGE_K = 64;     // inputs a stage
+constexpr int PF_A_BYTES = PF_COLS * 128;
+constexpr int PF_B_BYTES = PF_ROWS * 128;
+constexpr int PF_W_BYTES = 5120;   // packed units of a stage: one g64 unit (4608 B) or two g32 units (5120 B)
+constexpr int PF_STAGE = PF_A_BYTES + PF_B_BYTES + PF_W_BYTES;
+constexpr int PF_NST = 4;
+constexpr int PF_THREADS = 320;    // 10 warps
+constexpr int PF_SMEM = PF_NST * PF_STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr uint32_t PF_TMEM_COLS = 256;
+
+struct PrefillParams {
+  const uint32_t* w;
+  int64_t sb_stride;
+  int N, K, M;
+  void* out;
+  int64_t ldo;
+  int out_f32;
+  int* err;
+};
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
+  // K-major, 128-byte swizzle: rows 128 B apart inside an 8-row atom, atoms 1024 B apart (SBO), LBO unused (1),
+  // descriptor version 1, layout type 2 (SWIZZLE_128B)
+  const uint32_t lo = ((smem_byte_addr >> 4) & 0x3FFFu) | (1u << 16);
+  const uint32_t hi = 64u | (1u << 14) | (2u << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                   smem_addr(dst)),
+               "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
+      "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int GS>
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmx, const PrefillParams p) {
+  constexpr int S = GS / 16;                                 // k16 steps a group
+  constexpr int UNITS = PF_STAGE_K / GS;                     // units a stage (1 for g64, 2 for g32)
+  constexpr int WPL = words_per_lane(4, GS);
+  constexpr int UNITW = unit_words(4, GS);
+  static_assert(UNITS * UNITW * 4 <= PF_W_BYTES, "stage holds its packed units");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PF_NST * PF_STAGE);
+  uint64_t* b_full = bars;                    // x tile landed (tensor-map copy)
+  uint64_t* w_full = bars + PF_NST;           // packed units landed (bulk copy)
+  uint64_t* a_full = bars + 2 * PF_NST;       // A tile written by the 8 conversion warps
+  uint64_t* empty = bars + 3 * PF_NST;        // the MMAs that read the stage are done
+  uint64_t* acc_full = bars + 4 * PF_NST;     // every MMA of the tile is done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * PF_NST + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int sb = blockIdx.x, m0 = blockIdx.y * PF_ROWS;
+  const int nstages = p.K / PF_STAGE_K;
+
+  auto a_tile = [&](int s) { return smem + s * PF_STAGE; };
+  auto b_tile = [&](int s) { return smem + s * PF_STAGE + PF_A_BYTES; };
+  auto w_stage = [&](int s) { return smem + s * PF_STAGE + PF_A_BYTES + PF_B_BYTES; };
+  auto give_up = [&](int code) {
+    if (lane == 0) {
+      *abort_flag = code;
+      atomicCAS(p.err, 0, code);
+    }
+  };
+
+  if (tid == 0) {
+    for (int i = 0; i < PF_NST; ++i) {
+      mbar_init(b_full + i, 1);
+      mbar_init(w_full + i, 1);
+      mbar_init(a_full + i, 8);
+      mbar_init(empty + i, 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(PF_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ loads
+    const uint32_t* wsb = p.w + static_cast<int64_t>(sb) * p.sb_stride;
+    bool ok = true;
+    for (int i = 0; i < nstages && ok; ++i) {
+      const int s = i % PF_NST;
+      if (i >= PF_NST) {
+        ok = mbar_wait(empty + s, ((i - PF_NST) / PF_NST) & 1, abort_flag);
+        if (!ok) {
+          give_up(ERR_WAIT_EMPTY);
+          break;
+        }
+      }
+      if (lane == 0) {
+        mbar_expect_tx(w_full + s, UNITS * UNITW * 4);
+        bulk_load(w_stage(s), wsb + static_cast<int64_t>(i) * UNITS * UNITW, UNITS * UNITW * 4, w_full + s);
+        mbar_expect_tx(b_full + s, PF_B_BYTES);
+        tma_load_2d(b_tile(s), &tmx, i * PF_STAGE_K, m0, b_full + s);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issue (one thread)
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_ROWS >> 3) << 17) | ((PF_COLS >> 4) << 24);
+    bool ok = true;
+    for (int i = 0; i < nstages && ok; ++i) {
+      const int s = i % PF_NST;
+      const uint32_t parity = (i / PF_NST) & 1;
+      ok = mbar_wait(a_full + s, parity, abort_flag) && mbar_wait(b_full + s, parity, abort_flag);
+      if (!ok) {
+        give_up(ERR_WAIT_FULL);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (lane == 0) {
+        const uint64_t ad = umma_desc(smem_addr(a_tile(s))), bd = umma_desc(smem_addr(b_tile(s)));
+#pragma unroll
+        for (int k = 0; k < PF_STAGE_K / 16; ++k)
+          umma_bf16(tmem_base, ad + 2 * k, bd + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);    // + 32 bytes a k16 step
+        umma_commit(empty + s);
+        if (i == nstages - 1) umma_commit(acc_full);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ conversion: packed codes -> swizzled bf16 A tile
+    const int dw = warp - 2, tp = dw & 3, h = dw >> 2, g = lane >> 2, t = lane & 3;
+    const __nv_bfloat162 k128 = __floats2bfloat162_rn(128.f, 128.f);
+    bool ok = true;
+    for (int i = 0; i < nstages && ok; ++i) {
+      const int s = i % PF_NST;
+      const uint32_t parity = (i / PF_NST) & 1;
+      if (i >= PF_NST) ok = mbar_wait(empty + s, ((i - PF_NST) / PF_NST) & 1, abort_flag);
+      ok = ok && mbar_wait(w_full + s, parity, abort_flag);
+      if (!ok) {
+        give_up(ERR_WAIT_FULL);
+        break;
+      }
+      const uint32_t* wst = reinterpret_cast<const uint32_t*>(w_stage(s));
+      uint8_t* at = a_tile(s);
+#pragma unroll
+      for (int u = 0; u < UNITS; ++u) {
+        const uint32_t* unit = wst + u * UNITW;
+        uint32_t wd[S];
+        if constexpr (S == 4) {
+          const uint4 v = *reinterpret_cast<const uint4*>(unit + (tp * 32 + lane) * WPL + h * S);
+          wd[0] = v.x, wd[1] = v.y, wd[2] = v.z, wd[3] = v.w;
+        } else {
+          const uint2 v = *reinterpret_cast<const uint2*>(unit + (tp * 32 + lane) * WPL + h * S);
+          wd[0] = v.x, wd[1] = v.y;
+        }
+        const uint2 sbw = *reinterpret_cast<const uint2*>(unit + TILE_PAIRS * 32 * WPL + tp * 32 + g * 4 + h * 2);
+        const uint32_t sbv[2] = {sbw.x, sbw.y};                  // columns c0 and c0 + 8
+        __nv_bfloat162 sc[2], bi[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const __nv_bfloat16 sv = __ushort_as_bfloat16(static_cast<unsigned short>(sbv[r] & 0xFFFFu));
+          const __nv_bfloat16 bv = __ushort_as_bfloat16(static_cast<unsigned short>(sbv[r] >> 16));
+          sc[r] = __halves2bfloat162(sv, sv);
+          bi[r] = __halves2bfloat162(bv, bv);
+        }
+        const int c0 = 32 * tp + 16 * h + g;
+#pragma unroll
+        for (int sidx = 0; sidx < S; ++sidx)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t v = ((wd[sidx] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
+            const __nv_bfloat162 q2 = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), k128);       // exact code
+            const __nv_bfloat162 w2 = __hfma2(q2, sc[j & 1], bi[j & 1]);                            // one rounding
+            const int c = c0 + 8 * (j & 1), k = u * GS + 16 * sidx + 2 * t + 8 * (j >> 1);
+            *reinterpret_cast<__nv_bfloat162*>(at + c * 128 + (((k >> 3) ^ (c & 7)) << 4) + (k & 7) * 2) = w2;
+          }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core's reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_full + s);
+    }
+
+    // ------------------------------------------------------------------ epilogue: tensor memory -> global
+    const bool done = mbar_wait(acc_full, 0, abort_flag);
+    if (!done) give_up(ERR_WAIT_FULL);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (done && *abort_flag == 0) {
+      const int lg = warp & 3, half = dw >> 2;                   // this warp may touch TMEM lanes [32 lg, 32 lg + 32)
+      const int n = sb * PF_COLS + lg * 32 + lane;
+#pragma unroll 1
+      for (int chunk = 0; chunk < 4; ++chunk) {
+        uint32_t r[32];
+        const int col0 = half * 128 + chunk * 32;
+        tmem_load32(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + col0, r);
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int m = m0 + col0 + j;
+            if (m < p.M) {
+              if (p.out_f32) reinterpret_cast<float*>(p.out)[m * p.ldo + n] = __uint_as_float(r[j]);
+              else reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(PF_TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(sym);
+  });
+  return fn;
+}
+
+}  // namespace
+
+cudaError_t prefill_configure() {
+  cudaError_t e = cudaFuncSetAttribute(prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+  return e;
+}
+
+}  // namespace tf
+
+using namespace tf;
+
+extern "C" int tf_qmm_prefill(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int gs,
+                              void* out, int64_t ldo, int out_f32, void* stream) {
+  if (gs != 32 && gs != 64) return fail_moe(TF_ERR_UNSUPPORTED, "tf_qmm_prefill: 4-bit weights with groups of 32 or 64");
+  if (m < 1 || n < 1 || k < 64 || k % 64) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: K must be a positive multiple of 64");
+  if (!x || !tiled || !out || ldo < n || ldx < k) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: null pointer or short rows");
+  if (reinterpret_cast<uintptr_t>(x) % 16 || ldx % 8) return fail_moe(TF_ERR_ALIGN, "tf_qmm_prefill: x rows must start on 16-byte boundaries");
+  if (reinterpret_cast<uintptr_t>(tiled) % 16) return fail_moe(TF_ERR_ALIGN, "tf_qmm_prefill: tiled weights must be 16-byte aligned");
+  int* err = device_error_word();
+  if (err == nullptr) return fail_moe(TF_ERR_STATE, "tf_qmm_prefill: tf_init has not been called for the current device");
+  EncodeTiled encode = encode_fn();
+  if (encode == nullptr) return fail_moe(TF_ERR_UNSUPPORTED, "tf_qmm_prefill: the driver does not export cuTensorMapEncodeTiled");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldx) * 2};
+  const cuuint32_t box[2] = {PF_STAGE_K, PF_ROWS};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: cuTensorMapEncodeTiled refused the x tensor");
+  PrefillParams p;
+  p.w = static_cast<const uint32_t*>(tiled);
+  p.sb_stride = sb_stride > 0 ? sb_stride : static_cast<int64_t>(k / gs) * unit_words(4, gs);
+  p.N = n, p.K = k, p.M = m;
+  p.out = out, p.ldo = ldo, p.out_f32 = out_f32;
+  p.err = err;
+  dim3 grid((n + PF_COLS - 1) / PF_COLS, (m + PF_ROWS - 1) / PF_ROWS);
+  if (grid.y > 65535) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: too many rows");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (gs == 64) prefill_kernel<64><<<grid, PF_THREADS, PF_SMEM, s>>>(map, p);
+  else prefill_kernel<32><<<grid, PF_THREADS, PF_SMEM, s>>>(map, p);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_qmm_prefill");
+}

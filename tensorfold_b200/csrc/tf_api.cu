@@ -44,6 +44,14 @@ std::mutex g_init_mutex;
 
 }  // namespace
 
+cudaError_t prefill_configure();      // qmm_prefill.cu
+
+int* device_error_word() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES || !g_devices[dev].ready) return nullptr;
+  return g_devices[dev].err;
+}
+
 int fail_moe(int code, const char* msg) { return fail(code, "%s", msg); }
 int cuda_fail_moe(cudaError_t e, const char* what) { return cuda_fail(e, what); }
 
@@ -276,6 +284,7 @@ int tf_init(int device) {
   if (e == cudaSuccess) e = qmm_configure_b5();
   if (e == cudaSuccess) e = qmm_configure_b6();
   if (e == cudaSuccess) e = qmm_configure_b8();
+  if (e == cudaSuccess) e = prefill_configure();
   int* err = nullptr;
   if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_error_word);
   if (e == cudaSuccess) e = cudaMemset(err, 0, sizeof(int));

@@ -165,6 +165,26 @@ def matmul(x: torch.Tensor, q: Q4, xs: torch.Tensor | None = None, *, sk: int | 
     return part.reshape(-1)[:sk * m * q.n].view(sk, m, q.n)
 
 
+def prefill_matmul(x: torch.Tensor, q: Q4, *, f32: bool = False, tile: int = 0,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
+    """Prefill: weights rounded once to bf16, one fp32 chain over K on the tcgen05 tensor cores; any chunking gives the
+    same bits, not decode's.  ``tile`` is accepted for signature parity (cuda/kernels/qmm.py:160) and unused.  Formats
+    the tcgen05 kernel does not take (other widths, groups of 128, K not a multiple of 64) run through ``matmul``."""
+
+    x = _rows(x, q.k, "prefill_matmul")
+    if q.bits != 4 or q.gs not in (32, 64) or q.k % 64:
+        return matmul(x, q, f32=f32, out=out)
+    m = x.shape[0]
+    stream = _lib.stream_of(x)
+    if out is None:
+        out = torch.empty((m, q.n), dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
+    elif out.shape != (m, q.n) or out.dtype != (torch.float32 if f32 else torch.bfloat16) or out.stride(1) != 1:
+        raise ValueError("prefill_matmul: out must be (M, n) of the requested dtype with unit-stride rows")
+    _lib.check(_lib.lib().tf_qmm_prefill(x.data_ptr(), x.stride(0), m, q.weight.data_ptr(), q.weight.stride(0), q.n, q.k, q.gs,
+                                         out.data_ptr(), out.stride(0), int(f32), stream), "prefill_matmul")
+    return out
+
+
 def pack_pair(gate: tuple, up: tuple, gs: int, bits: int = 4) -> Q4:
     """Gate and up projections (each MLX words, scales, biases of n rows) as ONE weight of 2 n rows that interleaves 16
     gate rows with 16 up rows, so a matmul tile pair holds both halves of every SwiGLU output (see ``matmul_act``)."""
