@@ -135,6 +135,13 @@ int tf_moe_plan_static(const int* picks, int pairs, int experts, int tile, int* 
 int tf_moe_experts(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int n, int k, int gs,
                    const int* items, const int* counts, const int* members, int max_items, int tile, void* out, int64_t ldo,
                    int out_f32, int epi, float limit, void* stream);
+/* The same grouped projection in the prefill arithmetic (weights rounded once to bf16, one fp32 chain over K) on
+ * tcgen05: the rows are first copied in member order into `sorted` ([pairs, k] bf16, caller scratch), then every item
+ * (at most 128 pairs) runs as one tensor-memory tile per 128 output columns.  Plans for it use items of 128 pairs.
+ * Replaces the pybind `prefill` of cuda/experts.cpp:69-82 (cuda/experts_prefill.cu:31-152). */
+int tf_moe_experts_prefill(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int n, int k,
+                           int gs, const int* items, const int* counts, const int* members, int pairs, int max_items,
+                           void* sorted, void* out, int64_t ldo, int out_f32, int epi, float limit, void* stream);
 /* logits[r, e] = fp32 dot of bf16 rows x[r] and w[e].  Replaces the Triton `_router` of cuda/moe.py:23-55. */
 int tf_moe_router(const void* x, int64_t ldx, int rows, int d, const void* w, int ne, float* out, int64_t ldo, void* stream);
 /* Per row: top `topk` experts by fp32 logit (ties to the lower id), weights bf16(exp(l_k - l_0) / sum); with `shared`

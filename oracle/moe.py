@@ -110,8 +110,9 @@ def expert_pairs(x, picks, gate, up, down, gs: int, limit: float = 0.0, weight_b
     return act, y
 
 
-def down_pairs(act, picks, down, gs: int) -> np.ndarray:
-    """float64 down projection of given (bf16-valued) activations, pair p using expert picks[p]."""
+def down_pairs(act, picks, down, gs: int, weight_bf16: bool = False) -> np.ndarray:
+    """float64 down projection of given (bf16-valued) activations, pair p using expert picks[p]; ``weight_bf16`` rounds
+    the dequantised weights to bf16 first (the prefill form, tests/cuda/test_experts.py:146-148)."""
 
     act = np.asarray(act, dtype=np.float64)
     pe = np.asarray(picks).reshape(-1)
@@ -120,12 +121,13 @@ def down_pairs(act, picks, down, gs: int) -> np.ndarray:
     for p, e in enumerate(pe):
         e = int(e)
         if e not in cache:
-            cache[e] = dequantize(down[0][e], down[1][e], down[2][e], 4, gs)
+            w = dequantize(down[0][e], down[1][e], down[2][e], 4, gs)
+            cache[e] = bf16_round(w.astype(np.float32)).astype(np.float64) if weight_bf16 else w
         y[p] = cache[e] @ act[p]
     return y
 
 
-def expert_pairs_relu2(x, picks, up, down, gs: int):
+def expert_pairs_relu2(x, picks, up, down, gs: int, weight_bf16: bool = False):
     """The relu^2 form: act = relu(bf16(up x))^2 (before its bf16 rounding), then the down projection.
     Follows cuda/experts.cuh:67-70 and tests/cuda/test_experts.py:157-158."""
 
@@ -136,9 +138,11 @@ def expert_pairs_relu2(x, picks, up, down, gs: int):
     act = np.zeros((rows * slots, up[0].shape[1]))
     for p, e in enumerate(pe):
         w = dequantize(up[0][int(e)], up[1][int(e)], up[2][int(e)], 4, gs)
+        if weight_bf16:
+            w = bf16_round(w.astype(np.float32)).astype(np.float64)
         v = bf16_round((w @ x[p // slots]).astype(np.float32)).astype(np.float64)
         act[p] = np.maximum(v, 0.0) ** 2
-    return act, down_pairs(bf16_round(act.astype(np.float32)), picks, down, gs)
+    return act, down_pairs(bf16_round(act.astype(np.float32)), picks, down, gs, weight_bf16)
 
 
 def combine(y, wts) -> np.ndarray:

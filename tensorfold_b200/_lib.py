@@ -36,6 +36,8 @@ SIGNATURES = {
     "tf_moe_plan_static": (_i32, (_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp)),
     "tf_moe_experts": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _i64, _i32, _i32,
                               ctypes.c_float, _vp)),
+    "tf_moe_experts_prefill": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i32,
+                                      _i32, ctypes.c_float, _vp)),
     "tf_moe_router": (_i32, (_vp, _i64, _i32, _i32, _vp, _i32, _vp, _i64, _vp)),
     "tf_moe_topk": (_i32, (_vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp)),
     "tf_moe_combine": (_i32, (_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp)),

@@ -29,16 +29,20 @@ int* device_error_word();          // tf_api.cu: the current device's error word
 namespace {
 
 constexpr int PF_COLS = 128;       // output columns of a block tile (MMA M)
-constexpr int PF_ROWS = 256;       // rows of x of a block tile (MMA N)
 constexpr int PF_STAGE_K = 64;     // inputs a stage
 constexpr int PF_A_BYTES = PF_COLS * 128;
-constexpr int PF_B_BYTES = PF_ROWS * 128;
 constexpr int PF_W_BYTES = 5120;   // packed units of a stage: one g64 unit (4608 B) or two g32 units (5120 B)
-constexpr int PF_STAGE = PF_A_BYTES + PF_B_BYTES + PF_W_BYTES;
 constexpr int PF_NST = 4;
 constexpr int PF_THREADS = 320;    // 10 warps
-constexpr int PF_SMEM = PF_NST * PF_STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
-constexpr uint32_t PF_TMEM_COLS = 256;
+
+// ROWS = rows of x of a block tile (MMA N): 256 for dense prompts, 128 for the grouped expert form
+template <int ROWS>
+struct PfGeo {
+  static constexpr int B_BYTES = ROWS * 128;
+  static constexpr int STAGE = PF_A_BYTES + B_BYTES + PF_W_BYTES;
+  static constexpr int SMEM = PF_NST * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
+  static_assert(STAGE % 1024 == 0, "tiles stay 1024-byte aligned for the 128-byte swizzle");
+};
 
 struct PrefillParams {
   const uint32_t* w;
@@ -48,7 +52,25 @@ struct PrefillParams {
   int64_t ldo;
   int out_f32;
   int* err;
+  // grouped form (items != null): block (x, y) = plan item y = (expert, first, count <= ROWS); the tensor map covers the
+  // rows in member order, row first + r of it feeds pair members[first + r], which is the row of out that is written
+  const int* items;
+  const int* counts;
+  const int* members;
+  int64_t expert_stride;
+  int epi;                    // 0 store, 1 relu^2, 2 SwiGLU over gate/up rows interleaved in tiles of 16 (out: N / 2 columns)
+  float limit;
 };
+
+__device__ __forceinline__ float pf_bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float pf_swiglu(float g, float u, float limit) {
+  float gv = pf_bf16r(g), uv = pf_bf16r(u);
+  if (limit > 0.f) {
+    gv = fminf(gv, limit);
+    uv = fminf(fmaxf(uv, -limit), limit);
+  }
+  return pf_bf16r(gv / (1.f + expf(-gv))) * uv;
+}
 
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
   // K-major, 128-byte swizzle: rows 128 B apart inside an 8-row atom, atoms 1024 B apart (SBO), LBO unused (1),
@@ -89,8 +111,11 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int GS>
+template <int GS, int ROWS>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmx, const PrefillParams p) {
+  using Geo = PfGeo<ROWS>;
+  constexpr int PF_ROWS = ROWS, PF_B_BYTES = Geo::B_BYTES, PF_STAGE = Geo::STAGE;
+  constexpr uint32_t PF_TMEM_COLS = ROWS;
   constexpr int S = GS / 16;                                 // k16 steps a group
   constexpr int UNITS = PF_STAGE_K / GS;                     // units a stage (1 for g64, 2 for g32)
   constexpr int WPL = words_per_lane(4, GS);
@@ -109,8 +134,22 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int sb = blockIdx.x, m0 = blockIdx.y * PF_ROWS;
-  const int nstages = p.K / PF_STAGE_K;
+  const int sb = blockIdx.x;
+  const int nstages = (p.K + PF_STAGE_K - 1) / PF_STAGE_K;
+  const int total_units = p.K / GS;
+  const bool grouped = p.items != nullptr;
+  int m0 = blockIdx.y * PF_ROWS, rows_here, first = 0;
+  const uint32_t* wroot = p.w;
+  if (grouped) {
+    if (static_cast<int>(blockIdx.y) >= p.counts[0]) return;               // before any barrier or tensor-memory use
+    const int* item = p.items + 3 * blockIdx.y;
+    wroot += static_cast<int64_t>(item[0]) * p.expert_stride;
+    first = item[1];
+    rows_here = min(PF_ROWS, item[2]);
+    m0 = first;                                                             // row of the member-ordered input
+  } else {
+    rows_here = min(PF_ROWS, p.M - m0);
+  }
 
   auto a_tile = [&](int s) { return smem + s * PF_STAGE; };
   auto b_tile = [&](int s) { return smem + s * PF_STAGE + PF_A_BYTES; };
@@ -145,7 +184,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
 
   if (warp == 0) {
     // ------------------------------------------------------------------ loads
-    const uint32_t* wsb = p.w + static_cast<int64_t>(sb) * p.sb_stride;
+    const uint32_t* wsb = wroot + static_cast<int64_t>(sb) * p.sb_stride;
     bool ok = true;
     for (int i = 0; i < nstages && ok; ++i) {
       const int s = i % PF_NST;
@@ -157,8 +196,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         }
       }
       if (lane == 0) {
-        mbar_expect_tx(w_full + s, UNITS * UNITW * 4);
-        bulk_load(w_stage(s), wsb + static_cast<int64_t>(i) * UNITS * UNITW, UNITS * UNITW * 4, w_full + s);
+        const int units_here = min(UNITS, total_units - i * UNITS);
+        mbar_expect_tx(w_full + s, units_here * UNITW * 4);
+        bulk_load(w_stage(s), wsb + static_cast<int64_t>(i) * UNITS * UNITW, units_here * UNITW * 4, w_full + s);
         mbar_expect_tx(b_full + s, PF_B_BYTES);
         tma_load_2d(b_tile(s), &tmx, i * PF_STAGE_K, m0, b_full + s);
       }
@@ -203,8 +243,21 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
       }
       const uint32_t* wst = reinterpret_cast<const uint32_t*>(w_stage(s));
       uint8_t* at = a_tile(s);
+      const int units_here = min(UNITS, total_units - i * UNITS);
 #pragma unroll
       for (int u = 0; u < UNITS; ++u) {
+        if (u >= units_here) {
+          // K ends inside this stage: x is zero there (the tensor map fills it), the weights must be finite, so zero
+          const int c0z = 32 * tp + 16 * h + g;
+#pragma unroll
+          for (int sidx = 0; sidx < S; ++sidx)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int c = c0z + 8 * (j & 1), k = u * GS + 16 * sidx + 2 * t + 8 * (j >> 1);
+              *reinterpret_cast<uint32_t*>(at + c * 128 + (((k >> 3) ^ (c & 7)) << 4) + (k & 7) * 2) = 0u;
+            }
+          continue;
+        }
         const uint32_t* unit = wst + u * UNITW;
         uint32_t wd[S];
         if constexpr (S == 4) {
@@ -247,19 +300,39 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (done && *abort_flag == 0) {
       const int lg = warp & 3, half = dw >> 2;                   // this warp may touch TMEM lanes [32 lg, 32 lg + 32)
-      const int n = sb * PF_COLS + lg * 32 + lane;
+      const int n = sb * PF_COLS + lg * 32 + lane;               // the weight column this thread's lane holds
+      constexpr int CHUNKS = PF_ROWS / 64;                       // 32-row chunks of this warp's half of the rows
 #pragma unroll 1
-      for (int chunk = 0; chunk < 4; ++chunk) {
+      for (int chunk = 0; chunk < CHUNKS; ++chunk) {
         uint32_t r[32];
-        const int col0 = half * 128 + chunk * 32;
+        const int col0 = half * (PF_ROWS / 2) + chunk * 32;
         tmem_load32(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + col0, r);
-        if (n < p.N) {
+        if (p.epi == 2) {
+          // lanes 0-15 hold gate columns, lanes 16-31 the up columns of the same 16 outputs
+          const int nout = sb * (PF_COLS / 2) + lg * 16 + lane;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int m = m0 + col0 + j;
-            if (m < p.M) {
-              if (p.out_f32) reinterpret_cast<float*>(p.out)[m * p.ldo + n] = __uint_as_float(r[j]);
-              else reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            const float up = __shfl_down_sync(0xFFFFFFFFu, __uint_as_float(r[j]), 16);
+            const int rr = col0 + j;
+            if (lane < 16 && rr < rows_here && nout < p.N / 2) {
+              const int64_t m = grouped ? p.members[first + rr] : m0 + rr;
+              reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + nout] =
+                  __float2bfloat16_rn(pf_swiglu(__uint_as_float(r[j]), up, p.limit));
+            }
+          }
+        } else if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int rr = col0 + j;
+            if (rr < rows_here) {
+              const int64_t m = grouped ? p.members[first + rr] : m0 + rr;
+              float v = __uint_as_float(r[j]);
+              if (p.epi == 1) {
+                v = fmaxf(pf_bf16r(v), 0.f);
+                v = v * v;
+              }
+              if (p.out_f32) reinterpret_cast<float*>(p.out)[m * p.ldo + n] = v;
+              else reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(v);
             }
           }
         }
@@ -292,11 +365,45 @@ EncodeTiled encode_fn() {
 
 }  // namespace
 
+// dst[pos, :] = src[row(members[pos]), :]: the rows of a grouped call in member order, so an item's rows are contiguous
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, int64_t ld, const int* __restrict__ members,
+                                   const int* __restrict__ counts_total, int slots, int pairs, int k,
+                                   __nv_bfloat16* __restrict__ dst) {
+  const int lane = threadIdx.x & 31;
+  const int pos = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pos >= pairs) return;
+  const int pair = members[pos];
+  if (pair < 0 || pair >= pairs) return;                     // members past the planned pairs hold no pair
+  const int64_t row = slots > 0 ? pair / slots : pair;
+  const uint4* s4 = reinterpret_cast<const uint4*>(src + row * ld);
+  uint4* d4 = reinterpret_cast<uint4*>(dst + static_cast<int64_t>(pos) * k);
+  for (int i = lane; i < k / 8; i += 32) d4[i] = s4[i];
+}
+
 cudaError_t prefill_configure() {
-  cudaError_t e = cudaFuncSetAttribute(prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+  cudaError_t e = cudaFuncSetAttribute(prefill_kernel<64, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<256>::SMEM);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_kernel<32, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<256>::SMEM);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_kernel<64, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<128>::SMEM);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_kernel<32, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<128>::SMEM);
   return e;
 }
+
+namespace {
+
+int encode_rows(CUtensorMap* map, const void* x, int64_t ldx, int rows, int k, int box_rows) {
+  EncodeTiled encode = encode_fn();
+  if (encode == nullptr) return fail_moe(TF_ERR_UNSUPPORTED, "prefill: the driver does not export cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldx) * 2};
+  const cuuint32_t box[2] = {PF_STAGE_K, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TF_OK : fail_moe(TF_ERR_ARG, "prefill: cuTensorMapEncodeTiled refused the input tensor");
+}
+
+}  // namespace
 
 }  // namespace tf
 
@@ -305,34 +412,61 @@ using namespace tf;
 extern "C" int tf_qmm_prefill(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int gs,
                               void* out, int64_t ldo, int out_f32, void* stream) {
   if (gs != 32 && gs != 64) return fail_moe(TF_ERR_UNSUPPORTED, "tf_qmm_prefill: 4-bit weights with groups of 32 or 64");
-  if (m < 1 || n < 1 || k < 64 || k % 64) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: K must be a positive multiple of 64");
+  if (m < 1 || n < 1 || k < gs || k % gs) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: K must be a positive multiple of the group");
   if (!x || !tiled || !out || ldo < n || ldx < k) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: null pointer or short rows");
   if (reinterpret_cast<uintptr_t>(x) % 16 || ldx % 8) return fail_moe(TF_ERR_ALIGN, "tf_qmm_prefill: x rows must start on 16-byte boundaries");
   if (reinterpret_cast<uintptr_t>(tiled) % 16) return fail_moe(TF_ERR_ALIGN, "tf_qmm_prefill: tiled weights must be 16-byte aligned");
   int* err = device_error_word();
   if (err == nullptr) return fail_moe(TF_ERR_STATE, "tf_qmm_prefill: tf_init has not been called for the current device");
-  EncodeTiled encode = encode_fn();
-  if (encode == nullptr) return fail_moe(TF_ERR_UNSUPPORTED, "tf_qmm_prefill: the driver does not export cuTensorMapEncodeTiled");
   CUtensorMap map;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldx) * 2};
-  const cuuint32_t box[2] = {PF_STAGE_K, PF_ROWS};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: cuTensorMapEncodeTiled refused the x tensor");
-  PrefillParams p;
+  if (int rc = encode_rows(&map, x, ldx, m, k, 256)) return rc;
+  PrefillParams p = {};
   p.w = static_cast<const uint32_t*>(tiled);
   p.sb_stride = sb_stride > 0 ? sb_stride : static_cast<int64_t>(k / gs) * unit_words(4, gs);
   p.N = n, p.K = k, p.M = m;
   p.out = out, p.ldo = ldo, p.out_f32 = out_f32;
   p.err = err;
-  dim3 grid((n + PF_COLS - 1) / PF_COLS, (m + PF_ROWS - 1) / PF_ROWS);
+  dim3 grid((n + PF_COLS - 1) / PF_COLS, (m + 255) / 256);
   if (grid.y > 65535) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: too many rows");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (gs == 64) prefill_kernel<64><<<grid, PF_THREADS, PF_SMEM, s>>>(map, p);
-  else prefill_kernel<32><<<grid, PF_THREADS, PF_SMEM, s>>>(map, p);
+  if (gs == 64) prefill_kernel<64, 256><<<grid, PF_THREADS, PfGeo<256>::SMEM, s>>>(map, p);
+  else prefill_kernel<32, 256><<<grid, PF_THREADS, PfGeo<256>::SMEM, s>>>(map, p);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_qmm_prefill");
+}
+
+extern "C" int tf_moe_experts_prefill(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int n,
+                                      int k, int gs, const int* items, const int* counts, const int* members, int pairs,
+                                      int max_items, void* sorted, void* out, int64_t ldo, int out_f32, int epi, float limit,
+                                      void* stream) {
+  if (gs != 32 && gs != 64) return fail_moe(TF_ERR_UNSUPPORTED, "tf_moe_experts_prefill: 4-bit weights with groups of 32 or 64");
+  if (n < 1 || k < gs || k % gs || k % 8 || pairs < 1 || max_items < 1 || max_items > 65535)
+    return fail_moe(TF_ERR_ARG, "tf_moe_experts_prefill: bad sizes");
+  if (epi < 0 || epi > 2 || (epi == 2 && n % 32) || (epi != 0 && out_f32)) return fail_moe(TF_ERR_ARG, "tf_moe_experts_prefill: bad epilogue");
+  const int ncols = epi == 2 ? n / 2 : n;
+  if (!x || !tiled || !items || !counts || !members || !sorted || !out || ldo < ncols || slots < 0 || ldx < k)
+    return fail_moe(TF_ERR_ARG, "tf_moe_experts_prefill: null pointer or short rows");
+  if (reinterpret_cast<uintptr_t>(x) % 16 || ldx % 8 || reinterpret_cast<uintptr_t>(sorted) % 16)
+    return fail_moe(TF_ERR_ALIGN, "tf_moe_experts_prefill: rows must start on 16-byte boundaries");
+  int* err = device_error_word();
+  if (err == nullptr) return fail_moe(TF_ERR_STATE, "tf_moe_experts_prefill: tf_init has not been called for the current device");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  gather_rows_kernel<<<(pairs + 7) / 8, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), ldx, members, counts, slots, pairs, k,
+                                                   static_cast<__nv_bfloat16*>(sorted));
+  CUtensorMap map;
+  if (int rc = encode_rows(&map, sorted, k, pairs, k, 128)) return rc;
+  PrefillParams p = {};
+  p.w = static_cast<const uint32_t*>(tiled);
+  p.sb_stride = static_cast<int64_t>(k / gs) * unit_words(4, gs);
+  p.N = n, p.K = k, p.M = pairs;
+  p.out = out, p.ldo = ldo, p.out_f32 = out_f32;
+  p.err = err;
+  p.items = items, p.counts = counts, p.members = members;
+  p.expert_stride = expert_stride;
+  p.epi = epi, p.limit = limit;
+  dim3 grid((n + PF_COLS - 1) / PF_COLS, max_items);
+  if (gs == 64) prefill_kernel<64, 128><<<grid, PF_THREADS, PfGeo<128>::SMEM, s>>>(map, p);
+  else prefill_kernel<32, 128><<<grid, PF_THREADS, PfGeo<128>::SMEM, s>>>(map, p);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_experts_prefill");
 }

@@ -17,7 +17,7 @@ from .kernels import qmm
 NTW = 4                  # n8 tiles a warp
 COLS = 8 * NTW           # output columns a warp
 TILE = 16                # pairs an item holds (decode form)
-PREFILL_TILE = 64        # pairs an item holds (prefill form)
+PREFILL_TILE = 128       # pairs an item holds (prefill form: one tcgen05 tile of 128 rows; the reference's is 64)
 SMALL = 1024             # pairs the one-block plan takes; wider plans rank in blocks of 1024 pairs
 
 
@@ -124,6 +124,7 @@ class Plan:
         self.counts = torch.zeros((2,), dtype=torch.int32, device=device)
         self.rank = torch.zeros((pairs,), dtype=torch.int32, device=device)
         self.hist = torch.zeros((-(-pairs // SMALL) * experts,), dtype=torch.int32, device=device)
+        self.sorted = None       # prefill form: the call's rows in member order (made on first use, before any capture)
 
 
 def route(picks: torch.Tensor, plan: Plan) -> None:
@@ -150,6 +151,17 @@ def _grouped(x, slots, table, n, k, ex, plan, out, rows, epi, limit):
         raise ValueError("experts: out must be 2-D with unit-stride rows")
     stream = _lib.stream_of(x)
     items = min(max_items(rows * plan.slots, plan.experts, plan.tile), plan.items.shape[0])
+    if plan.prefill:
+        if ex.gs not in (32, 64):
+            raise ValueError("prefill plans take expert weights with groups of 32 or 64")
+        pairs = plan.members.shape[0]
+        if plan.sorted is None or plan.sorted.numel() < pairs * k:
+            plan.sorted = torch.empty((pairs * max(k, ex.dims, ex.width),), dtype=torch.bfloat16, device=x.device)
+        _lib.check(_lib.lib().tf_moe_experts_prefill(
+            x.data_ptr(), x.stride(0), slots, table.data_ptr(), table.stride(0), n, k, ex.gs, plan.items.data_ptr(),
+            plan.counts.data_ptr(), plan.members.data_ptr(), rows * plan.slots, items, plan.sorted.data_ptr(), out.data_ptr(),
+            out.stride(0), int(out.dtype == torch.float32), epi, float(limit), stream), "experts (prefill)")
+        return
     _lib.check(_lib.lib().tf_moe_experts(
         x.data_ptr(), x.stride(0), slots, table.data_ptr(), table.stride(0), n, k, ex.gs, plan.items.data_ptr(),
         plan.counts.data_ptr(), plan.members.data_ptr(), items, plan.tile, out.data_ptr(), out.stride(0),
