@@ -44,6 +44,16 @@ def measured_peaks() -> tuple[float, str]:
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def measured_tensor_peak() -> float:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["bf16_tflops"])
+        except Exception:
+            pass
+    return 1590.0
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons sampled every 100 ms while the measurement runs (read-only)."""
 
@@ -284,7 +294,19 @@ def dense_rows_bench(dev, layers, shapes, ring, splits) -> dict:
         us = sorted(times)[len(times) // 2] * 1e3 / steps
         entry = {"us_per_layer": us, "weight_gb_s": layer_bytes / us / 1e3}
         if rows >= 256:
-            entry["tflops"] = 2 * rows * sum(n * k for _, (n, k) in shapes) / us / 1e6
+            flops = 2 * rows * sum(n * k for _, (n, k) in shapes)
+            entry["tflops"] = flops / us / 1e6                               # the row-exact decode arithmetic at M rows
+
+            def pf(i):
+                for name, _ in shapes:
+                    qmm.prefill_matmul(xs[name], layers[i % ring][name], out=ys[name])
+
+            pf(0)
+            torch.cuda.synchronize()
+            _, ptimes = graph_time(pf, 2 * ring, stream)
+            pus = sorted(ptimes)[len(ptimes) // 2] * 1e3 / (2 * ring)
+            entry["prefill"] = {"us_per_layer": pus, "tflops": flops / pus / 1e6,
+                                "of_measured_bf16_peak": flops / pus / 1e6 / measured_tensor_peak()}
         out[f"M{rows}"] = entry
     return out
 

@@ -174,6 +174,11 @@ int tf_sum_ranks(const void* parts, int world, int64_t total, int parts_bf16, vo
 int tf_qmm_prefill(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int gs, void* out,
                    int64_t ldo, int out_f32, void* stream);
 
+/* tf_qmm_prefill with the experts' activation epilogue (epi 1 relu^2, 2 SwiGLU over a tf_pack_pair weight: out then has
+ * n / 2 bf16 columns): the prefill form of tf_qmm_act, used for shared experts run as dense projections. */
+int tf_qmm_prefill_act(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int gs, void* out,
+                       int64_t ldo, int out_f32, int epi, float limit, void* stream);
+
 /* out[i] = round(part[0][i] + part[1][i] + ...), slices added in order: cuda/kernels/qmm.cu:235-243 (reduce_kernel).
  * part: [sk, total] fp32; out: [total] bf16 or fp32. */
 int tf_reduce_slices(const float* part, int sk, int64_t total, void* out, int out_f32, void* stream);

@@ -44,6 +44,7 @@ SIGNATURES = {
     "tf_affine_rows": (_i32, (_vp, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp)),
     "tf_sum_ranks": (_i32, (_vp, _i32, _i64, _i32, _vp, _i32, _vp)),
     "tf_qmm_prefill": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _i64, _i32, _vp)),
+    "tf_qmm_prefill_act": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _i64, _i32, _i32, ctypes.c_float, _vp)),
     "tf_reduce_slices": (_i32, (_vp, _i32, _i64, _vp, _i32, _vp)),
 }
 

@@ -409,11 +409,20 @@ int encode_rows(CUtensorMap* map, const void* x, int64_t ldx, int rows, int k, i
 
 using namespace tf;
 
+extern "C" int tf_qmm_prefill_act(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int gs,
+                                  void* out, int64_t ldo, int out_f32, int epi, float limit, void* stream);
+
 extern "C" int tf_qmm_prefill(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int gs,
                               void* out, int64_t ldo, int out_f32, void* stream) {
+  return tf_qmm_prefill_act(x, ldx, m, tiled, sb_stride, n, k, gs, out, ldo, out_f32, 0, 0.f, stream);
+}
+
+extern "C" int tf_qmm_prefill_act(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int gs,
+                                  void* out, int64_t ldo, int out_f32, int epi, float limit, void* stream) {
   if (gs != 32 && gs != 64) return fail_moe(TF_ERR_UNSUPPORTED, "tf_qmm_prefill: 4-bit weights with groups of 32 or 64");
   if (m < 1 || n < 1 || k < gs || k % gs) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: K must be a positive multiple of the group");
-  if (!x || !tiled || !out || ldo < n || ldx < k) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: null pointer or short rows");
+  if (epi < 0 || epi > 2 || (epi == 2 && n % 32) || (epi != 0 && out_f32)) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: bad epilogue");
+  if (!x || !tiled || !out || ldo < (epi == 2 ? n / 2 : n) || ldx < k) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: null pointer or short rows");
   if (reinterpret_cast<uintptr_t>(x) % 16 || ldx % 8) return fail_moe(TF_ERR_ALIGN, "tf_qmm_prefill: x rows must start on 16-byte boundaries");
   if (reinterpret_cast<uintptr_t>(tiled) % 16) return fail_moe(TF_ERR_ALIGN, "tf_qmm_prefill: tiled weights must be 16-byte aligned");
   int* err = device_error_word();
@@ -426,6 +435,7 @@ extern "C" int tf_qmm_prefill(const void* x, int64_t ldx, int m, const void* til
   p.N = n, p.K = k, p.M = m;
   p.out = out, p.ldo = ldo, p.out_f32 = out_f32;
   p.err = err;
+  p.epi = epi, p.limit = limit;
   dim3 grid((n + PF_COLS - 1) / PF_COLS, (m + 255) / 256);
   if (grid.y > 65535) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: too many rows");
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -205,7 +205,7 @@ def pack_pair(gate: tuple, up: tuple, gs: int, bits: int = 4) -> Q4:
 
 
 def matmul_act(x: torch.Tensor, q: Q4, *, act: str = "swiglu", limit: float = 0.0, out: torch.Tensor | None = None,
-               pdl: bool = False) -> torch.Tensor:
+               pdl: bool = False, prefill: bool = False) -> torch.Tensor:
     """Projection with the experts' activation epilogue, dense form: ``act="swiglu"`` on a ``pack_pair`` weight gives
     bf16(bf16(silu(bf16 gate)) * bf16 up) as (M, n / 2); ``act="relu2"`` gives bf16(relu(bf16 v)^2) as (M, n)."""
 
@@ -219,6 +219,11 @@ def matmul_act(x: torch.Tensor, q: Q4, *, act: str = "swiglu", limit: float = 0.
         out = torch.empty((m, ncols), dtype=torch.bfloat16, device=x.device)
     elif out.shape != (m, ncols) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         raise ValueError("matmul_act: out must be (M, columns) bf16 with unit-stride rows")
+    if prefill and q.bits == 4 and q.gs in (32, 64):          # the prefill arithmetic (weights rounded once to bf16)
+        _lib.check(_lib.lib().tf_qmm_prefill_act(x.data_ptr(), x.stride(0), m, q.weight.data_ptr(), q.weight.stride(0), q.n, q.k,
+                                                 q.gs, out.data_ptr(), out.stride(0), 0, 2 if act == "swiglu" else 1,
+                                                 float(limit), stream), "matmul_act (prefill)")
+        return out
     _lib.check(_lib.lib().tf_qmm_act(x.data_ptr(), x.stride(0), m, q.weight.data_ptr(), q.weight.stride(0), q.n, q.k, q.bits,
                                      q.gs, out.data_ptr(), out.stride(0), 2 if act == "swiglu" else 1, float(limit), int(pdl),
                                      stream), "matmul_act")

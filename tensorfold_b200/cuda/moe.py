@@ -85,8 +85,12 @@ def moe(x: torch.Tensor, router_rows: torch.Tensor, ex: grouped.Experts, buf: Mo
     grouped.gate_up(x, ex, buf.plan, buf.act.view(-1, ex.width), rows)
     grouped.down(buf.act.view(-1, ex.width), ex, buf.plan, buf.y.view(-1, ex.dims), rows)
     if shared is not None:
-        act = qmm.matmul_act(x, shared.up, act="swiglu", limit=shared.limit)
-        qmm.matmul(act, shared.down, f32=buf.y.dtype == torch.float32, out=buf.y[:rows, top_k])
+        if buf.plan.prefill:                                    # prefill arithmetic for the dense shared expert too
+            act = qmm.matmul_act(x, shared.up, act="swiglu", limit=shared.limit, prefill=True)
+            qmm.prefill_matmul(act, shared.down, f32=buf.y.dtype == torch.float32, out=buf.y[:rows, top_k])
+        else:
+            act = qmm.matmul_act(x, shared.up, act="swiglu", limit=shared.limit)
+            qmm.matmul(act, shared.down, f32=buf.y.dtype == torch.float32, out=buf.y[:rows, top_k])
     return buf
 
 
