@@ -311,6 +311,47 @@ def dense_rows_bench(dev, layers, shapes, ring, splits) -> dict:
     return out
 
 
+def stacked_layer_bench(dev, rows_list=(1, 16)) -> dict:
+    """The same layer with the projections that share an input stacked at load time (q|k|v and gate|up, the reference's
+    ``qmm_fast.stack``): four launches a layer instead of seven.  Stacking changes K splits, hence bits, so it is a
+    load-time decision; reported beside the headline, which keeps the seven separate projections."""
+
+    import torch
+
+    from tensorfold_b200 import synthetic
+    from tensorfold_b200.cuda.kernels import qmm
+
+    shapes = dict(layer_shapes())
+    stacks = {"qkv": ("q_proj", "k_proj", "v_proj"), "o": ("o_proj",), "gate_up": ("gate_proj", "up_proj"), "down": ("down_proj",)}
+    layer_bytes = sum(weight_bytes(n, k) for n, k in shapes.values())
+    ring = max(2, -(-4 * L2_BYTES // layer_bytes))
+    layers = []
+    for li in range(ring):
+        packed = {}
+        for si, (sname, parts) in enumerate(stacks.items()):
+            ws = [synthetic.affine_weight(*shapes[p], BITS, GS, seed=5000 + 100 * li + 10 * si + j) for j, p in enumerate(parts)]
+            packed[sname] = qmm.pack(torch.cat([w[0] for w in ws]).to(dev), torch.cat([w[1] for w in ws]).to(dev),
+                                     torch.cat([w[2] for w in ws]).to(dev), GS)
+        layers.append(packed)
+    stream = torch.cuda.Stream()
+    out = {}
+    for rows in rows_list:
+        xs = {s: synthetic.activations(rows, layers[0][s].k, 3).to(dev) for s in stacks}
+        ys = {s: torch.empty((rows, layers[0][s].n), dtype=torch.bfloat16, device=dev) for s in stacks}
+
+        def fn(i):
+            for s in stacks:
+                qmm.matmul(xs[s], layers[i % ring][s], out=ys[s], pdl=True)
+
+        for i in range(2):
+            fn(i)
+        torch.cuda.synchronize()
+        _, times = graph_time(fn, 4 * ring, stream)
+        us = sorted(times)[len(times) // 2] * 1e3 / (4 * ring)
+        out[f"M{rows}"] = {"us_per_layer": us, "weight_gb_s": layer_bytes / us / 1e3, "launches_per_layer": len(stacks)}
+    return out
+
+
 def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict:
     """Tensor-parallel MoE decoder block: hidden 6144, 160 experts top 8 of width 1536 split by expert across the ranks,
     attention o_proj 8192 -> 6144 row-parallel; both bf16 partials [M, 6144] are reduced in rank order over NVLink."""
@@ -343,7 +384,8 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
         attn = synthetic.activations(rows, ko // world, 50 + rank).to(dev)
 
         def block():
-            h = tp.ordered_all_reduce(qmm.matmul(attn, o_proj))
+            part = qmm.prefill_matmul(attn, o_proj) if prefill else qmm.matmul(attn, o_proj)
+            h = tp.ordered_all_reduce(part)
             return layer.run(h, buf)
 
         for _ in range(3):
@@ -513,6 +555,9 @@ def run_b200(args) -> None:
         if world == 1:
             extras["moe_layer"] = moe_layer_bench(dev)
             extras["dense_rows"] = dense_rows_bench(dev, layers, shapes, ring, splits)
+            del layers
+            torch.cuda.empty_cache()
+            extras["stacked_layer"] = stacked_layer_bench(dev)
         extras["moe_block"] = moe_block_tp_bench(dev, rank, world)
 
     launches = args.steps * (len(shapes) + (2 if world > 1 else 0))

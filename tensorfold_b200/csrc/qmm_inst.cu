@@ -10,7 +10,7 @@ namespace tf {
 namespace {
 
 template <int GS, int MT, int KW>
-cudaError_t launch(const QmmParams& p, cudaStream_t stream, bool pdl) {
+cudaError_t launch(const CUtensorMap& tmx, const QmmParams& p, cudaStream_t stream, bool pdl) {
   using Geo = QmmGeo<TF_BITS, GS, MT, KW>;
   const int nblocks = p.sk;
   const int nsb = (p.N + SB_COLS - 1) / SB_COLS;
@@ -35,7 +35,7 @@ cudaError_t launch(const QmmParams& p, cudaStream_t stream, bool pdl) {
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  return cudaLaunchKernelEx(&cfg, qmm_tiled_kernel<TF_BITS, GS, MT, KW>, p);
+  return cudaLaunchKernelEx(&cfg, qmm_tiled_kernel<TF_BITS, GS, MT, KW>, tmx, p);
 }
 
 template <int GS, int MT, int KW>
@@ -45,17 +45,17 @@ cudaError_t configure() {
 }
 
 template <int GS>
-cudaError_t launch_gs(const QmmParams& p, int mt, int kw, cudaStream_t stream, bool pdl) {
+cudaError_t launch_gs(const CUtensorMap& tmx, const QmmParams& p, int mt, int kw, cudaStream_t stream, bool pdl) {
   switch (mt * 10 + kw) {
-    case 11: return launch<GS, 1, 1>(p, stream, pdl);
-    case 12: return launch<GS, 1, 2>(p, stream, pdl);
-    case 14: return launch<GS, 1, 4>(p, stream, pdl);
-    case 21: return launch<GS, 2, 1>(p, stream, pdl);
-    case 22: return launch<GS, 2, 2>(p, stream, pdl);
-    case 24: return launch<GS, 2, 4>(p, stream, pdl);
-    case 41: return launch<GS, 4, 1>(p, stream, pdl);
-    case 42: return launch<GS, 4, 2>(p, stream, pdl);
-    case 81: return launch<GS, 8, 1>(p, stream, pdl);
+    case 11: return launch<GS, 1, 1>(tmx, p, stream, pdl);
+    case 12: return launch<GS, 1, 2>(tmx, p, stream, pdl);
+    case 14: return launch<GS, 1, 4>(tmx, p, stream, pdl);
+    case 21: return launch<GS, 2, 1>(tmx, p, stream, pdl);
+    case 22: return launch<GS, 2, 2>(tmx, p, stream, pdl);
+    case 24: return launch<GS, 2, 4>(tmx, p, stream, pdl);
+    case 41: return launch<GS, 4, 1>(tmx, p, stream, pdl);
+    case 42: return launch<GS, 4, 2>(tmx, p, stream, pdl);
+    case 81: return launch<GS, 8, 1>(tmx, p, stream, pdl);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -79,11 +79,11 @@ cudaError_t configure_gs() {
 #define TF_CAT2(a, b) a##b
 #define TF_CAT(a, b) TF_CAT2(a, b)
 
-cudaError_t TF_CAT(qmm_launch_b, TF_BITS)(const QmmParams& p, int gs, int mt, int kw, cudaStream_t stream, bool pdl) {
+cudaError_t TF_CAT(qmm_launch_b, TF_BITS)(const CUtensorMap& tmx, const QmmParams& p, int gs, int mt, int kw, cudaStream_t stream, bool pdl) {
   switch (gs) {
-    case 32: return launch_gs<32>(p, mt, kw, stream, pdl);
-    case 64: return launch_gs<64>(p, mt, kw, stream, pdl);
-    case 128: return launch_gs<128>(p, mt, kw, stream, pdl);
+    case 32: return launch_gs<32>(tmx, p, mt, kw, stream, pdl);
+    case 64: return launch_gs<64>(tmx, p, mt, kw, stream, pdl);
+    case 128: return launch_gs<128>(tmx, p, mt, kw, stream, pdl);
     default: return cudaErrorInvalidValue;
   }
 }

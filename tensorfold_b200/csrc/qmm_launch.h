@@ -14,7 +14,7 @@ inline int mt_for_rows(int m) { return m <= 8 ? 1 : m <= 16 ? 2 : m <= 32 ? 4 : 
 inline int max_lanes(int mt) { return mt <= 2 ? 4 : mt == 4 ? 2 : 1; }
 
 #define TF_DECLARE_BITS(B)                                                                        \
-  cudaError_t qmm_launch_b##B(const QmmParams& p, int gs, int mt, int kw, cudaStream_t stream, bool pdl); \
+  cudaError_t qmm_launch_b##B(const CUtensorMap& tmx, const QmmParams& p, int gs, int mt, int kw, cudaStream_t stream, bool pdl); \
   cudaError_t qmm_configure_b##B();
 TF_DECLARE_BITS(2)
 TF_DECLARE_BITS(3)

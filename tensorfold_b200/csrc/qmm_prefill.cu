@@ -91,13 +91,6 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-                   smem_addr(dst)),
-               "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y)
-               : "memory");
-}
-
 __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
@@ -388,8 +381,6 @@ cudaError_t prefill_configure() {
   return e;
 }
 
-namespace {
-
 int encode_rows(CUtensorMap* map, const void* x, int64_t ldx, int rows, int k, int box_rows) {
   EncodeTiled encode = encode_fn();
   if (encode == nullptr) return fail_moe(TF_ERR_UNSUPPORTED, "prefill: the driver does not export cuTensorMapEncodeTiled");
@@ -402,8 +393,6 @@ int encode_rows(CUtensorMap* map, const void* x, int64_t ldx, int rows, int k, i
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? TF_OK : fail_moe(TF_ERR_ARG, "prefill: cuTensorMapEncodeTiled refused the input tensor");
 }
-
-}  // namespace
 
 }  // namespace tf
 

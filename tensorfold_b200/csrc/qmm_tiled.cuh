@@ -20,6 +20,7 @@
 #pragma once
 
 #include <cooperative_groups.h>
+#include <cuda.h>
 
 #include "tf_layout.h"
 #include "tf_ptx.cuh"
@@ -87,7 +88,9 @@ __device__ __forceinline__ float relu2_f(float v) {
   return u * u;
 }
 
-constexpr int XROW_BYTES = 272;            // 128 inputs of bf16 + 16 bytes so ldmatrix rows fall in distinct banks
+// A stage's rows of x: two half tiles of 64 inputs (128 bytes a row) in the 128-byte swizzle pattern (16-byte chunk c of
+// row r sits at chunk c ^ (r & 7)): what a tensor-map copy writes, and conflict-free for ldmatrix.
+constexpr int XHALF_ROW = 128;
 constexpr int RED_STRIDE = 132;            // floats per row of the output staging tile (conflict-free fragment stores)
 
 #ifndef TF_BUDGET1_KB
@@ -110,35 +113,47 @@ struct QmmGeo {
   static constexpr int WPL = words_per_lane(BITS, GS);
   static constexpr int UNITW = unit_words(BITS, GS);
   static constexpr int W_BYTES = G * UNITW * 4;             // one lane's weights of a stage
-  static constexpr int X_BYTES = ROWS * XROW_BYTES;
+  static constexpr int XHALF = ROWS * XHALF_ROW;           // bytes of a half tile (64 inputs of every row)
+  static constexpr int X_BYTES = 2 * XHALF;
   static constexpr int XS_BYTES = ROWS * G * 4;
-  static constexpr int X_OFF = KW * W_BYTES;
-  static constexpr int XS_OFF = X_OFF + X_BYTES;
-  static constexpr int STAGE = XS_OFF + XS_BYTES;
+  static constexpr int X_OFF = 0;                          // first: a stage starts 1024-byte aligned, as the swizzle needs
+  static constexpr int W_OFF = X_BYTES;
+  static constexpr int XS_OFF = W_OFF + KW * W_BYTES;
+  static constexpr int STAGE = (XS_OFF + XS_BYTES + 1023) / 1024 * 1024;
   static constexpr int RED_BYTES = KW * ROWS * RED_STRIDE * 4;
   static constexpr int BUDGET = (MT > 2 ? 110 : KW == 1 ? TF_BUDGET1_KB : KW == 2 ? TF_BUDGET2_KB : TF_BUDGET4_KB) * 1024;
   static constexpr int NST_A = BUDGET / STAGE, NST_B = (RED_BYTES + STAGE - 1) / STAGE;
   static constexpr int NST_C = NST_A < 2 ? 2 : (NST_A > 12 ? 12 : NST_A);
   static constexpr int NST = NST_C < NST_B ? NST_B : NST_C;
   static constexpr int BAR_BYTES = 3 * NST * 8 + 16;
-  static constexpr int SMEM = NST * STAGE + BAR_BYTES;
+  static constexpr int SMEM = NST * STAGE + BAR_BYTES + 1024;     // + slack to align the first stage
   // blocks per SM the register file should allow (64 registers a thread is the floor the kernel needs)
-  static constexpr int BY_SMEM = (227 * 1024) / (SMEM + 1024), BY_REGS = 65536 / (THREADS * 64);
+  static constexpr int BY_SMEM = (227 * 1024) / (SMEM + 1024), BY_REGS = 65536 / (THREADS * (MT == 2 ? 80 : 64));
   static constexpr int MINB = MT > 2 ? 1 : (BY_SMEM < BY_REGS ? BY_SMEM : BY_REGS) < 1 ? 1 : (BY_SMEM < BY_REGS ? BY_SMEM : BY_REGS);
-  static_assert(STAGE % 16 == 0 && W_BYTES % 16 == 0 && X_BYTES % 16 == 0, "stage parts stay 16-byte aligned");
+  static_assert(STAGE % 1024 == 0 && W_BYTES % 16 == 0 && XS_OFF % 16 == 0, "stage parts stay aligned");
   static_assert(NST * STAGE >= RED_BYTES, "the output staging tile reuses the stage memory");
   static_assert(SMEM <= 227 * 1024, "fits the shared memory of an SM");
 };
 
+// Shared-memory address of the ldmatrix.x4 that fetches inputs [k0, k0 + 32) (k0 a multiple of 32, relative to the stage)
+// of the m8 tile `mt`: lane l addresses row l & 7 of matrix l >> 3 (8 inputs each).  xrow = byte offset of the lane's row
+// in a half tile, sw0 / sw1 = the lane's swizzled chunk offsets for chunk bases 0 and 4.
+template <int XHALF>
+__device__ __forceinline__ uint32_t x_ldm_addr(uint32_t xbase, uint32_t xrow, uint32_t sw0, uint32_t sw1, int mt, int k0) {
+  const int chunk = k0 >> 3;                                // 16-byte chunk of the row where the 32 inputs start: 0, 4, 8 or 12
+  return xbase + (chunk >> 3) * XHALF + mt * 8 * XHALF_ROW + xrow + ((chunk & 4) ? sw1 : sw0);
+}
+
 // Group sums of one m8 tile by MMA against a tile of ones: d[0], d[1] = sums of rows 2t and 2t + 1 of the tile.
-template <int GS>
-__device__ __forceinline__ void ones_mma_group(float (&d)[4], uint32_t xaddr_lane) {
+template <int GS, int XHALF>
+__device__ __forceinline__ void ones_mma_group(float (&d)[4], uint32_t xbase, uint32_t xrow, uint32_t sw0, uint32_t sw1, int mt,
+                                               int k0) {
   const uint32_t ones[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};
   d[0] = d[1] = d[2] = d[3] = 0.f;
 #pragma unroll
   for (int s = 0; s < GS / 16; s += 2) {
     uint32_t b[4];
-    ldmatrix_x4(b, xaddr_lane + s * 32);
+    ldmatrix_x4(b, x_ldm_addr<XHALF>(xbase, xrow, sw0, sw1, mt, k0 + 16 * s));
     mma_bf16(d, ones, b[0], b[1]);
     mma_bf16(d, ones, b[2], b[3]);
   }
@@ -146,13 +161,14 @@ __device__ __forceinline__ void ones_mma_group(float (&d)[4], uint32_t xaddr_lan
 
 template <int BITS, int GS, int MT, int KW>
 __global__ void __launch_bounds__(QmmGeo<BITS, GS, MT, KW>::THREADS, QmmGeo<BITS, GS, MT, KW>::MINB)
-qmm_tiled_kernel(const QmmParams p) {
+qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
   using Geo = QmmGeo<BITS, GS, MT, KW>;
   constexpr int S = Geo::S, G = Geo::G, ROWS = Geo::ROWS, WPL = Geo::WPL, UNITW = Geo::UNITW, NST = Geo::NST;
   constexpr int CONSUMERS = Geo::CONSUMERS, THREADS = Geo::THREADS;
   constexpr bool SPLIT = Fmt<BITS>::SPLIT;
 
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + NST * Geo::STAGE);   // weights and x of a stage have landed
   uint64_t* empty = full + NST;                                           // every consumer warp is done with a stage
   uint64_t* sums = empty + NST;                                           // the stage's group sums are written
@@ -238,17 +254,29 @@ qmm_tiled_kernel(const QmmParams p) {
         const int ng = groups_of(st);
         mbar_expect_tx(full + slot, lanes_here * ng * UNITW * 4);
         for (int kw = 0; kw < lanes_here; ++kw)
-          bulk_load(stage_ptr(slot) + kw * Geo::W_BYTES, wbase + kw * p.sb_stride + static_cast<int64_t>(st) * G * UNITW,
+          bulk_load(stage_ptr(slot) + Geo::W_OFF + kw * Geo::W_BYTES, wbase + kw * p.sb_stride + static_cast<int64_t>(st) * G * UNITW,
                     ng * UNITW * 4, full + slot);
       }
     };
     auto issue_x = [&](int st, int slot) {
-      const int cpr = groups_of(st) * GS / 8;               // 16-byte chunks a row
-      const __nv_bfloat16* src = p.x + static_cast<int64_t>(g_first + st * G) * GS;
+      const int kext = groups_of(st) * GS;                  // inputs of this stage (at most 128)
       uint8_t* dst = stage_ptr(slot) + Geo::X_OFF;
-      for (int c = lane; c < rows_here * cpr; c += 32) {
-        const int r = c / cpr, q = c - r * cpr;
-        cp_async16(dst + r * XROW_BYTES + q * 16, src + row_of(r) * p.ldx + q * 8);
+      if (!grouped) {
+        // one tensor-map copy per 64 inputs: a [64 x ROWS] box lands in the swizzled half tile; rows past M read zero
+        if (lane == 0) {
+          const int boxes = (kext + 63) / 64;
+          mbar_expect_tx_only(full + slot, boxes * Geo::XHALF);
+          const int k0 = (g_first + st * G) * GS;
+          for (int b = 0; b < boxes; ++b) tma_load_2d(dst + b * Geo::XHALF, &tmx, k0 + 64 * b, m0, full + slot);
+        }
+      } else {
+        // gathered rows: 16-byte copies placed in the same swizzle pattern
+        const int cpr = kext / 8;                           // 16-byte chunks a row
+        const __nv_bfloat16* src = p.x + static_cast<int64_t>(g_first + st * G) * GS;
+        for (int c = lane; c < rows_here * cpr; c += 32) {
+          const int r = c / cpr, q = c - r * cpr;
+          cp_async16(dst + (q >> 3) * Geo::XHALF + r * XHALF_ROW + (((q & 7) ^ (r & 7)) << 4), src + row_of(r) * p.ldx + q * 8);
+        }
       }
       cp_async_arrive(full + slot);
     };
@@ -292,14 +320,15 @@ qmm_tiled_kernel(const QmmParams p) {
           xs_s[u * ROWS + r] = r < rows_here ? p.xs[row_of(r) * p.KG + g0 + u] : 0.f;
         }
       } else {
-        const uint32_t xs0 = smem_addr(stage_ptr(slot) + Geo::X_OFF) + (lane & 7) * XROW_BYTES + (lane >> 3) * 16;
+        const uint32_t xbase = smem_addr(stage_ptr(slot) + Geo::X_OFF), xrow = (lane & 7) * XHALF_ROW;
+        const uint32_t sw0 = (((lane >> 3) ^ (lane & 7)) << 4), sw1 = (((4 | (lane >> 3)) ^ (lane & 7)) << 4);
 #pragma unroll
         for (int u = 0; u < G; ++u) {
           if (u >= ng) break;
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             float d[4];
-            ones_mma_group<GS>(d, xs0 + mt * 8 * XROW_BYTES + u * GS * 2);
+            ones_mma_group<GS, Geo::XHALF>(d, xbase, xrow, sw0, sw1, mt, u * GS);
             if (lane < 4) *reinterpret_cast<float2*>(xs_s + u * ROWS + mt * 8 + 2 * lane) = make_float2(d[0], d[1]);
           }
         }
@@ -328,8 +357,9 @@ qmm_tiled_kernel(const QmmParams p) {
       }
       const int ng = groups_of(st);
       const uint8_t* sp = stage_ptr(slot);
-      const uint32_t* wst = reinterpret_cast<const uint32_t*>(sp + kw * Geo::W_BYTES);
-      const uint32_t xaddr = smem_addr(sp + Geo::X_OFF) + (lane & 7) * XROW_BYTES + (lane >> 3) * 16;
+      const uint32_t* wst = reinterpret_cast<const uint32_t*>(sp + Geo::W_OFF + kw * Geo::W_BYTES);
+      const uint32_t xbase = smem_addr(sp + Geo::X_OFF), xrow = (lane & 7) * XHALF_ROW;
+      const uint32_t sw0 = (((lane >> 3) ^ (lane & 7)) << 4), sw1 = (((4 | (lane >> 3)) ^ (lane & 7)) << 4);
       const float* xs_s = reinterpret_cast<const float*>(sp + Geo::XS_OFF);
 #pragma unroll
       for (int u = 0; u < G; ++u) {
@@ -365,7 +395,8 @@ qmm_tiled_kernel(const QmmParams p) {
         for (int s = 0; s < S; ++s) {
           if ((s & 1) == 0) {
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(bf[mt], xaddr + mt * 8 * XROW_BYTES + u * GS * 2 + s * 32);
+            for (int mt = 0; mt < MT; ++mt)
+              ldmatrix_x4(bf[mt], x_ldm_addr<Geo::XHALF>(xbase, xrow, sw0, sw1, mt, u * GS + 16 * s));
           }
 #pragma unroll
           for (int h = 0; h < 2; ++h) {

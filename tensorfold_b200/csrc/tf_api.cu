@@ -45,6 +45,7 @@ std::mutex g_init_mutex;
 }  // namespace
 
 cudaError_t prefill_configure();      // qmm_prefill.cu
+int encode_rows(CUtensorMap* map, const void* x, int64_t ldx, int rows, int k, int box_rows);
 
 int* device_error_word() {
   int dev = -1;
@@ -225,14 +226,19 @@ __global__ void sum_ranks_kernel(const void* __restrict__ parts, int world, int6
 
 namespace {
 
+// The dense form fetches the rows of x with tensor-map copies ([64 inputs x row tile] boxes, 128-byte swizzle); the map
+// is built per call on the host and travels as a kernel parameter.  The grouped form gathers rows itself (map unused).
 cudaError_t launch_bits(const QmmParams& p, int bits, int gs, int mt, int kw, cudaStream_t s, bool pdl) {
+  CUtensorMap tmx = {};
+  // (a single row has no stride to speak of: give the map a legal one)
+  if (p.items == nullptr && encode_rows(&tmx, p.x, p.M == 1 ? p.K : p.ldx, p.M, p.K, 8 * mt) != TF_OK) return cudaErrorInvalidValue;
   switch (bits) {
-    case 2: return qmm_launch_b2(p, gs, mt, kw, s, pdl);
-    case 3: return qmm_launch_b3(p, gs, mt, kw, s, pdl);
-    case 4: return qmm_launch_b4(p, gs, mt, kw, s, pdl);
-    case 5: return qmm_launch_b5(p, gs, mt, kw, s, pdl);
-    case 6: return qmm_launch_b6(p, gs, mt, kw, s, pdl);
-    default: return qmm_launch_b8(p, gs, mt, kw, s, pdl);
+    case 2: return qmm_launch_b2(tmx, p, gs, mt, kw, s, pdl);
+    case 3: return qmm_launch_b3(tmx, p, gs, mt, kw, s, pdl);
+    case 4: return qmm_launch_b4(tmx, p, gs, mt, kw, s, pdl);
+    case 5: return qmm_launch_b5(tmx, p, gs, mt, kw, s, pdl);
+    case 6: return qmm_launch_b6(tmx, p, gs, mt, kw, s, pdl);
+    default: return qmm_launch_b8(tmx, p, gs, mt, kw, s, pdl);
   }
 }
 
