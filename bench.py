@@ -624,9 +624,9 @@ def run_case(args) -> None:
         qs.append(qmm.pack(w[0].to(dev), w[1].to(dev), w[2].to(dev), GS))
     x = synthetic.activations(args.rows, k, 0).to(dev)
     for i in range(6):
-        y = qmm.matmul(x, qs[i % 3])
+        y = qmm.prefill_matmul(x, qs[i % 3]) if args.prefill else qmm.matmul(x, qs[i % 3])
     torch.cuda.synchronize()
-    print(json.dumps({"case": args.case, "rows": args.rows, "launches": 6, "max_abs": float(y.float().abs().max())}))
+    print(json.dumps({"case": args.case, "rows": args.rows, "prefill": args.prefill, "launches": 6, "max_abs": float(y.float().abs().max())}))
 
 
 def main() -> None:
@@ -638,6 +638,7 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--case", default="", help="profiler case: run six launches of one projection (e.g. gate_proj) and exit")
+    ap.add_argument("--prefill", action="store_true", help="with --case: the prefill arithmetic (tcgen05 kernel)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE layer / row-count sweeps reported beside the headline")
     ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")

@@ -144,6 +144,12 @@ int tf_moe_experts_prefill(const void* x, int64_t ldx, int slots, const void* ti
                            void* sorted, void* out, int64_t ldo, int out_f32, int epi, float limit, void* stream);
 /* logits[r, e] = fp32 dot of bf16 rows x[r] and w[e].  Replaces the Triton `_router` of cuda/moe.py:23-55. */
 int tf_moe_router(const void* x, int64_t ldx, int rows, int d, const void* w, int ne, float* out, int64_t ldo, void* stream);
+/* The same logits in the prefill arithmetic: (16 rows x 16 experts) tensor-core tiles, K in order, fp32 accumulate.  A
+ * row's bits do not depend on the row count, but they are not tf_moe_router's: a model keeps one form for its prompt
+ * passes.  d a multiple of 16; x rows and w 4-byte aligned.  Replaces the same Triton `_router` (cuda/moe.py:23-55,
+ * whose tl.dot tiles are this form). */
+int tf_moe_router_tiles(const void* x, int64_t ldx, int rows, int d, const void* w, int ne, float* out, int64_t ldo,
+                        void* stream);
 /* Per row: top `topk` experts by fp32 logit (ties to the lower id), weights bf16(exp(l_k - l_0) / sum); with `shared`
  * one more slot, expert id `experts`, weight bf16(sigmoid(bf16(logit[experts]))).  pick, wts: [rows, topk + shared].
  * Replaces the Triton `_topk_rows` of cuda/moe.py:58-85. */

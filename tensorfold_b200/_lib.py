@@ -39,6 +39,7 @@ SIGNATURES = {
     "tf_moe_experts_prefill": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i32,
                                       _i32, ctypes.c_float, _vp)),
     "tf_moe_router": (_i32, (_vp, _i64, _i32, _i32, _vp, _i32, _vp, _i64, _vp)),
+    "tf_moe_router_tiles": (_i32, (_vp, _i64, _i32, _i32, _vp, _i32, _vp, _i64, _vp)),
     "tf_moe_topk": (_i32, (_vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp)),
     "tf_moe_combine": (_i32, (_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp)),
     "tf_affine_rows": (_i32, (_vp, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp)),

@@ -161,6 +161,48 @@ __global__ void router_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, 
   if (lane == 0) out[r * ldo + e] = acc;
 }
 
+__device__ __forceinline__ void router_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The same logits in the prefill arithmetic: one warp per (16 rows, 16 experts) tile walks K in 16-input steps in order
+// (m16n8k16, fp32 accumulate), operands straight from global memory (the block's four warps share the 16 rows through
+// L1).  A row's logits depend on that row alone, whatever the row count; they are this kernel's bits, not the one-warp
+// kernel's, so a caller picks one form per model and keeps it.
+__global__ void __launch_bounds__(128) router_tiles_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int rows, int d,
+                                                           const __nv_bfloat16* __restrict__ w, int ne,
+                                                           float* __restrict__ out, int64_t ldo) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int e0 = (blockIdx.x * 4 + warp) * 16, r0 = blockIdx.y * 16;
+  if (e0 >= ne) return;
+  const int ra = min(r0 + g, rows - 1), rb = min(r0 + g + 8, rows - 1);
+  const uint32_t* xa = reinterpret_cast<const uint32_t*>(x + ra * ldx);
+  const uint32_t* xb = reinterpret_cast<const uint32_t*>(x + rb * ldx);
+  const uint32_t* w0 = reinterpret_cast<const uint32_t*>(w + static_cast<int64_t>(min(e0 + g, ne - 1)) * d);
+  const uint32_t* w1 = reinterpret_cast<const uint32_t*>(w + static_cast<int64_t>(min(e0 + 8 + g, ne - 1)) * d);
+  float acc[2][4] = {};
+#pragma unroll 4
+  for (int k = 0; k < d / 16; ++k) {
+    const int o = k * 8 + t;
+    const uint32_t a0 = xa[o], a1 = xb[o], a2 = xa[o + 4], a3 = xb[o + 4];
+    router_mma(acc[0], a0, a1, a2, a3, w0[o], w0[o + 4]);
+    router_mma(acc[1], a0, a1, a2, a3, w1[o], w1[o + 4]);
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int c = e0 + 8 * j + 2 * t;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = r0 + g + 8 * h;
+      if (r < rows && c < ne) out[r * ldo + c] = acc[j][2 * h];
+      if (r < rows && c + 1 < ne) out[r * ldo + c + 1] = acc[j][2 * h + 1];
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // top-k: one warp per row
 // ---------------------------------------------------------------------------------------------------------------------
@@ -327,6 +369,20 @@ int tf_moe_router(const void* x, int64_t ldx, int rows, int d, const void* w, in
                                                                      static_cast<const __nv_bfloat16*>(w), ne, out, ldo);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_router");
+}
+
+int tf_moe_router_tiles(const void* x, int64_t ldx, int rows, int d, const void* w, int ne, float* out, int64_t ldo,
+                        void* stream) {
+  if (rows < 1 || d < 16 || ne < 1 || !x || !w || !out || ldx < d || ldo < ne)
+    return fail_moe(TF_ERR_ARG, "tf_moe_router_tiles: bad arguments");
+  if (d % 16 || ldx % 2 || reinterpret_cast<uintptr_t>(x) % 4 || reinterpret_cast<uintptr_t>(w) % 4)
+    return fail_moe(TF_ERR_ARG, "tf_moe_router_tiles: d must be a multiple of 16, rows of x and w 4-byte aligned");
+  if (rows > 65535 * 16) return fail_moe(TF_ERR_ARG, "tf_moe_router_tiles: too many rows");
+  dim3 grid((ne + 63) / 64, (rows + 15) / 16);
+  router_tiles_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x), ldx, rows, d,
+                                                                           static_cast<const __nv_bfloat16*>(w), ne, out, ldo);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_router_tiles");
 }
 
 int tf_moe_topk(const float* logits, int64_t ldl, int rows, int experts, int topk, int shared, int* pick, float* wts,

@@ -222,8 +222,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     }
   } else {
     // ------------------------------------------------------------------ conversion: packed codes -> swizzled bf16 A tile
-    const int dw = warp - 2, tp = dw & 3, h = dw >> 2, g = lane >> 2, t = lane & 3;
+    // A warp owns 16 output columns (tile pair tp, half h) of every stage.  Per 16-input step a thread holds the four
+    // m8n8 fragments (two column octets x two input octets) of its lane's codes, so one stmatrix.x4 writes four 8 x 16-byte
+    // row segments of the swizzled tile; lane l supplies the address of row l % 8 of fragment l / 8.
+    const int dw = warp - 2, tp = dw & 3, h = dw >> 2, g = lane >> 2;
     const __nv_bfloat162 k128 = __floats2bfloat162_rn(128.f, 128.f);
+    uint32_t row_off[4];                                        // this lane's row segment of each 16-input step of a stage
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      row_off[q] = (32 * tp + 16 * h + 8 * ((lane >> 3) & 1) + (lane & 7)) * 128 + (((2 * q + (lane >> 4)) ^ (lane & 7)) << 4);
     bool ok = true;
     for (int i = 0; i < nstages && ok; ++i) {
       const int s = i % PF_NST;
@@ -235,52 +242,47 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         break;
       }
       const uint32_t* wst = reinterpret_cast<const uint32_t*>(w_stage(s));
-      uint8_t* at = a_tile(s);
+      const uint32_t at = smem_addr(a_tile(s));
       const int units_here = min(UNITS, total_units - i * UNITS);
 #pragma unroll
       for (int u = 0; u < UNITS; ++u) {
-        if (u >= units_here) {
-          // K ends inside this stage: x is zero there (the tensor map fills it), the weights must be finite, so zero
-          const int c0z = 32 * tp + 16 * h + g;
-#pragma unroll
-          for (int sidx = 0; sidx < S; ++sidx)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int c = c0z + 8 * (j & 1), k = u * GS + 16 * sidx + 2 * t + 8 * (j >> 1);
-              *reinterpret_cast<uint32_t*>(at + c * 128 + (((k >> 3) ^ (c & 7)) << 4) + (k & 7) * 2) = 0u;
-            }
-          continue;
-        }
-        const uint32_t* unit = wst + u * UNITW;
-        uint32_t wd[S];
-        if constexpr (S == 4) {
-          const uint4 v = *reinterpret_cast<const uint4*>(unit + (tp * 32 + lane) * WPL + h * S);
-          wd[0] = v.x, wd[1] = v.y, wd[2] = v.z, wd[3] = v.w;
-        } else {
-          const uint2 v = *reinterpret_cast<const uint2*>(unit + (tp * 32 + lane) * WPL + h * S);
-          wd[0] = v.x, wd[1] = v.y;
-        }
-        const uint2 sbw = *reinterpret_cast<const uint2*>(unit + TILE_PAIRS * 32 * WPL + tp * 32 + g * 4 + h * 2);
-        const uint32_t sbv[2] = {sbw.x, sbw.y};                  // columns c0 and c0 + 8
+        uint32_t wd[S] = {};
         __nv_bfloat162 sc[2], bi[2];
+        sc[0] = sc[1] = bi[0] = bi[1] = __floats2bfloat162_rn(0.f, 0.f);
+        // past the end of K (it ends inside this stage) x is zero (the tensor map fills it) and the weights must be
+        // finite: codes, scales and biases of zero give zero weights
+        if (u < units_here) {
+          const uint32_t* unit = wst + u * UNITW;
+          if constexpr (S == 4) {
+            const uint4 v = *reinterpret_cast<const uint4*>(unit + (tp * 32 + lane) * WPL + h * S);
+            wd[0] = v.x, wd[1] = v.y, wd[2] = v.z, wd[3] = v.w;
+          } else {
+            const uint2 v = *reinterpret_cast<const uint2*>(unit + (tp * 32 + lane) * WPL + h * S);
+            wd[0] = v.x, wd[1] = v.y;
+          }
+          const uint2 sbw = *reinterpret_cast<const uint2*>(unit + TILE_PAIRS * 32 * WPL + tp * 32 + g * 4 + h * 2);
+          const uint32_t sbv[2] = {sbw.x, sbw.y};                  // columns c0 and c0 + 8
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const __nv_bfloat16 sv = __ushort_as_bfloat16(static_cast<unsigned short>(sbv[r] & 0xFFFFu));
-          const __nv_bfloat16 bv = __ushort_as_bfloat16(static_cast<unsigned short>(sbv[r] >> 16));
-          sc[r] = __halves2bfloat162(sv, sv);
-          bi[r] = __halves2bfloat162(bv, bv);
+          for (int r = 0; r < 2; ++r) {
+            const uint32_t s2 = __byte_perm(sbv[r], 0u, 0x1010), b2 = __byte_perm(sbv[r], 0u, 0x3232);
+            sc[r] = *reinterpret_cast<const __nv_bfloat162*>(&s2);
+            bi[r] = *reinterpret_cast<const __nv_bfloat162*>(&b2);
+          }
         }
-        const int c0 = 32 * tp + 16 * h + g;
 #pragma unroll
-        for (int sidx = 0; sidx < S; ++sidx)
+        for (int sidx = 0; sidx < S; ++sidx) {
+          uint32_t frag[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint32_t v = ((wd[sidx] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
             const __nv_bfloat162 q2 = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), k128);       // exact code
             const __nv_bfloat162 w2 = __hfma2(q2, sc[j & 1], bi[j & 1]);                            // one rounding
-            const int c = c0 + 8 * (j & 1), k = u * GS + 16 * sidx + 2 * t + 8 * (j >> 1);
-            *reinterpret_cast<__nv_bfloat162*>(at + c * 128 + (((k >> 3) ^ (c & 7)) << 4) + (k & 7) * 2) = w2;
+            frag[j] = *reinterpret_cast<const uint32_t*>(&w2);
           }
+          asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(at + row_off[u * S + sidx]),
+                       "r"(frag[0]), "r"(frag[1]), "r"(frag[2]), "r"(frag[3])
+                       : "memory");
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core's reads
       __syncwarp();

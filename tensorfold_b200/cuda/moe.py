@@ -12,8 +12,9 @@ from . import experts as grouped
 from .kernels import qmm
 
 
-def router(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """x [R, D] bf16, rows [E + 1, D] bf16 (router rows, then the shared expert's gate row) -> [R, E + 1] fp32."""
+def router(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = None, *, prefill: bool = False) -> torch.Tensor:
+    """x [R, D] bf16, rows [E + 1, D] bf16 (router rows, then the shared expert's gate row) -> [R, E + 1] fp32.
+    ``prefill`` takes the tensor-core tiles (other bits than the decode form; each form is stable over row counts)."""
 
     if x.dtype != torch.bfloat16 or rows.dtype != torch.bfloat16 or x.dim() != 2 or rows.dim() != 2 or x.shape[1] != rows.shape[1]:
         raise ValueError("router: x [R, D] and rows [E + 1, D] must be bf16 with the same D")
@@ -25,8 +26,8 @@ def router(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = None)
     if out is None:
         out = torch.empty((m, ne), dtype=torch.float32, device=x.device)
     stream = _lib.stream_of(x)
-    _lib.check(_lib.lib().tf_moe_router(x.data_ptr(), x.stride(0), m, d, rows.data_ptr(), ne, out.data_ptr(), out.stride(0),
-                                        stream), "router")
+    fn = _lib.lib().tf_moe_router_tiles if prefill else _lib.lib().tf_moe_router
+    _lib.check(fn(x.data_ptr(), x.stride(0), m, d, rows.data_ptr(), ne, out.data_ptr(), out.stride(0), stream), "router")
     return out
 
 
@@ -80,7 +81,7 @@ def moe(x: torch.Tensor, router_rows: torch.Tensor, ex: grouped.Experts, buf: Mo
     """Route x [R, D] and run its experts into buf.y [R, k + 1, D] (bf16 in prefill); slot k is the shared expert."""
 
     rows = x.shape[0]
-    router(x, router_rows, buf.logits[:rows])
+    router(x, router_rows, buf.logits[:rows], prefill=buf.plan.prefill)
     select(buf.logits[:rows], buf, top_k, experts)
     grouped.gate_up(x, ex, buf.plan, buf.act.view(-1, ex.width), rows)
     grouped.down(buf.act.view(-1, ex.width), ex, buf.plan, buf.y.view(-1, ex.dims), rows)

@@ -34,6 +34,10 @@ def test_router_and_topk_match_the_oracle():
     ref = omoe.router_logits(x.float().numpy(), wr.float().numpy())
     assert np.abs(logits.cpu().numpy() - ref).max() <= 1e-4 * np.abs(ref).max()
     assert torch.equal(moe.router(x[5:6].to(DEV), wr.to(DEV)), logits[5:6])             # a row alone: same bits
+    tiles = moe.router(x.to(DEV), wr.to(DEV), prefill=True)                              # tensor-core tiles: its own bits,
+    assert np.abs(tiles.cpu().numpy() - ref).max() <= 1e-4 * np.abs(ref).max()          # ragged rows (33) and experts (129)
+    assert torch.equal(moe.router(x[17:18].to(DEV), wr.to(DEV), prefill=True), tiles[17:18])
+    assert torch.equal(moe.router(x[:32].to(DEV), wr[:16].to(DEV), prefill=True), tiles[:32, :16])
 
     class Cfg:
         num_experts_per_tok, num_experts, moe_intermediate_size, hidden_size = k, e, 64, 64
