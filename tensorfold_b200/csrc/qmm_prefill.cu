@@ -6,10 +6,14 @@
 // kernel's bits (that one keeps the affine terms in fp32).
 //
 // Block tile = 128 output columns x 256 rows of x, "swap-AB": the dequantised weights are the MMA's A operand (M = 128),
-// the rows of x its B operand (N = 256), so every dequantised weight feeds 256 rows and the conversion (CUDA cores)
-// keeps pace with the tensor pipe.  Roles: warp 0 loads (a 2-D tensor-map copy of the x tile with the 128-byte swizzle
-// and a bulk copy of the packed units, per 64-input stage), warp 1 owns tensor memory and issues the MMAs, warps 2-9
-// turn packed codes into the swizzled bf16 A tile and afterwards drain the accumulator to global memory.
+// the rows of x its B operand (N = 256), so every dequantised weight feeds 256 rows.  Two rings decouple the latencies:
+// packed units arrive from HBM (about 2000 cycles away) by bulk copies into a ring of small slots; a stage of the main
+// ring holds the dequantised A tile and the x tile (a 2-D tensor-map copy with the 128-byte swizzle) of 64 inputs
+// behind ONE full barrier and ONE empty barrier, because every barrier operation of the MMA-issuing thread costs about
+// as much as an MMA issue and the tensor pipe idles while that thread does anything else.  Roles: warp 0 loads x,
+// warp 1 owns tensor memory and issues the MMAs, warp 2 loads packed units, warps 4-19 are two groups of eight
+// conversion warps that take alternate stages (a stage's conversion has a long dependent chain, so two stages are
+// always in conversion) and afterwards all sixteen drain the accumulator to global memory.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -32,16 +36,23 @@ constexpr int PF_COLS = 128;       // output columns of a block tile (MMA M)
 constexpr int PF_STAGE_K = 64;     // inputs a stage
 constexpr int PF_A_BYTES = PF_COLS * 128;
 constexpr int PF_W_BYTES = 5120;   // packed units of a stage: one g64 unit (4608 B) or two g32 units (5120 B)
-constexpr int PF_NST = 4;
-constexpr int PF_THREADS = 320;    // 10 warps
+constexpr int PF_NW = 6;           // packed-unit slots in flight
+constexpr int PF_THREADS = 640;    // 20 warps: x loads, MMA, unit loads, (idle), 2 x 8 conversion
+constexpr int PF_CONV0 = 4;        // first conversion warp (a multiple of 4: tensor-memory lane groups go by warp % 4)
+constexpr int PF_BAR_BYTES = 512;
 
 // ROWS = rows of x of a block tile (MMA N): 256 for dense prompts, 128 for the grouped expert form
 template <int ROWS>
 struct PfGeo {
   static constexpr int B_BYTES = ROWS * 128;
-  static constexpr int STAGE = PF_A_BYTES + B_BYTES + PF_W_BYTES;
-  static constexpr int SMEM = PF_NST * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int STAGE = PF_A_BYTES + B_BYTES;
+  static constexpr int NS = ROWS == 256 ? 4 : 6;           // stages in flight (even: the conversion groups alternate)
+  static constexpr int W_OFF = NS * STAGE, BAR_OFF = W_OFF + PF_NW * PF_W_BYTES;
+  static constexpr int SMEM = BAR_OFF + PF_BAR_BYTES + 1024 /* alignment slack */;
   static_assert(STAGE % 1024 == 0, "tiles stay 1024-byte aligned for the 128-byte swizzle");
+  static_assert((2 * NS + 2 * PF_NW + 1) * 8 + 16 <= PF_BAR_BYTES, "barriers fit");
+  static_assert(NS % 2 == 0, "conversion groups alternate stages");
+  static_assert(SMEM <= 232448, "fits the opt-in shared memory of a block");
 };
 
 struct PrefillParams {
@@ -80,15 +91,23 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// The whole warp runs these with warp-uniform operands (so the descriptors can live in uniform registers); the
+// instruction itself is predicated on `leader`, true in exactly one lane.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                                          uint32_t leader) {
   asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      "{\n.reg .pred p, q;\nsetp.ne.b32 p, %4, 0;\nsetp.ne.b32 q, %5, 0;\n"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
       : "memory");
 }
 
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+__device__ __forceinline__ void umma_commit(uint64_t* bar, uint32_t leader) {
+  asm volatile(
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %1, 0;\n"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}" ::"r"(smem_addr(bar)),
+      "r"(leader)
+      : "memory");
 }
 
 __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -104,26 +123,35 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+#ifdef PF_TRACE
+// debugging aid (compiled out by default): block (0, 0)'s clock at each stage's events
+__device__ long long g_pf_trace[8 * 512];
+#define PF_MARK(ev, i) \
+  do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (i) < 512) g_pf_trace[(ev) * 512 + (i)] = clock64(); } while (0)
+#else
+#define PF_MARK(ev, i) do { } while (0)
+#endif
+
 template <int GS, int ROWS>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmx, const PrefillParams p) {
   using Geo = PfGeo<ROWS>;
-  constexpr int PF_ROWS = ROWS, PF_B_BYTES = Geo::B_BYTES, PF_STAGE = Geo::STAGE;
+  constexpr int PF_ROWS = ROWS, PF_B_BYTES = Geo::B_BYTES, NS = Geo::NS;
   constexpr uint32_t PF_TMEM_COLS = ROWS;
   constexpr int S = GS / 16;                                 // k16 steps a group
   constexpr int UNITS = PF_STAGE_K / GS;                     // units a stage (1 for g64, 2 for g32)
   constexpr int WPL = words_per_lane(4, GS);
   constexpr int UNITW = unit_words(4, GS);
-  static_assert(UNITS * UNITW * 4 <= PF_W_BYTES, "stage holds its packed units");
+  static_assert(UNITS * UNITW * 4 <= PF_W_BYTES, "slot holds a stage's packed units");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PF_NST * PF_STAGE);
-  uint64_t* b_full = bars;                    // x tile landed (tensor-map copy)
-  uint64_t* w_full = bars + PF_NST;           // packed units landed (bulk copy)
-  uint64_t* a_full = bars + 2 * PF_NST;       // A tile written by the 8 conversion warps
-  uint64_t* empty = bars + 3 * PF_NST;        // the MMAs that read the stage are done
-  uint64_t* acc_full = bars + 4 * PF_NST;     // every MMA of the tile is done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * PF_NST + 1);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Geo::BAR_OFF);
+  uint64_t* full = bars;                            // stage ready: 8 conversion warps arrived and the x tile landed
+  uint64_t* empty = full + NS;                      // the MMAs that read the stage are done
+  uint64_t* w_full = empty + NS;                    // packed units landed (bulk copy)
+  uint64_t* w_empty = w_full + PF_NW;               // the 8 conversion warps of the stage's group have read the slot
+  uint64_t* acc_full = w_empty + PF_NW;             // every MMA of the tile is done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -144,9 +172,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     rows_here = min(PF_ROWS, p.M - m0);
   }
 
-  auto a_tile = [&](int s) { return smem + s * PF_STAGE; };
-  auto b_tile = [&](int s) { return smem + s * PF_STAGE + PF_A_BYTES; };
-  auto w_stage = [&](int s) { return smem + s * PF_STAGE + PF_A_BYTES + PF_B_BYTES; };
+  auto a_tile = [&](int s) { return smem + s * Geo::STAGE; };
+  auto b_tile = [&](int s) { return smem + s * Geo::STAGE + PF_A_BYTES; };
+  auto w_slot = [&](int s) { return smem + Geo::W_OFF + s * PF_W_BYTES; };
   auto give_up = [&](int code) {
     if (lane == 0) {
       *abort_flag = code;
@@ -155,12 +183,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
   };
 
   if (tid == 0) {
-    for (int i = 0; i < PF_NST; ++i) {
-      mbar_init(b_full + i, 1);
-      mbar_init(w_full + i, 1);
-      mbar_init(a_full + i, 8);
-      mbar_init(empty + i, 1);
-    }
+    for (int i = 0; i < NS; ++i) mbar_init(full + i, 9), mbar_init(empty + i, 1);
+    for (int i = 0; i < PF_NW; ++i) mbar_init(w_full + i, 1), mbar_init(w_empty + i, 8);
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -176,24 +200,46 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ loads
-    const uint32_t* wsb = wroot + static_cast<int64_t>(sb) * p.sb_stride;
+    // ------------------------------------------------------------------ x tiles (L2 -> shared, tensor-map copies)
     bool ok = true;
     for (int i = 0; i < nstages && ok; ++i) {
-      const int s = i % PF_NST;
-      if (i >= PF_NST) {
-        ok = mbar_wait(empty + s, ((i - PF_NST) / PF_NST) & 1, abort_flag);
+      const int s = i % NS;
+      if (i >= NS) {
+        ok = mbar_wait(empty + s, (i / NS - 1) & 1, abort_flag);
         if (!ok) {
           give_up(ERR_WAIT_EMPTY);
           break;
         }
       }
+      PF_MARK(0, i);
+      if (lane == 0) {
+#ifdef PF_DBG_NOX
+        mbar_arrive(full + s);
+#else
+        mbar_expect_tx(full + s, PF_B_BYTES);
+        tma_load_2d(b_tile(s), &tmx, i * PF_STAGE_K, m0, full + s);
+#endif
+      }
+      __syncwarp();
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ packed units (HBM -> shared, bulk copies)
+    const uint32_t* wsb = wroot + static_cast<int64_t>(sb) * p.sb_stride;
+    bool ok = true;
+    for (int i = 0; i < nstages && ok; ++i) {
+      const int s = i % PF_NW;
+      if (i >= PF_NW) {
+        ok = mbar_wait(w_empty + s, (i / PF_NW - 1) & 1, abort_flag);
+        if (!ok) {
+          give_up(ERR_WAIT_EMPTY);
+          break;
+        }
+      }
+      PF_MARK(1, i);
       if (lane == 0) {
         const int units_here = min(UNITS, total_units - i * UNITS);
         mbar_expect_tx(w_full + s, units_here * UNITW * 4);
-        bulk_load(w_stage(s), wsb + static_cast<int64_t>(i) * UNITS * UNITW, units_here * UNITW * 4, w_full + s);
-        mbar_expect_tx(b_full + s, PF_B_BYTES);
-        tma_load_2d(b_tile(s), &tmx, i * PF_STAGE_K, m0, b_full + s);
+        bulk_load(w_slot(s), wsb + static_cast<int64_t>(i) * UNITS * UNITW, units_here * UNITW * 4, w_full + s);
       }
       __syncwarp();
     }
@@ -202,47 +248,49 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_ROWS >> 3) << 17) | ((PF_COLS >> 4) << 24);
     bool ok = true;
     for (int i = 0; i < nstages && ok; ++i) {
-      const int s = i % PF_NST;
-      const uint32_t parity = (i / PF_NST) & 1;
-      ok = mbar_wait(a_full + s, parity, abort_flag) && mbar_wait(b_full + s, parity, abort_flag);
+      const int st = i % NS;
+      ok = mbar_wait_ready(full + st, (i / NS) & 1, abort_flag);
       if (!ok) {
         give_up(ERR_WAIT_FULL);
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (lane == 0) {
-        const uint64_t ad = umma_desc(smem_addr(a_tile(s))), bd = umma_desc(smem_addr(b_tile(s)));
+      PF_MARK(4, i);
+      {
+        const uint32_t leader = lane == 0 ? 1u : 0u;
+#ifndef PF_DBG_NOMMA
+        const uint64_t ad = umma_desc(smem_addr(a_tile(st))), bd = umma_desc(smem_addr(b_tile(st)));
 #pragma unroll
         for (int k = 0; k < PF_STAGE_K / 16; ++k)
-          umma_bf16(tmem_base, ad + 2 * k, bd + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);    // + 32 bytes a k16 step
-        umma_commit(empty + s);
-        if (i == nstages - 1) umma_commit(acc_full);
+          umma_bf16(tmem_base, ad + 2 * k, bd + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u, leader);   // + 32 bytes a k16 step
+#endif
+        PF_MARK(6, i);
+        umma_commit(empty + st, leader);
+        if (i == nstages - 1) umma_commit(acc_full, leader);
       }
+      PF_MARK(5, i);
       __syncwarp();
     }
-  } else {
+  } else if (warp >= PF_CONV0) {
     // ------------------------------------------------------------------ conversion: packed codes -> swizzled bf16 A tile
-    // A warp owns 16 output columns (tile pair tp, half h) of every stage.  Per 16-input step a thread holds the four
-    // m8n8 fragments (two column octets x two input octets) of its lane's codes, so one stmatrix.x4 writes four 8 x 16-byte
-    // row segments of the swizzled tile; lane l supplies the address of row l % 8 of fragment l / 8.
-    const int dw = warp - 2, tp = dw & 3, h = dw >> 2, g = lane >> 2;
+    const int cw = warp - PF_CONV0, group = cw >> 3, dw = cw & 7, tp = dw & 3, h = dw >> 2, g = lane >> 2;
     const __nv_bfloat162 k128 = __floats2bfloat162_rn(128.f, 128.f);
     uint32_t row_off[4];                                        // this lane's row segment of each 16-input step of a stage
 #pragma unroll
     for (int q = 0; q < 4; ++q)
       row_off[q] = (32 * tp + 16 * h + 8 * ((lane >> 3) & 1) + (lane & 7)) * 128 + (((2 * q + (lane >> 4)) ^ (lane & 7)) << 4);
     bool ok = true;
-    for (int i = 0; i < nstages && ok; ++i) {
-      const int s = i % PF_NST;
-      const uint32_t parity = (i / PF_NST) & 1;
-      if (i >= PF_NST) ok = mbar_wait(empty + s, ((i - PF_NST) / PF_NST) & 1, abort_flag);
-      ok = ok && mbar_wait(w_full + s, parity, abort_flag);
+    for (int i = group; i < nstages && ok; i += 2) {
+      const int sw = i % PF_NW, st = i % NS;
+      ok = mbar_wait(w_full + sw, (i / PF_NW) & 1, abort_flag);
+      if (ok && i >= NS) ok = mbar_wait(empty + st, (i / NS - 1) & 1, abort_flag);
       if (!ok) {
         give_up(ERR_WAIT_FULL);
         break;
       }
-      const uint32_t* wst = reinterpret_cast<const uint32_t*>(w_stage(s));
-      const uint32_t at = smem_addr(a_tile(s));
+      if (cw == 0 || cw == 8) PF_MARK(2, i);
+      const uint32_t* wst = reinterpret_cast<const uint32_t*>(w_slot(sw));
+      const uint32_t at = smem_addr(a_tile(st));
       const int units_here = min(UNITS, total_units - i * UNITS);
 #pragma unroll
       for (int u = 0; u < UNITS; ++u) {
@@ -269,6 +317,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             bi[r] = *reinterpret_cast<const __nv_bfloat162*>(&b2);
           }
         }
+#ifndef PF_DBG_NOCONV
 #pragma unroll
         for (int sidx = 0; sidx < S; ++sidx) {
           uint32_t frag[4];
@@ -283,10 +332,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                        "r"(frag[0]), "r"(frag[1]), "r"(frag[2]), "r"(frag[3])
                        : "memory");
         }
+#endif
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core's reads
       __syncwarp();
-      if (lane == 0) mbar_arrive(a_full + s);
+      if (lane == 0) {
+        mbar_arrive(full + st);
+        mbar_arrive(w_empty + sw);                               // the slot's words are in registers or already used
+      }
+      if (cw == 0 || cw == 8) PF_MARK(3, i);
     }
 
     // ------------------------------------------------------------------ epilogue: tensor memory -> global
@@ -294,13 +348,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     if (!done) give_up(ERR_WAIT_FULL);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (done && *abort_flag == 0) {
-      const int lg = warp & 3, half = dw >> 2;                   // this warp may touch TMEM lanes [32 lg, 32 lg + 32)
+      const int lg = warp & 3, part = cw >> 2;                   // this warp may touch TMEM lanes [32 lg, 32 lg + 32)
       const int n = sb * PF_COLS + lg * 32 + lane;               // the weight column this thread's lane holds
-      constexpr int CHUNKS = PF_ROWS / 64;                       // 32-row chunks of this warp's half of the rows
+      constexpr int CHUNKS = PF_ROWS / 128;                      // 32-row chunks of this warp's quarter of the rows
 #pragma unroll 1
       for (int chunk = 0; chunk < CHUNKS; ++chunk) {
         uint32_t r[32];
-        const int col0 = half * (PF_ROWS / 2) + chunk * 32;
+        const int col0 = part * (PF_ROWS / 4) + chunk * 32;
         tmem_load32(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + col0, r);
         if (p.epi == 2) {
           // lanes 0-15 hold gate columns, lanes 16-31 the up columns of the same 16 outputs
@@ -374,6 +428,12 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, int64_
   uint4* d4 = reinterpret_cast<uint4*>(dst + static_cast<int64_t>(pos) * k);
   for (int i = lane; i < k / 8; i += 32) d4[i] = s4[i];
 }
+
+#ifdef PF_TRACE
+extern "C" int tf_debug_pf_trace(long long* host) {
+  return cudaMemcpyFromSymbol(host, g_pf_trace, sizeof(g_pf_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 cudaError_t prefill_configure() {
   cudaError_t e = cudaFuncSetAttribute(prefill_kernel<64, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<256>::SMEM);

@@ -69,6 +69,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   return __all_sync(0xFFFFFFFFu, ok);
 }
 
+// The same for a barrier that is normally complete already: one non-blocking test first (a test is cheaper than a
+// potentially suspending try_wait), the bounded wait only if it fails.
+__device__ __forceinline__ bool mbar_wait_ready(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  if (__all_sync(0xFFFFFFFFu, ok != 0)) return true;
+  return mbar_wait(bar, parity, abort_flag);
+}
+
 // Bounded wait for a lane that already probed once: loops only if `ready` is false; uniform result across the warp.
 __device__ __forceinline__ bool mbar_wait_probed(bool ready, uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
   if (__all_sync(0xFFFFFFFFu, ready)) return true;
