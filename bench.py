@@ -459,8 +459,22 @@ def run_b200(args) -> None:
                      else qmm.default_split(nout[name], kin[name], GS)) for name, _ in shapes}
     reduced = {}
 
+    branches = world == 1 and not args.no_branches
+
     def step(i: int, pdl: bool) -> None:
         layer = layers[i % ring]
+
+        def mm(name: str, p: bool):
+            return lambda: qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=p, sk=splits[name])
+
+        if branches:
+            # the layer's dataflow: q/k/v read the same rows and so do gate/up, so each set runs side by side; o_proj
+            # waits for the first set (attention sits between them in a model), down_proj for the second
+            qmm.fork_join([mm("q_proj", pdl), mm("k_proj", False), mm("v_proj", False)])
+            mm("o_proj", False)()
+            qmm.fork_join([mm("gate_proj", False), mm("up_proj", False)])
+            mm("down_proj", False)()
+            return
         for name, _ in shapes:
             if world > 1 and name not in column:            # row-parallel: bf16 partial, rank-ordered reduction
                 qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=False, sk=splits[name])
@@ -577,7 +591,9 @@ def run_b200(args) -> None:
                        "weight_bytes_per_step": layer_bytes, "ring_layers": ring,
                        "l2": f"steps cycle a ring of {ring} distinct layers ({ring * layer_bytes / world / 1e6:.0f} MB of weights "
                              "a GPU, larger than the 126 MB L2), so no flush is needed",
-                       "launch": "CUDA graph of the timed steps" + (", programmatic dependent launch" if pdl else ""),
+                       "launch": "CUDA graph of the timed steps" + (", programmatic dependent launch" if pdl else "")
+                                 + ("; q/k/v side by side, then o, then gate/up side by side, then down (graph branches)"
+                                    if branches else ""),
                        "parallelism": "single GPU" if world == 1 else
                        f"tp{world}: q/k/v/gate/up column-parallel, o/down row-parallel with a rank-ordered bf16 reduction",
                        "k_slices": splits, "lanes": args.lanes},
@@ -639,6 +655,7 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--case", default="", help="profiler case: run six launches of one projection (e.g. gate_proj) and exit")
     ap.add_argument("--prefill", action="store_true", help="with --case: the prefill arithmetic (tcgen05 kernel)")
+    ap.add_argument("--no-branches", action="store_true", help="launch the seven projections one after another")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE layer / row-count sweeps reported beside the headline")
     ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")

@@ -31,7 +31,9 @@ namespace cg = cooperative_groups;
 
 #ifdef TF_TRACE
 // debug build only: block (0, 0, 0) logs (event, stage, clock) into shared memory, dumped to p.part when it ends
+#ifndef TF_TRACE_EVENTS
 #define TF_TRACE_EVENTS 200
+#endif
 #define TF_MARK(ev, st)                                                                    \
   do {                                                                                     \
     if (tf_trace_on && lane == 0 && tf_tr < TF_TRACE_EVENTS) {                             \

@@ -185,6 +185,37 @@ def prefill_matmul(x: torch.Tensor, q: Q4, *, f32: bool = False, tile: int = 0,
     return out
 
 
+_side_streams: dict = {}
+
+
+def fork_join(calls) -> None:
+    """Runs independent launches side by side: ``calls`` are thunks that launch on the current stream (projections that
+    read the same input, like q/k/v or gate/up).  The first runs on the current stream, the others on side streams that
+    wait for everything already queued on it; the current stream then waits for all of them.  Works eagerly and under
+    CUDA-graph capture (the waits become graph edges).  A decode-sized projection cannot fill the GPU on its own (its
+    launch, first-byte latency and slice reduction are fixed costs), so independent ones overlap nearly for free."""
+
+    calls = list(calls)
+    if len(calls) < 2:
+        for fn in calls:
+            fn()
+        return
+    main = torch.cuda.current_stream()
+    pool = _side_streams.setdefault(main.device, [])
+    while len(pool) < len(calls) - 1:
+        pool.append(torch.cuda.Stream(device=main.device))
+    fork = torch.cuda.Event()
+    fork.record(main)
+    calls[0]()
+    for fn, side in zip(calls[1:], pool):
+        side.wait_event(fork)
+        with torch.cuda.stream(side):
+            fn()
+        done = torch.cuda.Event()
+        done.record(side)
+        main.wait_event(done)
+
+
 def pack_pair(gate: tuple, up: tuple, gs: int, bits: int = 4) -> Q4:
     """Gate and up projections (each MLX words, scales, biases of n rows) as ONE weight of 2 n rows that interleaves 16
     gate rows with 16 up rows, so a matmul tile pair holds both halves of every SwiGLU output (see ``matmul_act``)."""

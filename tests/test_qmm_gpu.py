@@ -189,6 +189,35 @@ def test_lane_mapping_never_changes_bits():
         lib.tf_tune(b"qmm_lanes", 0)
 
 
+def test_fork_join_runs_independent_projections_side_by_side():
+    """q/k/v-style projections of the same rows launched through fork_join give the bits of one-after-another launches,
+    eagerly and from a captured CUDA graph."""
+
+    shapes = [(1024, 1024), (256, 1024), (256, 1024)]
+    qs = [qmm.pack(*to_dev(synthetic.affine_weight(n, k, 4, 64, seed=40 + i)), 64) for i, (n, k) in enumerate(shapes)]
+    x = synthetic.activations(9, 1024, 5).to(DEV)
+    want = [qmm.matmul(x, q) for q in qs]
+    outs = [torch.zeros_like(w) for w in want]
+    thunks = [(lambda q=q, o=o: qmm.matmul(x, q, out=o)) for q, o in zip(qs, outs)]
+    qmm.fork_join(thunks)
+    torch.cuda.synchronize()
+    for o, w in zip(outs, want):
+        assert torch.equal(o, w)
+    for o in outs:
+        o.zero_()
+    stream, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            qmm.fork_join(thunks)
+            y = qmm.matmul(outs[0], qs[1])                             # a dependent launch after the join
+        graph.replay()
+    torch.cuda.synchronize()
+    for o, w in zip(outs, want):
+        assert torch.equal(o, w)
+    assert torch.equal(y, qmm.matmul(want[0], qs[1]))
+
+
 def test_no_wait_gave_up():
     x = torch.zeros(1, device=DEV)
     assert _lib.device_error(x) == 0
