@@ -246,30 +246,52 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue (one thread)
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_ROWS >> 3) << 17) | ((PF_COLS >> 4) << 24);
-    bool ok = true;
-    for (int i = 0; i < nstages && ok; ++i) {
-      const int st = i % NS;
-      ok = mbar_wait_ready(full + st, (i / NS) & 1, abort_flag);
-      if (!ok) {
-        give_up(ERR_WAIT_FULL);
-        break;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      PF_MARK(4, i);
-      {
-        const uint32_t leader = lane == 0 ? 1u : 0u;
-#ifndef PF_DBG_NOMMA
-        const uint64_t ad = umma_desc(smem_addr(a_tile(st))), bd = umma_desc(smem_addr(b_tile(st)));
+    // The tensor pipe's queue is short and every instruction of this warp between two MMA issues is dead time for
+    // it, so the loop is unrolled over the ring (descriptors precomputed, no index arithmetic) and the next stage's
+    // full barrier is tested between this stage's MMAs, while earlier ones are still executing.
+    const uint32_t leader = lane == 0 ? 1u : 0u;
+    uint64_t adesc[NS], bdesc[NS];
 #pragma unroll
-        for (int k = 0; k < PF_STAGE_K / 16; ++k)
-          umma_bf16(tmem_base, ad + 2 * k, bd + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u, leader);   // + 32 bytes a k16 step
+    for (int st = 0; st < NS; ++st) {
+      adesc[st] = umma_desc(smem_addr(a_tile(st)));
+      bdesc[st] = umma_desc(smem_addr(b_tile(st)));
+    }
+    bool ok = mbar_wait(full, 0, abort_flag);
+    if (!ok) give_up(ERR_WAIT_FULL);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t phase = 0;                                          // parity of the full barriers of this pass over the ring
+    for (int base = 0; base < nstages && ok; base += NS, phase ^= 1u) {
+#pragma unroll
+      for (int st = 0; st < NS; ++st) {
+        const int i = base + st;
+        if (i >= nstages || !ok) break;
+        const int nx = (st + 1) % NS;
+        const uint32_t nx_phase = st + 1 == NS ? phase ^ 1u : phase;
+        const bool more = i + 1 < nstages;
+        bool next_ready = false;
+        PF_MARK(4, i);
+#ifndef PF_DBG_NOMMA
+        umma_bf16(tmem_base, adesc[st], bdesc[st], IDESC, i > 0 ? 1u : 0u, leader);
+        umma_bf16(tmem_base, adesc[st] + 2, bdesc[st] + 2, IDESC, 1u, leader);       // + 32 bytes a k16 step
+        umma_bf16(tmem_base, adesc[st] + 4, bdesc[st] + 4, IDESC, 1u, leader);
+        if (more) {
+          next_ready = mbar_test(full + nx, nx_phase);
+          if (next_ready) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        umma_bf16(tmem_base, adesc[st] + 6, bdesc[st] + 6, IDESC, 1u, leader);
+#else
+        if (more) next_ready = mbar_test(full + nx, nx_phase);
 #endif
         PF_MARK(6, i);
         umma_commit(empty + st, leader);
-        if (i == nstages - 1) umma_commit(acc_full, leader);
+        if (!more) umma_commit(acc_full, leader);
+        PF_MARK(5, i);
+        if (more && !next_ready) {
+          ok = mbar_wait(full + nx, nx_phase, abort_flag);
+          if (!ok) give_up(ERR_WAIT_FULL);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
       }
-      PF_MARK(5, i);
-      __syncwarp();
     }
   } else if (warp >= PF_CONV0) {
     // ------------------------------------------------------------------ conversion: packed codes -> swizzled bf16 A tile

@@ -69,6 +69,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   return __all_sync(0xFFFFFFFFu, ok);
 }
 
+// One non-blocking test by a whole warp: true, for all lanes alike, when the phase with this parity is complete.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return __all_sync(0xFFFFFFFFu, ok != 0);
+}
+
 // The same for a barrier that is normally complete already: one non-blocking test first (a test is cheaper than a
 // potentially suspending try_wait), the bounded wait only if it fails.
 __device__ __forceinline__ bool mbar_wait_ready(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {

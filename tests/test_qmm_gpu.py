@@ -194,7 +194,7 @@ def test_fork_join_runs_independent_projections_side_by_side():
     eagerly and from a captured CUDA graph."""
 
     shapes = [(1024, 1024), (256, 1024), (256, 1024)]
-    qs = [qmm.pack(*to_dev(synthetic.affine_weight(n, k, 4, 64, seed=40 + i)), 64) for i, (n, k) in enumerate(shapes)]
+    qs = [qmm.pack(*to_dev(*synthetic.affine_weight(n, k, 4, 64, seed=40 + i)), 64) for i, (n, k) in enumerate(shapes)]
     x = synthetic.activations(9, 1024, 5).to(DEV)
     want = [qmm.matmul(x, q) for q in qs]
     outs = [torch.zeros_like(w) for w in want]
