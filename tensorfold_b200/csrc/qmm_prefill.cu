@@ -6,14 +6,15 @@
 // kernel's bits (that one keeps the affine terms in fp32).
 //
 // Block tile = 128 output columns x 256 rows of x, "swap-AB": the dequantised weights are the MMA's A operand (M = 128),
-// the rows of x its B operand (N = 256), so every dequantised weight feeds 256 rows.  Two rings decouple the latencies:
-// packed units arrive from HBM (about 2000 cycles away) by bulk copies into a ring of small slots; a stage of the main
-// ring holds the dequantised A tile and the x tile (a 2-D tensor-map copy with the 128-byte swizzle) of 64 inputs
-// behind ONE full barrier and ONE empty barrier, because every barrier operation of the MMA-issuing thread costs about
-// as much as an MMA issue and the tensor pipe idles while that thread does anything else.  Roles: warp 0 loads x,
-// warp 1 owns tensor memory and issues the MMAs, warp 2 loads packed units, warps 4-19 are two groups of eight
-// conversion warps that take alternate stages (a stage's conversion has a long dependent chain, so two stages are
-// always in conversion) and afterwards all sixteen drain the accumulator to global memory.
+// the rows of x its B operand (N = 256), so every dequantised weight feeds 256 rows.  The kernel is persistent: a grid
+// no larger than the number of SMs, tiles dealt round-robin, and every producer simply runs on into the block's next
+// tile, so a tile's prologue (first bytes are about 2000 cycles away) and its drain overlap the neighbouring tiles'
+// MMAs.  Two rings decouple the latencies: packed units arrive from HBM by bulk copies into a ring of small slots; a
+// stage of the main ring holds the dequantised A tile and the x tile (a 2-D tensor-map copy with the 128-byte
+// swizzle) of 64 inputs behind ONE full barrier and ONE empty barrier.  Two accumulators in tensor memory alternate
+// between tiles.  Roles: warp 0 loads x, warp 1 owns tensor memory and issues the MMAs, warp 2 loads packed units,
+// warps 4-19 are two groups of eight conversion warps that take alternate stages (a stage's conversion is a long
+// dependent chain, so two stages are always in conversion), warps 20-23 drain the finished accumulator to global memory.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -37,8 +38,9 @@ constexpr int PF_STAGE_K = 64;     // inputs a stage
 constexpr int PF_A_BYTES = PF_COLS * 128;
 constexpr int PF_W_BYTES = 5120;   // packed units of a stage: one g64 unit (4608 B) or two g32 units (5120 B)
 constexpr int PF_NW = 6;           // packed-unit slots in flight
-constexpr int PF_THREADS = 640;    // 20 warps: x loads, MMA, unit loads, (idle), 2 x 8 conversion
-constexpr int PF_CONV0 = 4;        // first conversion warp (a multiple of 4: tensor-memory lane groups go by warp % 4)
+constexpr int PF_THREADS = 768;    // 24 warps: x loads, MMA, unit loads, (idle), 2 x 8 conversion, 4 drain
+constexpr int PF_CONV0 = 4;        // first conversion warp
+constexpr int PF_DRAIN0 = 20;      // first drain warp (a multiple of 4: tensor-memory lane groups go by warp % 4)
 constexpr int PF_BAR_BYTES = 512;
 
 // ROWS = rows of x of a block tile (MMA N): 256 for dense prompts, 128 for the grouped expert form
@@ -50,7 +52,7 @@ struct PfGeo {
   static constexpr int W_OFF = NS * STAGE, BAR_OFF = W_OFF + PF_NW * PF_W_BYTES;
   static constexpr int SMEM = BAR_OFF + PF_BAR_BYTES + 1024 /* alignment slack */;
   static_assert(STAGE % 1024 == 0, "tiles stay 1024-byte aligned for the 128-byte swizzle");
-  static_assert((2 * NS + 2 * PF_NW + 1) * 8 + 16 <= PF_BAR_BYTES, "barriers fit");
+  static_assert((2 * NS + 2 * PF_NW + 4) * 8 + 16 <= PF_BAR_BYTES, "barriers fit");
   static_assert(NS % 2 == 0, "conversion groups alternate stages");
   static_assert(SMEM <= 232448, "fits the opt-in shared memory of a block");
 };
@@ -123,20 +125,11 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-#ifdef PF_TRACE
-// debugging aid (compiled out by default): block (0, 0)'s clock at each stage's events
-__device__ long long g_pf_trace[8 * 512];
-#define PF_MARK(ev, i) \
-  do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (i) < 512) g_pf_trace[(ev) * 512 + (i)] = clock64(); } while (0)
-#else
-#define PF_MARK(ev, i) do { } while (0)
-#endif
-
 template <int GS, int ROWS>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmx, const PrefillParams p) {
   using Geo = PfGeo<ROWS>;
   constexpr int PF_ROWS = ROWS, PF_B_BYTES = Geo::B_BYTES, NS = Geo::NS;
-  constexpr uint32_t PF_TMEM_COLS = ROWS;
+  constexpr uint32_t PF_TMEM_COLS = 2 * ROWS;                // two accumulators: one fills while the other drains
   constexpr int S = GS / 16;                                 // k16 steps a group
   constexpr int UNITS = PF_STAGE_K / GS;                     // units a stage (1 for g64, 2 for g32)
   constexpr int WPL = words_per_lane(4, GS);
@@ -150,27 +143,49 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
   uint64_t* empty = full + NS;                      // the MMAs that read the stage are done
   uint64_t* w_full = empty + NS;                    // packed units landed (bulk copy)
   uint64_t* w_empty = w_full + PF_NW;               // the 8 conversion warps of the stage's group have read the slot
-  uint64_t* acc_full = w_empty + PF_NW;             // every MMA of the tile is done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_full = w_empty + PF_NW;             // [2] every MMA of a tile is done
+  uint64_t* acc_empty = acc_full + 2;               // [2] the 4 drain warps have read the accumulator
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int sb = blockIdx.x;
   const int nstages = (p.K + PF_STAGE_K - 1) / PF_STAGE_K;
   const int total_units = p.K / GS;
+  const int nsb = (p.N + PF_COLS - 1) / PF_COLS;
   const bool grouped = p.items != nullptr;
-  int m0 = blockIdx.y * PF_ROWS, rows_here, first = 0;
-  const uint32_t* wroot = p.w;
-  if (grouped) {
-    if (static_cast<int>(blockIdx.y) >= p.counts[0]) return;               // before any barrier or tensor-memory use
-    const int* item = p.items + 3 * blockIdx.y;
-    wroot += static_cast<int64_t>(item[0]) * p.expert_stride;
-    first = item[1];
-    rows_here = min(PF_ROWS, item[2]);
-    m0 = first;                                                             // row of the member-ordered input
-  } else {
-    rows_here = min(PF_ROWS, p.M - m0);
-  }
+  // Tiles = column blocks x row tiles (plan items in the grouped form), column block fastest, dealt round-robin to the
+  // blocks of a grid no larger than the number of SMs.  Every role walks the same (tile, stage) sequence, so a running
+  // stage count g names the ring slot (g % NS) and its phase without any exchange between the roles.
+  const int row_tiles = grouped ? p.counts[0] : (p.M + PF_ROWS - 1) / PF_ROWS;
+  const int tiles = nsb * row_tiles;
+  const int first_tile = blockIdx.x;
+  if (first_tile >= tiles) return;                           // before any barrier or tensor-memory use
+  const int my_tiles = (tiles - first_tile + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int total = my_tiles * nstages;                      // stages this block runs
+
+  struct Tile {
+    int sb, m0, rows_here, first;
+    const uint32_t* wroot;
+  };
+  auto tile_at = [&](int it) {
+    const int t = first_tile + it * static_cast<int>(gridDim.x);
+    Tile ti;
+    ti.sb = t % nsb;
+    const int y = t / nsb;
+    ti.wroot = p.w;
+    if (grouped) {
+      const int* item = p.items + 3 * y;
+      ti.wroot += static_cast<int64_t>(item[0]) * p.expert_stride;
+      ti.first = item[1];
+      ti.rows_here = min(PF_ROWS, item[2]);
+      ti.m0 = item[1];                                       // row of the member-ordered input
+    } else {
+      ti.first = 0;
+      ti.m0 = y * PF_ROWS;
+      ti.rows_here = min(PF_ROWS, p.M - ti.m0);
+    }
+    return ti;
+  };
 
   auto a_tile = [&](int s) { return smem + s * Geo::STAGE; };
   auto b_tile = [&](int s) { return smem + s * Geo::STAGE + PF_A_BYTES; };
@@ -185,7 +200,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) mbar_init(full + i, 9), mbar_init(empty + i, 1);
     for (int i = 0; i < PF_NW; ++i) mbar_init(w_full + i, 1), mbar_init(w_empty + i, 8);
-    mbar_init(acc_full, 1);
+    for (int i = 0; i < 2; ++i) mbar_init(acc_full + i, 1), mbar_init(acc_empty + i, 4);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -202,90 +217,97 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
   if (warp == 0) {
     // ------------------------------------------------------------------ x tiles (L2 -> shared, tensor-map copies)
     bool ok = true;
-    for (int i = 0; i < nstages && ok; ++i) {
-      const int s = i % NS;
-      if (i >= NS) {
-        ok = mbar_wait(empty + s, (i / NS - 1) & 1, abort_flag);
-        if (!ok) {
-          give_up(ERR_WAIT_EMPTY);
-          break;
+    int g = 0;
+    for (int it = 0; it < my_tiles && ok; ++it) {
+      const Tile ti = tile_at(it);
+      for (int ls = 0; ls < nstages && ok; ++ls, ++g) {
+        const int s = g % NS;
+        if (g >= NS) {
+          ok = mbar_wait(empty + s, (g / NS - 1) & 1, abort_flag);
+          if (!ok) {
+            give_up(ERR_WAIT_EMPTY);
+            break;
+          }
         }
+        if (lane == 0) {
+          mbar_expect_tx(full + s, PF_B_BYTES);
+          tma_load_2d(b_tile(s), &tmx, ls * PF_STAGE_K, ti.m0, full + s);
+        }
+        __syncwarp();
       }
-      PF_MARK(0, i);
-      if (lane == 0) {
-#ifdef PF_DBG_NOX
-        mbar_arrive(full + s);
-#else
-        mbar_expect_tx(full + s, PF_B_BYTES);
-        tma_load_2d(b_tile(s), &tmx, i * PF_STAGE_K, m0, full + s);
-#endif
-      }
-      __syncwarp();
     }
   } else if (warp == 2) {
     // ------------------------------------------------------------------ packed units (HBM -> shared, bulk copies)
-    const uint32_t* wsb = wroot + static_cast<int64_t>(sb) * p.sb_stride;
     bool ok = true;
-    for (int i = 0; i < nstages && ok; ++i) {
-      const int s = i % PF_NW;
-      if (i >= PF_NW) {
-        ok = mbar_wait(w_empty + s, (i / PF_NW - 1) & 1, abort_flag);
-        if (!ok) {
-          give_up(ERR_WAIT_EMPTY);
-          break;
+    int g = 0;
+    for (int it = 0; it < my_tiles && ok; ++it) {
+      const Tile ti = tile_at(it);
+      const uint32_t* wsb = ti.wroot + static_cast<int64_t>(ti.sb) * p.sb_stride;
+      for (int ls = 0; ls < nstages && ok; ++ls, ++g) {
+        const int s = g % PF_NW;
+        if (g >= PF_NW) {
+          ok = mbar_wait(w_empty + s, (g / PF_NW - 1) & 1, abort_flag);
+          if (!ok) {
+            give_up(ERR_WAIT_EMPTY);
+            break;
+          }
         }
+        if (lane == 0) {
+          const int units_here = min(UNITS, total_units - ls * UNITS);
+          mbar_expect_tx(w_full + s, units_here * UNITW * 4);
+          bulk_load(w_slot(s), wsb + static_cast<int64_t>(ls) * UNITS * UNITW, units_here * UNITW * 4, w_full + s);
+        }
+        __syncwarp();
       }
-      PF_MARK(1, i);
-      if (lane == 0) {
-        const int units_here = min(UNITS, total_units - i * UNITS);
-        mbar_expect_tx(w_full + s, units_here * UNITW * 4);
-        bulk_load(w_slot(s), wsb + static_cast<int64_t>(i) * UNITS * UNITW, units_here * UNITW * 4, w_full + s);
-      }
-      __syncwarp();
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue (one thread)
-    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_ROWS >> 3) << 17) | ((PF_COLS >> 4) << 24);
     // The tensor pipe's queue is short and every instruction of this warp between two MMA issues is dead time for
-    // it, so the loop is unrolled over the ring (descriptors precomputed, no index arithmetic) and the next stage's
-    // full barrier is tested between this stage's MMAs, while earlier ones are still executing.
+    // it, so the loop is unrolled over the ring (descriptors by constant offsets, no index arithmetic) and the next
+    // stage's full barrier is tested between this stage's MMAs, while earlier ones are still executing.
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_ROWS >> 3) << 17) | ((PF_COLS >> 4) << 24);
+    constexpr uint64_t SLOT_STEP = Geo::STAGE >> 4;            // a ring slot further, in descriptor address units
     const uint32_t leader = lane == 0 ? 1u : 0u;
-    uint64_t adesc[NS], bdesc[NS];
-#pragma unroll
-    for (int st = 0; st < NS; ++st) {
-      adesc[st] = umma_desc(smem_addr(a_tile(st)));
-      bdesc[st] = umma_desc(smem_addr(b_tile(st)));
-    }
+    const uint64_t ad0 = umma_desc(smem_addr(a_tile(0))), bd0 = umma_desc(smem_addr(b_tile(0)));
     bool ok = mbar_wait(full, 0, abort_flag);
     if (!ok) give_up(ERR_WAIT_FULL);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     uint32_t phase = 0;                                          // parity of the full barriers of this pass over the ring
-    for (int base = 0; base < nstages && ok; base += NS, phase ^= 1u) {
+    int ls = 0, it = 0;                                          // stage inside the tile, tile count of this block
+    for (int base = 0; base < total && ok; base += NS, phase ^= 1u) {
 #pragma unroll
       for (int st = 0; st < NS; ++st) {
-        const int i = base + st;
-        if (i >= nstages || !ok) break;
+        const int g = base + st;
+        if (g >= total || !ok) break;
+        if (ls == 0 && it >= 2) {                                // the accumulator's last tile must have been drained
+          ok = mbar_wait(acc_empty + (it & 1), ((it >> 1) - 1) & 1, abort_flag);
+          if (!ok) {
+            give_up(ERR_WAIT_EMPTY);
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        const uint32_t acc = tmem_base + static_cast<uint32_t>(it & 1) * PF_ROWS;
+        const uint64_t ad = ad0 + st * SLOT_STEP, bd = bd0 + st * SLOT_STEP;
         const int nx = (st + 1) % NS;
         const uint32_t nx_phase = st + 1 == NS ? phase ^ 1u : phase;
-        const bool more = i + 1 < nstages;
+        const bool more = g + 1 < total;
         bool next_ready = false;
-        PF_MARK(4, i);
-#ifndef PF_DBG_NOMMA
-        umma_bf16(tmem_base, adesc[st], bdesc[st], IDESC, i > 0 ? 1u : 0u, leader);
-        umma_bf16(tmem_base, adesc[st] + 2, bdesc[st] + 2, IDESC, 1u, leader);       // + 32 bytes a k16 step
-        umma_bf16(tmem_base, adesc[st] + 4, bdesc[st] + 4, IDESC, 1u, leader);
+        umma_bf16(acc, ad, bd, IDESC, ls > 0 ? 1u : 0u, leader);
+        umma_bf16(acc, ad + 2, bd + 2, IDESC, 1u, leader);       // + 32 bytes a k16 step inside the swizzle atom
+        umma_bf16(acc, ad + 4, bd + 4, IDESC, 1u, leader);
         if (more) {
           next_ready = mbar_test(full + nx, nx_phase);
           if (next_ready) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        umma_bf16(tmem_base, adesc[st] + 6, bdesc[st] + 6, IDESC, 1u, leader);
-#else
-        if (more) next_ready = mbar_test(full + nx, nx_phase);
-#endif
-        PF_MARK(6, i);
+        umma_bf16(acc, ad + 6, bd + 6, IDESC, 1u, leader);
         umma_commit(empty + st, leader);
-        if (!more) umma_commit(acc_full, leader);
-        PF_MARK(5, i);
+        if (ls == nstages - 1) {
+          umma_commit(acc_full + (it & 1), leader);
+          ls = 0, ++it;
+        } else {
+          ++ls;
+        }
         if (more && !next_ready) {
           ok = mbar_wait(full + nx, nx_phase, abort_flag);
           if (!ok) give_up(ERR_WAIT_FULL);
@@ -293,27 +315,29 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         }
       }
     }
-  } else if (warp >= PF_CONV0) {
+  } else if (warp >= PF_CONV0 && warp < PF_DRAIN0) {
     // ------------------------------------------------------------------ conversion: packed codes -> swizzled bf16 A tile
-    const int cw = warp - PF_CONV0, group = cw >> 3, dw = cw & 7, tp = dw & 3, h = dw >> 2, g = lane >> 2;
+    // A warp owns 16 output columns (tile pair tp, half h) of every stage its group takes.  Per 16-input step a thread
+    // holds the four m8n8 fragments (two column octets x two input octets) of its lane's codes, so one stmatrix.x4
+    // writes four 8 x 16-byte row segments of the swizzled tile; lane l supplies the address of row l % 8 of fragment l / 8.
+    const int cw = warp - PF_CONV0, group = cw >> 3, dw = cw & 7, tp = dw & 3, h = dw >> 2, g8 = lane >> 2;
     const __nv_bfloat162 k128 = __floats2bfloat162_rn(128.f, 128.f);
     uint32_t row_off[4];                                        // this lane's row segment of each 16-input step of a stage
 #pragma unroll
     for (int q = 0; q < 4; ++q)
       row_off[q] = (32 * tp + 16 * h + 8 * ((lane >> 3) & 1) + (lane & 7)) * 128 + (((2 * q + (lane >> 4)) ^ (lane & 7)) << 4);
     bool ok = true;
-    for (int i = group; i < nstages && ok; i += 2) {
-      const int sw = i % PF_NW, st = i % NS;
+    for (int i = group; i < total && ok; i += 2) {             // i = the block's running stage count
+      const int sw = i % PF_NW, st = i % NS, ls = i % nstages;
       ok = mbar_wait(w_full + sw, (i / PF_NW) & 1, abort_flag);
       if (ok && i >= NS) ok = mbar_wait(empty + st, (i / NS - 1) & 1, abort_flag);
       if (!ok) {
         give_up(ERR_WAIT_FULL);
         break;
       }
-      if (cw == 0 || cw == 8) PF_MARK(2, i);
       const uint32_t* wst = reinterpret_cast<const uint32_t*>(w_slot(sw));
       const uint32_t at = smem_addr(a_tile(st));
-      const int units_here = min(UNITS, total_units - i * UNITS);
+      const int units_here = min(UNITS, total_units - ls * UNITS);
 #pragma unroll
       for (int u = 0; u < UNITS; ++u) {
         uint32_t wd[S] = {};
@@ -330,7 +354,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             const uint2 v = *reinterpret_cast<const uint2*>(unit + (tp * 32 + lane) * WPL + h * S);
             wd[0] = v.x, wd[1] = v.y;
           }
-          const uint2 sbw = *reinterpret_cast<const uint2*>(unit + TILE_PAIRS * 32 * WPL + tp * 32 + g * 4 + h * 2);
+          const uint2 sbw = *reinterpret_cast<const uint2*>(unit + TILE_PAIRS * 32 * WPL + tp * 32 + g8 * 4 + h * 2);
           const uint32_t sbv[2] = {sbw.x, sbw.y};                  // columns c0 and c0 + 8
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
@@ -339,7 +363,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             bi[r] = *reinterpret_cast<const __nv_bfloat162*>(&b2);
           }
         }
-#ifndef PF_DBG_NOCONV
 #pragma unroll
         for (int sidx = 0; sidx < S; ++sidx) {
           uint32_t frag[4];
@@ -354,7 +377,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                        "r"(frag[0]), "r"(frag[1]), "r"(frag[2]), "r"(frag[3])
                        : "memory");
         }
-#endif
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core's reads
       __syncwarp();
@@ -362,52 +384,87 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         mbar_arrive(full + st);
         mbar_arrive(w_empty + sw);                               // the slot's words are in registers or already used
       }
-      if (cw == 0 || cw == 8) PF_MARK(3, i);
     }
-
-    // ------------------------------------------------------------------ epilogue: tensor memory -> global
-    const bool done = mbar_wait(acc_full, 0, abort_flag);
-    if (!done) give_up(ERR_WAIT_FULL);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (done && *abort_flag == 0) {
-      const int lg = warp & 3, part = cw >> 2;                   // this warp may touch TMEM lanes [32 lg, 32 lg + 32)
-      const int n = sb * PF_COLS + lg * 32 + lane;               // the weight column this thread's lane holds
-      constexpr int CHUNKS = PF_ROWS / 128;                      // 32-row chunks of this warp's quarter of the rows
+  } else if (warp >= PF_DRAIN0) {
+    // ------------------------------------------------------------------ drain: tensor memory -> global, a tile behind
+    const int lg = warp & 3;                                   // this warp may touch TMEM lanes [32 lg, 32 lg + 32)
+    for (int it = 0; it < my_tiles; ++it) {
+      const Tile ti = tile_at(it);
+      const int ab = it & 1, rows_here = ti.rows_here, first = ti.first, m0 = ti.m0, sb = ti.sb;
+      const bool done = mbar_wait(acc_full + ab, (it >> 1) & 1, abort_flag);
+      if (!done) {
+        give_up(ERR_WAIT_FULL);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (*abort_flag != 0) break;
+      // A lane holds one output column for 32 rows of x.  Each group of eight lanes transposes its 8 x 8 blocks in
+      // registers (three butterfly steps), so a lane then holds eight neighbouring columns of one row and writes them
+      // as 16 bytes: a store instruction costs about the same whatever its width, and narrow ones made the drain the
+      // slowest part of a tile.
+      const bool swiglu = p.epi == 2;
+      const int col = swiglu ? sb * (PF_COLS / 2) + lg * 16 + lane : sb * PF_COLS + lg * 32 + lane;
+      const int ncols = swiglu ? p.N / 2 : p.N;
+      const bool live = col < ncols && (!swiglu || lane < 16);
+      const bool wide = !p.out_f32 && (ncols & 7) == 0 && (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+      const int l8 = lane & 7;
 #pragma unroll 1
-      for (int chunk = 0; chunk < CHUNKS; ++chunk) {
+      for (int col0 = 0; col0 < rows_here; col0 += 32) {         // 32 rows of x a pass
         uint32_t r[32];
-        const int col0 = part * (PF_ROWS / 4) + chunk * 32;
-        tmem_load32(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + col0, r);
-        if (p.epi == 2) {
-          // lanes 0-15 hold gate columns, lanes 16-31 the up columns of the same 16 outputs
-          const int nout = sb * (PF_COLS / 2) + lg * 16 + lane;
+        tmem_load32(tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(ab * PF_ROWS + col0), r);
+        float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float up = __shfl_down_sync(0xFFFFFFFFu, __uint_as_float(r[j]), 16);
-            const int rr = col0 + j;
-            if (lane < 16 && rr < rows_here && nout < p.N / 2) {
+        for (int j = 0; j < 32; ++j) {
+          v[j] = __uint_as_float(r[j]);
+          if (swiglu) {                                          // lanes 0-15 hold gate columns, 16-31 the up columns
+            const float up = __shfl_down_sync(0xFFFFFFFFu, v[j], 16);
+            v[j] = pf_swiglu(v[j], up, p.limit);
+          } else if (p.epi == 1) {
+            v[j] = fmaxf(pf_bf16r(v[j]), 0.f);
+            v[j] = v[j] * v[j];
+          }
+        }
+        if (wide) {
+#pragma unroll
+          for (int blk = 0; blk < 4; ++blk) {                    // rows 8 blk .. 8 blk + 7 of the pass
+            float* a = v + 8 * blk;
+#pragma unroll
+            for (int mask = 4; mask >= 1; mask >>= 1) {
+              const bool upper = (l8 & mask) != 0;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                if (i & mask) continue;
+                const float got = __shfl_xor_sync(0xFFFFFFFFu, upper ? a[i] : a[i | mask], mask);
+                if (upper) a[i] = got;
+                else a[i | mask] = got;
+              }
+            }
+            const int rr = col0 + 8 * blk + l8;                  // a[c] = column (col - l8 + c) of row rr
+            if (live && rr < rows_here) {
               const int64_t m = grouped ? p.members[first + rr] : m0 + rr;
-              reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + nout] =
-                  __float2bfloat16_rn(pf_swiglu(__uint_as_float(r[j]), up, p.limit));
+              uint4 o;
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(a[0], a[1]), t1 = __floats2bfloat162_rn(a[2], a[3]);
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(a[4], a[5]), t3 = __floats2bfloat162_rn(a[6], a[7]);
+              o.x = *reinterpret_cast<uint32_t*>(&t0), o.y = *reinterpret_cast<uint32_t*>(&t1);
+              o.z = *reinterpret_cast<uint32_t*>(&t2), o.w = *reinterpret_cast<uint32_t*>(&t3);
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + m * p.ldo + (col - l8)) = o;
             }
           }
-        } else if (n < p.N) {
+        } else if (live) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int rr = col0 + j;
             if (rr < rows_here) {
               const int64_t m = grouped ? p.members[first + rr] : m0 + rr;
-              float v = __uint_as_float(r[j]);
-              if (p.epi == 1) {
-                v = fmaxf(pf_bf16r(v), 0.f);
-                v = v * v;
-              }
-              if (p.out_f32) reinterpret_cast<float*>(p.out)[m * p.ldo + n] = v;
-              else reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(v);
+              if (p.out_f32) reinterpret_cast<float*>(p.out)[m * p.ldo + col] = v[j];
+              else reinterpret_cast<__nv_bfloat16*>(p.out)[m * p.ldo + col] = __float2bfloat16_rn(v[j]);
             }
           }
         }
       }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + ab);
     }
   }
 
@@ -451,11 +508,19 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, int64_
   for (int i = lane; i < k / 8; i += 32) d4[i] = s4[i];
 }
 
-#ifdef PF_TRACE
-extern "C" int tf_debug_pf_trace(long long* host) {
-  return cudaMemcpyFromSymbol(host, g_pf_trace, sizeof(g_pf_trace)) == cudaSuccess ? 0 : 1;
+
+// SMs of the current device (cached per device)
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
 }
-#endif
 
 cudaError_t prefill_configure() {
   cudaError_t e = cudaFuncSetAttribute(prefill_kernel<64, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<256>::SMEM);
@@ -509,8 +574,11 @@ extern "C" int tf_qmm_prefill_act(const void* x, int64_t ldx, int m, const void*
   p.out = out, p.ldo = ldo, p.out_f32 = out_f32;
   p.err = err;
   p.epi = epi, p.limit = limit;
-  dim3 grid((n + PF_COLS - 1) / PF_COLS, (m + 255) / 256);
-  if (grid.y > 65535) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: too many rows");
+  const int64_t tiles = static_cast<int64_t>((n + PF_COLS - 1) / PF_COLS) * ((m + 255) / 256);
+  if (tiles > (1 << 24)) return fail_moe(TF_ERR_ARG, "tf_qmm_prefill: too many tiles");
+  const int sms = sm_count();
+  if (sms < 1) return fail_moe(TF_ERR_STATE, "tf_qmm_prefill: cannot read the SM count");
+  dim3 grid(static_cast<unsigned>(tiles < sms ? tiles : sms));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (gs == 64) prefill_kernel<64, 256><<<grid, PF_THREADS, PfGeo<256>::SMEM, s>>>(map, p);
   else prefill_kernel<32, 256><<<grid, PF_THREADS, PfGeo<256>::SMEM, s>>>(map, p);
@@ -547,7 +615,10 @@ extern "C" int tf_moe_experts_prefill(const void* x, int64_t ldx, int slots, con
   p.items = items, p.counts = counts, p.members = members;
   p.expert_stride = expert_stride;
   p.epi = epi, p.limit = limit;
-  dim3 grid((n + PF_COLS - 1) / PF_COLS, max_items);
+  const int64_t tiles = static_cast<int64_t>((n + PF_COLS - 1) / PF_COLS) * max_items;   // upper bound: the plan says how many
+  const int sms = sm_count();
+  if (sms < 1) return fail_moe(TF_ERR_STATE, "tf_moe_experts_prefill: cannot read the SM count");
+  dim3 grid(static_cast<unsigned>(tiles < sms ? tiles : sms));
   if (gs == 64) prefill_kernel<64, 128><<<grid, PF_THREADS, PfGeo<128>::SMEM, s>>>(map, p);
   else prefill_kernel<32, 128><<<grid, PF_THREADS, PfGeo<128>::SMEM, s>>>(map, p);
   const cudaError_t e = cudaGetLastError();
