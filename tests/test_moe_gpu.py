@@ -7,7 +7,7 @@ import torch
 
 from oracle import affine as oaff
 from oracle import moe as omoe
-from tensorfold_b200 import synthetic
+from tensorfold_b200 import _lib, synthetic
 from tensorfold_b200.cuda import experts, moe
 from tensorfold_b200.cuda.kernels import qmm
 
@@ -107,6 +107,22 @@ def test_layer_matches_the_oracle(prefill):
     assert np.abs(out.float().cpu().numpy() - ref).max() <= 2 ** -6 * np.abs(ref).max()
     for r in (0, 9, 20):                                        # a row alone routes and runs to the same bits
         assert torch.equal(moe.run(x[r:r + 1].to(DEV), m, prefill=prefill), out[r:r + 1]), r
+
+
+def test_prompt_sized_layer_runs_many_tiles_a_block():
+    """1200 rows, top 4 of 16 experts: about 50 plan items x 4 column blocks, more tiles than SMs, so the persistent
+    prefill kernel runs several (item, column block) tiles a block.  Rows must keep the bits of a small call and the
+    first rows must match the oracle."""
+
+    d, e, ni, sni, gs, top_k = 512, 16, 256, 512, 64, 4
+    m, raw = layer(d, e, ni, sni, gs, top_k, 19)
+    x = synthetic.activations(1200, d, 4)
+    out = moe.run(x.to(DEV), m, prefill=True)
+    for a, b in ((0, 5), (600, 601), (1100, 1200)):
+        assert torch.equal(moe.run(x[a:b].to(DEV), m, prefill=True), out[a:b]), (a, b)
+    ref, _ = oracle_layer(x[:6], raw, gs, top_k)
+    assert np.abs(out[:6].float().cpu().numpy() - ref).max() <= 2 ** -6 * np.abs(ref).max()
+    assert _lib.device_error(out) == 0
 
 
 def test_benchmark_moe_layer_shapes_rows_are_bit_stable():

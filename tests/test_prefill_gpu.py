@@ -66,6 +66,27 @@ def test_rows_do_not_depend_on_the_chunk(n, k, gs):
     assert torch.equal(qmm.prefill_matmul(wide[:, :k], q), whole)             # strided rows
 
 
+def test_blocks_that_run_several_tiles_keep_the_bits():
+    """360 tiles on at most 148 persistent blocks: a block runs two or three tiles back to back on alternating
+    accumulators.  Every 256-row chunk run on its own (40 tiles: one per block) must give the same bits, and the whole
+    must match the oracle."""
+
+    n, k, gs, m = 5120, 256, 64, 2304
+    w = synthetic.affine_weight(n, k, 4, gs, seed=77)
+    q = qmm.pack(*to_dev(*w), gs)
+    x = synthetic.activations(m, k, 9)
+    whole = qmm.prefill_matmul(x.to(DEV), q)
+    for a in range(0, m, 256):
+        assert torch.equal(qmm.prefill_matmul(x[a:a + 256].to(DEV), q), whole[a:a + 256]), a
+    ref = reference(x, *w, gs)
+    assert np.abs(whole.float().cpu().numpy() - ref).max() <= np.abs(ref).max() * 2 ** -7
+    pair = qmm.pack_pair(to_dev(*w), to_dev(*synthetic.affine_weight(n, k, 4, gs, seed=78)), gs)
+    act = qmm.matmul_act(x.to(DEV), pair, act="swiglu", prefill=True)       # 80 x 9 tiles through the SwiGLU drain
+    for a in (0, 1024, 2048):
+        assert torch.equal(qmm.matmul_act(x[a:a + 256].to(DEV), pair, act="swiglu", prefill=True), act[a:a + 256]), a
+    assert _lib.device_error(whole) == 0
+
+
 def test_other_formats_fall_back_to_the_exact_matmul():
     w = synthetic.affine_weight(256, 1024, 3, 128, seed=4)
     q = qmm.pack(*to_dev(*w), 128, bits=3)
