@@ -470,10 +470,11 @@ def run_b200(args) -> None:
         if branches:
             # the layer's dataflow: q/k/v read the same rows and so do gate/up, so each set runs side by side; o_proj
             # waits for the first set (attention sits between them in a model), down_proj for the second
+            chain = pdl and not args.no_chain_pdl          # main-stream launches overlap their predecessor's tail
             qmm.fork_join([mm("q_proj", pdl), mm("k_proj", False), mm("v_proj", False)])
-            mm("o_proj", False)()
-            qmm.fork_join([mm("gate_proj", False), mm("up_proj", False)])
-            mm("down_proj", False)()
+            mm("o_proj", chain)()
+            qmm.fork_join([mm("gate_proj", chain), mm("up_proj", False)])
+            mm("down_proj", chain)()
             return
         for name, _ in shapes:
             if world > 1 and name not in column:            # row-parallel: bf16 partial, rank-ordered reduction
@@ -656,6 +657,7 @@ def main() -> None:
     ap.add_argument("--case", default="", help="profiler case: run six launches of one projection (e.g. gate_proj) and exit")
     ap.add_argument("--prefill", action="store_true", help="with --case: the prefill arithmetic (tcgen05 kernel)")
     ap.add_argument("--no-branches", action="store_true", help="launch the seven projections one after another")
+    ap.add_argument("--no-chain-pdl", action="store_true", help="with branches: programmatic launch for q_proj only")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE layer / row-count sweeps reported beside the headline")
     ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")

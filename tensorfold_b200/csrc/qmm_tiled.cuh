@@ -493,8 +493,9 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
       for (int e = 0; e < valid; ++e) dst[e] = __float2bfloat16_rn(swiglu_f(src[e], src[16 + e], p.limit));
     }
   } else if (!failed) {
-    for (int idx = tid; idx < lanes_here * ROWS * 16; idx += THREADS) {
-      if (idx % share != mine_rank) continue;
+    // 8-column pieces of the block's tiles; piece idx belongs to slice idx % share.  A block's own pieces go to
+    // consecutive threads, so (up to THREADS of them) they are summed in one round of remote loads.
+    for (int idx = tid * share + mine_rank; idx < lanes_here * ROWS * 16; idx += THREADS * share) {
       const int kw = idx / (ROWS * 16), rem = idx % (ROWS * 16);
       const int ml = rem >> 4, c8 = (rem & 15) * 8, n = (sb0 + kw) * SB_COLS + c8;
       if (ml >= rows_here || n >= p.N) continue;
