@@ -459,7 +459,7 @@ def run_b200(args) -> None:
                      else qmm.default_split(nout[name], kin[name], GS)) for name, _ in shapes}
     reduced = {}
 
-    branches = world == 1 and not args.no_branches
+    branches = not args.no_branches
 
     def step(i: int, pdl: bool) -> None:
         layer = layers[i % ring]
@@ -467,14 +467,25 @@ def run_b200(args) -> None:
         def mm(name: str, p: bool):
             return lambda: qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=p, sk=splits[name])
 
+        def row_parallel(name: str):                        # bf16 partial, then the rank-ordered reduction
+            qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=False, sk=splits[name])
+            reduced[name] = tp.ordered_all_reduce(dev_y[name])
+
         if branches:
             # the layer's dataflow: q/k/v read the same rows and so do gate/up, so each set runs side by side; o_proj
-            # waits for the first set (attention sits between them in a model), down_proj for the second
+            # waits for the first set (attention sits between them in a model), down_proj for the second.  With
+            # several ranks only the column-parallel sets fork; the collectives stay on the main stream.
             chain = pdl and not args.no_chain_pdl          # main-stream launches overlap their predecessor's tail
             qmm.fork_join([mm("q_proj", pdl), mm("k_proj", False), mm("v_proj", False)])
-            mm("o_proj", chain)()
+            if world > 1:
+                row_parallel("o_proj")
+            else:
+                mm("o_proj", chain)()
             qmm.fork_join([mm("gate_proj", chain), mm("up_proj", False)])
-            mm("down_proj", chain)()
+            if world > 1:
+                row_parallel("down_proj")
+            else:
+                mm("down_proj", chain)()
             return
         for name, _ in shapes:
             if world > 1 and name not in column:            # row-parallel: bf16 partial, rank-ordered reduction
