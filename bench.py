@@ -447,10 +447,30 @@ def run_b200(args) -> None:
         layers.append(packed)
     kin = {name: (k if name in column or world == 1 else k // world) for name, (n, k) in shapes}
     nout = {name: (n // world if name in column and world > 1 else n) for name, (n, k) in shapes}
-    host_x = {name: synthetic.activations(rows, kin[name], 31 + i).pin_memory() for i, (name, _) in enumerate(shapes)}
-    dev_x = {name: t.to(dev) for name, t in host_x.items()}
-    dev_y = {name: torch.empty((rows, nout[name]), dtype=torch.bfloat16, device=dev) for name, _ in shapes}
-    host_y = {name: torch.empty((rows, nout[name]), dtype=torch.bfloat16).pin_memory() for name, _ in shapes}
+    # One pinned slab for the step's inputs and one for its outputs (and the same on the device): the end-to-end arm
+    # then moves a step's rows with one copy each way instead of one per projection.
+    def slab(sizes, pinned):
+        total = sum(sizes.values())
+        buf = torch.empty((total,), dtype=torch.bfloat16).pin_memory() if pinned else torch.empty((total,), dtype=torch.bfloat16, device=dev)
+        views, at = {}, 0
+        for name, size in sizes.items():
+            views[name] = buf[at:at + size]
+            at += size
+        return buf, views
+
+    x_sizes = {name: rows * kin[name] for name, _ in shapes}
+    y_sizes = {name: rows * nout[name] for name, _ in shapes}
+    host_x_slab, host_xv = slab(x_sizes, True)
+    host_y_slab, host_yv = slab(y_sizes, True)
+    dev_x_slab, dev_xv = slab(x_sizes, False)
+    dev_y_slab, dev_yv = slab(y_sizes, False)
+    host_x = {name: host_xv[name].view(rows, kin[name]) for name, _ in shapes}
+    host_y = {name: host_yv[name].view(rows, nout[name]) for name, _ in shapes}
+    dev_x = {name: dev_xv[name].view(rows, kin[name]) for name, _ in shapes}
+    dev_y = {name: dev_yv[name].view(rows, nout[name]) for name, _ in shapes}
+    for i, (name, _) in enumerate(shapes):
+        host_x[name].copy_(synthetic.activations(rows, kin[name], 31 + i))
+    dev_x_slab.copy_(host_x_slab)
     torch.cuda.synchronize()
 
     if args.lanes:
@@ -512,12 +532,10 @@ def run_b200(args) -> None:
             with torch.cuda.graph(graph, stream=stream):
                 for i in range(first, first + count):
                     if with_copies:
-                        for name, _ in shapes:
-                            dev_x[name].copy_(host_x[name], non_blocking=True)
+                        dev_x_slab.copy_(host_x_slab, non_blocking=True)
                     step(i, use_pdl)
                     if with_copies:
-                        for name, _ in shapes:
-                            host_y[name].copy_(dev_y[name], non_blocking=True)
+                        host_y_slab.copy_(dev_y_slab, non_blocking=True)
         return graph
 
     try:

@@ -203,6 +203,86 @@ __global__ void __launch_bounds__(128) router_tiles_kernel(const __nv_bfloat16* 
   }
 }
 
+// The same arithmetic from shared memory: a block of four warps takes 64 rows x 32 experts, 64 inputs a step, staged by
+// 16-byte cp.async copies into 128-byte rows with the chunk index xor-ed by the row (conflict-free ldmatrix), two
+// buffers.  Each (row, expert) accumulator sees the same m16n8k16 operands in the same order as in
+// router_tiles_kernel, so both give the same bits; this one reads x once per 32 experts instead of once per 16 and
+// fetches fragments with ldmatrix instead of 4-byte global loads.
+__device__ __forceinline__ void router_ldm4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+__global__ void __launch_bounds__(128) router_tiles_staged_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int rows,
+                                                                  int d, const __nv_bfloat16* __restrict__ w, int ne,
+                                                                  float* __restrict__ out, int64_t ldo) {
+  __shared__ __align__(128) uint8_t sx[2][64 * 128];
+  __shared__ __align__(128) uint8_t sw[2][32 * 128];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int e0 = blockIdx.x * 32, r0 = blockIdx.y * 64;
+  const int chunks = d / 64;
+  auto stage = [&](int c, int buf) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {                              // 64 rows x 8 pieces of 16 bytes
+      const int p = tid + 128 * i, row = p >> 3, ch = p & 7;
+      const __nv_bfloat16* src = x + static_cast<int64_t>(min(r0 + row, rows - 1)) * ldx + c * 64 + ch * 8;
+      const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(sx[buf] + row * 128 + ((ch ^ (row & 7)) << 4)));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {                              // 32 experts x 8 pieces
+      const int p = tid + 128 * i, row = p >> 3, ch = p & 7;
+      const __nv_bfloat16* src = w + static_cast<int64_t>(min(e0 + row, ne - 1)) * d + c * 64 + ch * 8;
+      const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(sw[buf] + row * 128 + ((ch ^ (row & 7)) << 4)));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float acc[4][4] = {};
+  stage(0, 0);
+  for (int c = 0; c < chunks; ++c) {
+    const int buf = c & 1;
+    if (c + 1 < chunks) {
+      stage(c + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const uint32_t xs = static_cast<uint32_t>(__cvta_generic_to_shared(sx[buf]));
+    const uint32_t ws = static_cast<uint32_t>(__cvta_generic_to_shared(sw[buf]));
+#pragma unroll
+    for (int k16 = 0; k16 < 4; ++k16) {
+      uint32_t a[4], b0[4], b1[4];
+      {
+        const int row = 16 * warp + (lane & 15), ch = 2 * k16 + (lane >> 4);
+        router_ldm4(a, xs + row * 128 + ((ch ^ (row & 7)) << 4));       // rows 0-7 / 8-15 x inputs 0-7 / 8-15 of the step
+      }
+      {
+        const int row = (lane & 7) + 8 * (lane >> 4), ch = 2 * k16 + ((lane >> 3) & 1);
+        router_ldm4(b0, ws + row * 128 + ((ch ^ (row & 7)) << 4));       // experts 0-15: (b0, b1) of two n8 tiles
+        router_ldm4(b1, ws + (row + 16) * 128 + ((ch ^ (row & 7)) << 4));   // experts 16-31 ((row + 16) & 7 == row & 7)
+      }
+      router_mma(acc[0], a[0], a[1], a[2], a[3], b0[0], b0[1]);
+      router_mma(acc[1], a[0], a[1], a[2], a[3], b0[2], b0[3]);
+      router_mma(acc[2], a[0], a[1], a[2], a[3], b1[0], b1[1]);
+      router_mma(acc[3], a[0], a[1], a[2], a[3], b1[2], b1[3]);
+    }
+    __syncthreads();                                          // the buffer is staged again two steps on
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = e0 + 8 * j + 2 * t;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = r0 + 16 * warp + g + 8 * h;
+      if (r < rows && c < ne) out[r * ldo + c] = acc[j][2 * h];
+      if (r < rows && c + 1 < ne) out[r * ldo + c + 1] = acc[j][2 * h + 1];
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // top-k: one warp per row
 // ---------------------------------------------------------------------------------------------------------------------
@@ -378,9 +458,16 @@ int tf_moe_router_tiles(const void* x, int64_t ldx, int rows, int d, const void*
   if (d % 16 || ldx % 2 || reinterpret_cast<uintptr_t>(x) % 4 || reinterpret_cast<uintptr_t>(w) % 4)
     return fail_moe(TF_ERR_ARG, "tf_moe_router_tiles: d must be a multiple of 16, rows of x and w 4-byte aligned");
   if (rows > 65535 * 16) return fail_moe(TF_ERR_ARG, "tf_moe_router_tiles: too many rows");
-  dim3 grid((ne + 63) / 64, (rows + 15) / 16);
-  router_tiles_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x), ldx, rows, d,
-                                                                           static_cast<const __nv_bfloat16*>(w), ne, out, ldo);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
+  if (d % 64 == 0 && ldx % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
+    dim3 grid((ne + 31) / 32, (rows + 63) / 64);             // staged through shared memory: the same bits, faster
+    router_tiles_staged_kernel<<<grid, 128, 0, st>>>(xp, ldx, rows, d, wp, ne, out, ldo);
+  } else {
+    dim3 grid((ne + 63) / 64, (rows + 15) / 16);
+    router_tiles_kernel<<<grid, 128, 0, st>>>(xp, ldx, rows, d, wp, ne, out, ldo);
+  }
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_router_tiles");
 }

@@ -38,6 +38,9 @@ def test_router_and_topk_match_the_oracle():
     assert np.abs(tiles.cpu().numpy() - ref).max() <= 1e-4 * np.abs(ref).max()          # ragged rows (33) and experts (129)
     assert torch.equal(moe.router(x[17:18].to(DEV), wr.to(DEV), prefill=True), tiles[17:18])
     assert torch.equal(moe.router(x[:32].to(DEV), wr[:16].to(DEV), prefill=True), tiles[:32, :16])
+    wide = torch.zeros((rows, d + 2), dtype=torch.bfloat16)            # rows 4 bytes off the 16-byte grid: the kernel
+    wide[:, :d] = x                                                    # that reads fragments straight from global memory
+    assert torch.equal(moe.router(wide.to(DEV)[:, :d], wr.to(DEV), prefill=True), tiles)   # gives the staged kernel's bits
 
     class Cfg:
         num_experts_per_tok, num_experts, moe_intermediate_size, hidden_size = k, e, 64, 64
