@@ -475,11 +475,11 @@ def run_b200(args) -> None:
 
     if args.lanes:
         _lib.check(_lib.lib().tf_tune(b"qmm_lanes", args.lanes), "tune")
-    splits = {name: (qmm.split_k(nout[name], kin[name], GS, args.sk_target) if args.sk_target
-                     else qmm.default_split(nout[name], kin[name], GS)) for name, _ in shapes}
-    reduced = {}
-
     branches = not args.no_branches
+    paired = ("gate_proj", "up_proj") if branches else ()    # forked as an equal pair: each aims for half the machine
+    splits = {name: (qmm.split_k(nout[name], kin[name], GS, args.sk_target) if args.sk_target
+                     else qmm.default_split(nout[name], kin[name], GS, share=2 if name in paired else 1)) for name, _ in shapes}
+    reduced = {}
 
     def step(i: int, pdl: bool) -> None:
         layer = layers[i % ring]
@@ -598,7 +598,8 @@ def run_b200(args) -> None:
     if not args.no_extras:
         if world == 1:
             extras["moe_layer"] = moe_layer_bench(dev)
-            extras["dense_rows"] = dense_rows_bench(dev, layers, shapes, ring, splits)
+            extras["dense_rows"] = dense_rows_bench(dev, layers, shapes, ring,
+                                                    {name: qmm.default_split(nout[name], kin[name], GS) for name, _ in shapes})
             del layers
             torch.cuda.empty_cache()
             extras["stacked_layer"] = stacked_layer_bench(dev)

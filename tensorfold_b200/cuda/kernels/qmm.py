@@ -85,10 +85,12 @@ def split_k(n: int, k: int, gs: int = 64, target: int = 192) -> int:
 LANE_TARGET = 600      # 64-column tiles x slices this build aims for (measured on B200: about four blocks per SM)
 
 
-def default_split(n: int, k: int, gs: int = 64) -> int:
-    """The K slices ``matmul`` uses when it is given none: ``split_k`` with this build's occupancy target."""
+def default_split(n: int, k: int, gs: int = 64, share: int = 1) -> int:
+    """The K slices ``matmul`` uses when it is given none: ``split_k`` with this build's occupancy target.  ``share`` > 1
+    is for a launch that runs side by side with ``share - 1`` others of its size (``fork_join`` of gate and up): each
+    aims for its share of the machine, which means fewer, longer slices."""
 
-    return split_k(n, k, gs, LANE_TARGET)
+    return split_k(n, k, gs, max(1, LANE_TARGET // max(1, share)))
 
 
 def bucket(m: int) -> int:
