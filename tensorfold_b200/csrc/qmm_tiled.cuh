@@ -123,17 +123,19 @@ struct QmmGeo {
   static constexpr int XS_OFF = W_OFF + KW * W_BYTES;
   static constexpr int STAGE = (XS_OFF + XS_BYTES + 1023) / 1024 * 1024;
   static constexpr int RED_BYTES = KW * ROWS * RED_STRIDE * 4;
+  // slices pushed by the cluster's blocks: 16 pieces of 32 bytes a row and lane (+ one piece a slice of rounding)
+  static constexpr int RECV_BYTES = KW * ROWS * 512 + 8 * 32;
   static constexpr int BUDGET = (MT > 2 ? 110 : KW == 1 ? TF_BUDGET1_KB : KW == 2 ? TF_BUDGET2_KB : TF_BUDGET4_KB) * 1024;
-  static constexpr int NST_A = BUDGET / STAGE, NST_B = (RED_BYTES + STAGE - 1) / STAGE;
+  static constexpr int NST_A = BUDGET / STAGE, NST_B = (RED_BYTES + RECV_BYTES + STAGE - 1) / STAGE;
   static constexpr int NST_C = NST_A < 2 ? 2 : (NST_A > 12 ? 12 : NST_A);
   static constexpr int NST = NST_C < NST_B ? NST_B : NST_C;
-  static constexpr int BAR_BYTES = 3 * NST * 8 + 16;
+  static constexpr int BAR_BYTES = 3 * NST * 8 + 8 + 16;   // full, empty, sums per stage; the receive barrier; abort flag
   static constexpr int SMEM = NST * STAGE + BAR_BYTES + 1024;     // + slack to align the first stage
   // blocks per SM the register file should allow (64 registers a thread is the floor the kernel needs)
   static constexpr int BY_SMEM = (227 * 1024) / (SMEM + 1024), BY_REGS = 65536 / (THREADS * (MT == 2 ? 80 : 64));
   static constexpr int MINB = MT > 2 ? 1 : (BY_SMEM < BY_REGS ? BY_SMEM : BY_REGS) < 1 ? 1 : (BY_SMEM < BY_REGS ? BY_SMEM : BY_REGS);
   static_assert(STAGE % 1024 == 0 && W_BYTES % 16 == 0 && XS_OFF % 16 == 0, "stage parts stay aligned");
-  static_assert(NST * STAGE >= RED_BYTES, "the output staging tile reuses the stage memory");
+  static_assert(NST * STAGE >= RED_BYTES + RECV_BYTES, "the output staging tile and the receive area reuse the stage memory");
   static_assert(SMEM <= 227 * 1024, "fits the shared memory of an SM");
 };
 
@@ -174,7 +176,8 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + NST * Geo::STAGE);   // weights and x of a stage have landed
   uint64_t* empty = full + NST;                                           // every consumer warp is done with a stage
   uint64_t* sums = empty + NST;                                           // the stage's group sums are written
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sums + NST);
+  uint64_t* recv_bar = sums + NST;                                        // every block of the cluster has pushed its slice
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(recv_bar + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef TF_TRACE
@@ -222,6 +225,7 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
       mbar_init(empty + i, CONSUMERS);
       mbar_init(sums + i, 1);
     }
+    mbar_init(recv_bar, p.sk);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -478,7 +482,6 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
 #endif
 
   const bool failed = *abort_flag != 0;
-  const int share = clustered ? p.sk : 1, mine_rank = clustered ? slice : 0;
   if (!failed && p.epi == 2) {
     // SwiGLU: a tile pair holds 16 gate columns then the 16 up columns of the same outputs; out has N / 2 columns (bf16)
     const int nout = p.N / 2;
@@ -493,39 +496,11 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
       for (int e = 0; e < valid; ++e) dst[e] = __float2bfloat16_rn(swiglu_f(src[e], src[16 + e], p.limit));
     }
   } else if (!failed) {
-    // 8-column pieces of the block's tiles; piece idx belongs to slice idx % share.  A block's own pieces go to
-    // consecutive threads, so (up to THREADS of them) they are summed in one round of remote loads.
-    for (int idx = tid * share + mine_rank; idx < lanes_here * ROWS * 16; idx += THREADS * share) {
-      const int kw = idx / (ROWS * 16), rem = idx % (ROWS * 16);
-      const int ml = rem >> 4, c8 = (rem & 15) * 8, n = (sb0 + kw) * SB_COLS + c8;
-      if (ml >= rows_here || n >= p.N) continue;
+    // One 8-column piece (row ml of lane kw, columns c8 .. c8 + 7) goes out: epilogue, then slices / fp32 / bf16.
+    auto emit = [&](float (&v)[8], int kw, int ml, int c8) {
+      const int n = (sb0 + kw) * SB_COLS + c8;
+      if (n >= p.N) return;
       const int64_t m = grouped ? p.members[first + ml] : m0 + ml;
-      const int off = kw * RED_TILE + ml * RED_STRIDE + c8;
-      float v[8];
-      if (clustered) {
-        // slice order ((s0 + s1) + s2) + ...: slice s is block s of the cluster.  All remote loads are issued before
-        // the first add so their latencies overlap (a cluster holds at most 8 slices).
-        float4 lo[8], hi[8];
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-          if (s < p.sk) {
-            const float* src = (s == slice ? red : cluster.map_shared_rank(red, s)) + off;
-            lo[s] = *reinterpret_cast<const float4*>(src);
-            hi[s] = *reinterpret_cast<const float4*>(src + 4);
-          }
-        v[0] = lo[0].x, v[1] = lo[0].y, v[2] = lo[0].z, v[3] = lo[0].w;
-        v[4] = hi[0].x, v[5] = hi[0].y, v[6] = hi[0].z, v[7] = hi[0].w;
-#pragma unroll
-        for (int s = 1; s < 8; ++s)
-          if (s < p.sk) {
-            v[0] += lo[s].x, v[1] += lo[s].y, v[2] += lo[s].z, v[3] += lo[s].w;
-            v[4] += hi[s].x, v[5] += hi[s].y, v[6] += hi[s].z, v[7] += hi[s].w;
-          }
-      } else {
-        const float4 lo = *reinterpret_cast<const float4*>(red + off);
-        const float4 hi = *reinterpret_cast<const float4*>(red + off + 4);
-        v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
-      }
       const int valid = min(8, p.N - n);
       if (p.epi == 1) {
 #pragma unroll
@@ -555,9 +530,68 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
           for (int e = 0; e < valid; ++e) dst[e] = __float2bfloat16_rn(v[e]);
         }
       }
+    };
+    const int pieces = lanes_here * ROWS * 16;              // 8-column pieces of the block's tiles
+    if (clustered) {
+      // Piece idx is summed by block idx % sk of the cluster.  Every block PUSHES its pieces into their owners' receive
+      // areas (slot [slice][idx / sk], 32 bytes; the area sits behind the staging tile in every block's stage memory,
+      // free since the cluster barrier above), then arrives on each owner's receive barrier.  An owner that has seen
+      // all sk arrivals holds every slice of its pieces locally, sums them in slice order and may leave: nothing is
+      // read remotely and no second cluster barrier is needed (a block is written to only before its own last wait).
+      const int per_owner = (pieces + p.sk - 1) / p.sk;
+      float* recv = red + (Geo::RED_BYTES + 15) / 16 * 4;     // [sk][per_owner][8], the same place in every block
+      for (int idx = tid; idx < pieces; idx += THREADS) {
+        const int kw = idx / (ROWS * 16), rem = idx % (ROWS * 16), ml = rem >> 4, c8 = (rem & 15) * 8;
+        if (ml >= rows_here) continue;
+        const float* src = red + kw * RED_TILE + ml * RED_STRIDE + c8;
+        float* dst = cluster.map_shared_rank(recv, idx % p.sk) + (static_cast<int64_t>(slice) * per_owner + idx / p.sk) * 8;
+        *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+        *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
+      }
+      __syncthreads();                                        // every thread's pushes come before the arrivals
+      if (tid < p.sk) mbar_arrive_cluster(recv_bar, tid);
+      if (!mbar_wait_cluster(recv_bar, 0, abort_flag)) {
+        give_up(ERR_WAIT_FULL);
+      } else {
+        for (int j = tid; j * p.sk + slice < pieces; j += THREADS) {
+          const int idx = j * p.sk + slice;
+          const int kw = idx / (ROWS * 16), rem = idx % (ROWS * 16), ml = rem >> 4, c8 = (rem & 15) * 8;
+          if (ml >= rows_here) continue;
+          float v[8];
+          {
+            const float4 lo = *reinterpret_cast<const float4*>(recv + j * 8);
+            const float4 hi = *reinterpret_cast<const float4*>(recv + j * 8 + 4);
+            v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
+          }
+          for (int sl = 1; sl < p.sk; ++sl) {                 // slice order ((s0 + s1) + s2) + ...
+            const float* src = recv + (static_cast<int64_t>(sl) * per_owner + j) * 8;
+            const float4 lo = *reinterpret_cast<const float4*>(src);
+            const float4 hi = *reinterpret_cast<const float4*>(src + 4);
+            v[0] += lo.x, v[1] += lo.y, v[2] += lo.z, v[3] += lo.w, v[4] += hi.x, v[5] += hi.y, v[6] += hi.z, v[7] += hi.w;
+          }
+          emit(v, kw, ml, c8);
+        }
+      }
+    } else {
+      for (int idx = tid; idx < pieces; idx += THREADS) {
+        const int kw = idx / (ROWS * 16), rem = idx % (ROWS * 16), ml = rem >> 4, c8 = (rem & 15) * 8;
+        if (ml >= rows_here) continue;
+        const float* src = red + kw * RED_TILE + ml * RED_STRIDE + c8;
+        const float4 lo = *reinterpret_cast<const float4*>(src);
+        const float4 hi = *reinterpret_cast<const float4*>(src + 4);
+        float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        emit(v, kw, ml, c8);
+      }
     }
   }
-  if (clustered) cluster.sync();                            // peers may still be reading this block's tiles
+  if (failed && clustered) {
+    // a block that gave up pushes nothing, but it still tells its peers and stays until they have pushed (or their
+    // own waits run out): they write into this block's shared memory
+    __syncthreads();
+    if (tid < p.sk) mbar_arrive_cluster(recv_bar, tid);
+    volatile int never = 0;
+    mbar_wait_cluster(recv_bar, 0, &never);
+  }
 #ifdef TF_TRACE
   __syncthreads();
   if (tid == 0 && p.xs == nullptr && p.part != nullptr && p.cluster) {

@@ -93,6 +93,32 @@ __device__ __forceinline__ bool mbar_wait_ready(uint64_t* bar, uint32_t parity, 
   return mbar_wait(bar, parity, abort_flag);
 }
 
+// Arrival on the same barrier in block `cta` of this cluster; the arriving thread's (and, through a preceding
+// __syncthreads, its block's) earlier writes to that block's shared memory are visible to whoever sees the phase flip.
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(bar)), "r"(cta));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+// Bounded wait (whole warp, like mbar_wait) that acquires at cluster scope: for barriers other blocks arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
+  bool ok = false;
+  for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity), "r"(20000u)
+        : "memory");
+    if (done) {
+      ok = true;
+      break;
+    }
+    if ((i & 255u) == 255u && *abort_flag) break;
+  }
+  return __all_sync(0xFFFFFFFFu, ok);
+}
+
 // Bounded wait for a lane that already probed once: loops only if `ready` is false; uniform result across the warp.
 __device__ __forceinline__ bool mbar_wait_probed(bool ready, uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
   if (__all_sync(0xFFFFFFFFu, ready)) return true;
