@@ -13,10 +13,12 @@
 //
 // Block = KW column lanes x 4 consumer warps (a lane streams one 128-column super-block over the block's K slice; each
 // of its warps owns 32 columns and all rows of the row tile) + a copy warp (one bulk copy per lane and stage for the
-// packed weights, 16-byte asynchronous copies for the rows of x, which all lanes share) + a sums warp that computes the
-// group sums of x once for the whole block.  The blocks that hold the K slices of the same columns form a thread-block
-// cluster; the slices are summed in slice order through distributed shared memory.  When the caller wants the slices,
-// or there are more than a cluster can hold, they go to `part` in global memory.  Geometry never changes a bit.
+// packed weights; tensor-map copies into 128-byte-swizzled half tiles for the rows of x, which all lanes share, 16-byte
+// asynchronous copies in the grouped form that gathers rows) + a sums warp that computes the group sums of x once for
+// the whole block.  The blocks that hold the K slices of the same columns form a thread-block cluster: after one
+// cluster barrier every block pushes its slice of each 8-column piece into the shared memory of the block that owns
+// the piece, and the owner adds the slices in slice order.  When the caller wants the slices, or there are more than a
+// cluster can hold, they go to `part` in global memory.  Geometry never changes a bit.
 #pragma once
 
 #include <cooperative_groups.h>
