@@ -526,11 +526,67 @@ def run_b200(args) -> None:
     stream = torch.cuda.Stream()
     pdl = not args.no_pdl and world == 1
 
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    names = [name for name, _ in shapes]
+
+    def span(sizes, first_name, last_name):                  # [from, to) of consecutive projections in a slab
+        at = 0
+        for name in names:
+            if name == first_name:
+                lo = at
+            at += sizes[name]
+            if name == last_name:
+                return lo, at
+        raise KeyError(last_name)
+
+    def e2e_step(i: int) -> None:
+        """One layer with its copies overlapped: q/k/v's rows go in first, the other inputs while q/k/v run; each set's
+        results leave for the host while the next set computes.  Every byte of the step still crosses in the step."""
+
+        layer = layers[i % ring]
+        main = torch.cuda.current_stream()
+
+        def mm(name: str):
+            return lambda: qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=False, sk=splits[name])
+
+        def after(stream_to, fn):                           # fn on stream_to once everything queued on main is done
+            ev = torch.cuda.Event()
+            ev.record(main)
+            stream_to.wait_event(ev)
+            with torch.cuda.stream(stream_to):
+                fn()
+
+        def result(first_name, last_name):
+            lo, hi = span(y_sizes, first_name, last_name)
+            after(copy_out, lambda: host_y_slab[lo:hi].copy_(dev_y_slab[lo:hi], non_blocking=True))
+
+        lo, hi = span(x_sizes, "q_proj", "v_proj")
+        rest = span(x_sizes, "o_proj", "down_proj")
+        after(copy_in, lambda: dev_x_slab[rest[0]:rest[1]].copy_(host_x_slab[rest[0]:rest[1]], non_blocking=True))
+        staged = torch.cuda.Event()
+        staged.record(copy_in)
+        dev_x_slab[lo:hi].copy_(host_x_slab[lo:hi], non_blocking=True)
+        qmm.fork_join([mm("q_proj"), mm("k_proj"), mm("v_proj")])
+        result("q_proj", "v_proj")
+        main.wait_event(staged)
+        mm("o_proj")()
+        result("o_proj", "o_proj")
+        qmm.fork_join([mm("gate_proj"), mm("up_proj")])
+        result("gate_proj", "up_proj")
+        mm("down_proj")()
+        result("down_proj", "down_proj")
+        done = torch.cuda.Event()
+        done.record(copy_out)
+        main.wait_event(done)
+
     def capture(first: int, count: int, with_copies: bool, use_pdl: bool):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(stream):
             with torch.cuda.graph(graph, stream=stream):
                 for i in range(first, first + count):
+                    if with_copies and world == 1 and branches:
+                        e2e_step(i)
+                        continue
                     if with_copies:
                         dev_x_slab.copy_(host_x_slab, non_blocking=True)
                     step(i, use_pdl)
