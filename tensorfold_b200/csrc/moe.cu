@@ -364,6 +364,45 @@ __global__ void combine_kernel(const void* __restrict__ y, const float* __restri
   if (c + 1 < d) out[static_cast<int64_t>(r) * d + c + 1] = __float2bfloat16_rn(a1);
 }
 
+// The same sums, eight columns a thread with 16-byte loads (d a multiple of 8, y and out 16-byte aligned): every
+// element still takes its slots in slot order with one fma each, so the bits are those of combine_kernel.
+template <bool YBF16>
+__global__ void __launch_bounds__(128) combine_wide_kernel(const void* __restrict__ y, const float* __restrict__ wts, int rows,
+                                                           int slots, int d, __nv_bfloat16* __restrict__ out) {
+  const int r = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (r >= rows || c >= d) return;
+  float a[8] = {};
+#pragma unroll 3
+  for (int k = 0; k < slots; ++k) {
+    const float w = wts[r * slots + k];
+    if (w == 0.f) continue;                                      // a slot another rank owns: its y is never read
+    const int64_t off = (static_cast<int64_t>(r) * slots + k) * d + c;
+    float v[8];
+    if (YBF16) {
+      const uint4 q = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(y) + off);
+      const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(u[i] << 16);
+        v[2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
+      }
+    } else {
+      const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(y) + off);
+      const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(y) + off + 4);
+      v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = fmaf(w, v[i], a[i]);
+  }
+  uint4 o;
+  __nv_bfloat162 t0 = __floats2bfloat162_rn(a[0], a[1]), t1 = __floats2bfloat162_rn(a[2], a[3]);
+  __nv_bfloat162 t2 = __floats2bfloat162_rn(a[4], a[5]), t3 = __floats2bfloat162_rn(a[6], a[7]);
+  o.x = *reinterpret_cast<uint32_t*>(&t0), o.y = *reinterpret_cast<uint32_t*>(&t1);
+  o.z = *reinterpret_cast<uint32_t*>(&t2), o.w = *reinterpret_cast<uint32_t*>(&t3);
+  *reinterpret_cast<uint4*>(out + static_cast<int64_t>(r) * d + c) = o;
+}
+
 }  // namespace
 
 }  // namespace tf
@@ -484,8 +523,15 @@ int tf_moe_topk(const float* logits, int64_t ldl, int rows, int experts, int top
 
 int tf_moe_combine(const void* y, int y_bf16, const float* wts, int rows, int slots, int d, void* out, void* stream) {
   if (rows < 1 || slots < 1 || d < 1 || !y || !wts || !out || rows > 65535) return fail_moe(TF_ERR_ARG, "tf_moe_combine: bad arguments");
-  dim3 grid((d / 2 + 127) / 128 + 1, rows);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (d % 8 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+    dim3 wide((d / 8 + 127) / 128, rows);
+    if (y_bf16) combine_wide_kernel<true><<<wide, 128, 0, s>>>(y, wts, rows, slots, d, static_cast<__nv_bfloat16*>(out));
+    else combine_wide_kernel<false><<<wide, 128, 0, s>>>(y, wts, rows, slots, d, static_cast<__nv_bfloat16*>(out));
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_combine");
+  }
+  dim3 grid((d / 2 + 127) / 128 + 1, rows);
   if (y_bf16) combine_kernel<true><<<grid, 128, 0, s>>>(y, wts, rows, slots, d, static_cast<__nv_bfloat16*>(out));
   else combine_kernel<false><<<grid, 128, 0, s>>>(y, wts, rows, slots, d, static_cast<__nv_bfloat16*>(out));
   const cudaError_t e = cudaGetLastError();

@@ -64,6 +64,12 @@ def test_combine_is_slot_ordered_fp32():
     assert np.abs(out.float().cpu().numpy() - ref).max() <= 2 ** -8 * np.abs(ref).max()
     out16 = moe.combine(y.to(torch.bfloat16).to(DEV), w.to(DEV))
     assert torch.equal(out16[3:4], moe.combine(y[3:4].to(torch.bfloat16).to(DEV), w[3:4].to(DEV)))
+    w[:, 2] = 0                                                        # a slot that is skipped
+    for dtype in (torch.float32, torch.bfloat16):                      # 336 columns: 16-byte loads; 337: the scalar kernel
+        wide = torch.randn((19, 7, 337), generator=g).to(dtype)
+        a = moe.combine(wide[:, :, :336].contiguous().to(DEV), w.to(DEV))
+        b = moe.combine(wide.to(DEV), w.to(DEV))
+        assert torch.equal(a, b[:, :336])
 
 
 def layer(d, e, ni, shared_ni, gs, top_k, seed):
