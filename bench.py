@@ -478,7 +478,7 @@ def run_b200(args) -> None:
     branches = not args.no_branches
     paired = ("gate_proj", "up_proj") if branches else ()    # forked as an equal pair: each aims for half the machine
     splits = {name: (qmm.split_k(nout[name], kin[name], GS, args.sk_target) if args.sk_target
-                     else qmm.default_split(nout[name], kin[name], GS, share=2 if name in paired else 1)) for name, _ in shapes}
+                     else qmm.default_split(nout[name], kin[name], GS, share=args.pair_share if name in paired else 1)) for name, _ in shapes}
     reduced = {}
 
     def step(i: int, pdl: bool) -> None:
@@ -744,6 +744,7 @@ def main() -> None:
     ap.add_argument("--prefill", action="store_true", help="with --case: the prefill arithmetic (tcgen05 kernel)")
     ap.add_argument("--no-branches", action="store_true", help="launch the seven projections one after another")
     ap.add_argument("--no-chain-pdl", action="store_true", help="with branches: programmatic launch for q_proj only")
+    ap.add_argument("--pair-share", type=int, default=2, help="tuning: share of the machine gate/up aim for when forked")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE layer / row-count sweeps reported beside the headline")
     ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")

@@ -82,3 +82,16 @@ def test_gloo_ranks_agree_bit_for_bit_and_sum_in_rank_order(tmp_path, world):
     want = oaff.sum_rank_partials([g[0].numpy() for g in got])
     for local, summed in got:
         assert torch.equal(summed.float(), torch.from_numpy(want))
+
+
+def test_default_split_share_asks_for_fewer_longer_slices():
+    """Launches forked in pairs (gate and up) aim for half the machine each: fewer K slices, never more."""
+
+    from tensorfold_b200.cuda.kernels import qmm
+
+    assert qmm.default_split(17408, 5120) == 4 and qmm.default_split(17408, 5120, share=2) == 2
+    assert qmm.default_split(6144, 5120) == qmm.default_split(6144, 5120, share=1) == 8
+    for n, k in ((1024, 5120), (5120, 17408), (17408, 5120), (256, 512)):
+        for share in (1, 2, 3, 4):
+            assert 1 <= qmm.default_split(n, k, share=share) <= qmm.default_split(n, k)
+            assert (k // 64) % qmm.default_split(n, k, share=share) == 0
