@@ -80,19 +80,6 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xFFFFFFFFu, ok != 0);
 }
 
-// The same for a barrier that is normally complete already: one non-blocking test first (a test is cheaper than a
-// potentially suspending try_wait), the bounded wait only if it fails.
-__device__ __forceinline__ bool mbar_wait_ready(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok)
-      : "r"(smem_addr(bar)), "r"(parity)
-      : "memory");
-  if (__all_sync(0xFFFFFFFFu, ok != 0)) return true;
-  return mbar_wait(bar, parity, abort_flag);
-}
-
 // Arrival on the same barrier in block `cta` of this cluster; the arriving thread's (and, through a preceding
 // __syncthreads, its block's) earlier writes to that block's shared memory are visible to whoever sees the phase flip.
 __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta) {
@@ -174,16 +161,6 @@ __device__ __forceinline__ void mma_bf16_zero(float (&d)[4], const uint32_t (&a)
       "{%10, %10, %10, %10};"
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
-}
-
-// (d0, d1) = (a0 * b + c0, a1 * b + c1), two IEEE fp32 fmas in one sm_100 instruction.
-__device__ __forceinline__ void fma2(float& c0, float& c1, float a0, float a1, float b) {
-  uint64_t a, bb, c;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
-  asm("mov.b64 %0, {%1, %1};" : "=l"(bb) : "f"(b));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "f"(c0), "f"(c1));
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c) : "l"(a), "l"(bb));
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(c0), "=f"(c1) : "l"(c));
 }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
