@@ -1,5 +1,5 @@
 """The projection record the kernels' callers pass around.  Mirrors ``QLinear`` of the reference
-(families/qwen3_5/cuda/weights.py:14-40); checkpoint loading itself is outside this build."""
+(families/qwen3_5/cuda/weights.py:14-40); ``tensorfold_b200.cuda.checkpoint`` fills it from safetensors files."""
 
 from __future__ import annotations
 
