@@ -172,6 +172,16 @@ int tf_affine_rows(const void* ids, int ids64, int rows, const void* words, cons
  * rank0.float() + rank1.float() of families/qwen3_5/cuda/distributed.py:281-284. */
 int tf_sum_ranks(const void* parts, int world, int64_t total, int parts_bf16, void* out, int out_f32, void* stream);
 
+/* Glue that feeds the matmuls (rows contiguous, bf16, 16-byte aligned; d a multiple of gs; one block a row, so a row's
+ * bits do not depend on the row count).
+ * tf_add_rmsnorm: h = bf16(x + r) (r and h may be null: then h = x), y = bf16(h * inv * w) with
+ * inv = 1 / sqrt(mean(h^2) + eps) in fp32, xs[row, g] = fp32 sum of y over group g (xs may be null).
+ * tf_swiglu: out = bf16(g * sigmoid(g) * u) in fp32 with one rounding, xs as above.
+ * Replace the Triton `_add_rmsnorm` and `_swiglu` of families/qwen3_5/cuda/glue.py:10-40,130-151. */
+int tf_add_rmsnorm(const void* x, const void* r, const void* w, int rows, int d, float eps, void* h, void* y, float* xs,
+                   int gs, void* stream);
+int tf_swiglu(const void* gate, const void* up, int rows, int n, void* out, float* xs, int gs, void* stream);
+
 /* Prefill matmul on tcgen05 / tensor memory: every weight rounded once to bf16, w = bf16(fma(q, s, b)), then one fp32
  * accumulation chain over K; any chunking of the rows gives the same bits (not the bits of tf_qmm).  4-bit weights,
  * groups of 32 or 64, k % 64 == 0.  x: [m, k] bf16, 16-byte aligned rows (ldx % 8 == 0); out: [m, n] bf16 or fp32.

@@ -43,6 +43,8 @@ SIGNATURES = {
     "tf_moe_topk": (_i32, (_vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp)),
     "tf_moe_combine": (_i32, (_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp)),
     "tf_affine_rows": (_i32, (_vp, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp)),
+    "tf_add_rmsnorm": (_i32, (_vp, _vp, _vp, _i32, _i32, ctypes.c_float, _vp, _vp, _vp, _i32, _vp)),
+    "tf_swiglu": (_i32, (_vp, _vp, _i32, _i32, _vp, _vp, _i32, _vp)),
     "tf_sum_ranks": (_i32, (_vp, _i32, _i64, _i32, _vp, _i32, _vp)),
     "tf_qmm_prefill": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _i64, _i32, _vp)),
     "tf_qmm_prefill_act": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _i64, _i32, _i32, ctypes.c_float, _vp)),
