@@ -21,7 +21,6 @@ from typing import Sequence
 
 import torch
 
-from ..families.qwen3_5.cuda import distributed
 from ..families.qwen3_5.cuda.weights import QLinear
 from .kernels import affine
 
@@ -245,4 +244,4 @@ def load_packed(ckpt: Checkpoint, prefix: str, device: torch.device | str, **kw)
     return qmm.pack(q.weight, q.scales, q.biases, q.gs, bits=q.bits)
 
 
-__all__ = ["ALIGN", "PIECE", "Spans", "read_header", "Entry", "Checkpoint", "load_packed", "distributed"]
+__all__ = ["ALIGN", "PIECE", "Spans", "read_header", "Entry", "Checkpoint", "load_packed"]
