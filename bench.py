@@ -407,6 +407,49 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
     return out
 
 
+def glue_bench(dev) -> dict:
+    """The row-wise glue that feeds the matmuls, at decode and prompt row counts: microseconds and bytes moved per
+    second (reads of the inputs, writes of the outputs and of the group sums) against the measured HBM peak.  A ring of
+    buffer sets larger than L2 keeps the figures honest."""
+
+    import torch
+
+    from tensorfold_b200 import synthetic
+    from tensorfold_b200.families.qwen3_5.cuda import glue
+
+    peak, _ = measured_peaks()
+    stream = torch.cuda.Stream()
+    d, n = 5120, 17408
+    out = {"add_rmsnorm": {}, "swiglu": {}}
+    for rows in (16, 2048):
+        ring = max(2, -(-3 * L2_BYTES // (8 * rows * d)))
+        ring = min(ring, 64)
+        xs = [synthetic.activations(rows, d, 3).to(dev) for _ in range(min(ring, 4))]
+        w = torch.ones((d,), dtype=torch.bfloat16, device=dev)
+        sets = [(xs[i % len(xs)].clone(), xs[(i + 1) % len(xs)].clone()) for i in range(ring)]
+        with torch.cuda.stream(stream):
+            glue.add_rmsnorm(sets[0][0], sets[0][1], w, 1e-6)
+            torch.cuda.synchronize()
+        _, times = graph_time(lambda i: glue.add_rmsnorm(sets[i % ring][0], sets[i % ring][1], w, 1e-6), 4 * ring, stream)
+        us = sorted(times)[len(times) // 2] * 1e3 / (4 * ring)
+        moved = 8 * rows * d + 4 * rows * (d // 64)
+        out["add_rmsnorm"][f"M{rows}"] = {"us": us, "gb_s": moved / us / 1e3, "of_measured_hbm": moved / us / 1e3 / peak}
+        del sets
+        ring = max(2, min(32, -(-3 * L2_BYTES // (6 * rows * n))))
+        gu = [(synthetic.activations(rows, n, 5 + i).to(dev), synthetic.activations(rows, n, 9 + i).to(dev)) for i in range(min(ring, 3))]
+        sets = [(gu[i % len(gu)][0].clone(), gu[i % len(gu)][1].clone()) for i in range(ring)]
+        with torch.cuda.stream(stream):
+            glue.swiglu(*sets[0])
+            torch.cuda.synchronize()
+        _, times = graph_time(lambda i: glue.swiglu(*sets[i % ring]), 4 * ring, stream)
+        us = sorted(times)[len(times) // 2] * 1e3 / (4 * ring)
+        moved = 6 * rows * n + 4 * rows * (n // 64)
+        out["swiglu"][f"M{rows}"] = {"us": us, "gb_s": moved / us / 1e3, "of_measured_hbm": moved / us / 1e3 / peak}
+        del sets, gu
+        torch.cuda.empty_cache()
+    return out
+
+
 def run_b200(args) -> None:
     import torch
     import torch.distributed as dist
@@ -651,15 +694,26 @@ def run_b200(args) -> None:
     ms, e2e_ms = times.tolist()
 
     extras = {}
-    if not args.no_extras:
-        if world == 1:
-            extras["moe_layer"] = moe_layer_bench(dev)
-            extras["dense_rows"] = dense_rows_bench(dev, layers, shapes, ring,
-                                                    {name: qmm.default_split(nout[name], kin[name], GS) for name, _ in shapes})
-            del layers
-            torch.cuda.empty_cache()
-            extras["stacked_layer"] = stacked_layer_bench(dev)
-        extras["moe_block"] = moe_block_tp_bench(dev, rank, world)
+    wanted = set() if args.no_extras else set(args.extras.split(","))
+
+    def extra(name: str, fn) -> None:                       # a failing side figure must not cost the headline line
+        if "all" not in wanted and name not in wanted:
+            return
+        try:
+            extras[name] = fn()
+        except Exception as exc:                             # noqa: BLE001 - reported in the line instead
+            extras[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
+    if world == 1:
+        extra("moe_layer", lambda: moe_layer_bench(dev))
+        extra("dense_rows", lambda: dense_rows_bench(dev, layers, shapes, ring,
+                                                     {name: qmm.default_split(nout[name], kin[name], GS) for name, _ in shapes}))
+        del layers
+        torch.cuda.empty_cache()
+        extra("stacked_layer", lambda: stacked_layer_bench(dev))
+        extra("glue", lambda: glue_bench(dev))
+    if "all" in wanted or "moe_block" in wanted:
+        extras["moe_block"] = moe_block_tp_bench(dev, rank, world)      # holds collectives: every rank runs it or none
 
     launches = args.steps * (len(shapes) + (2 if world > 1 else 0))
     io_bytes = sum(2 * rows * (n + k) for _, (n, k) in shapes)
@@ -747,6 +801,8 @@ def main() -> None:
     ap.add_argument("--pair-share", type=int, default=2, help="tuning: share of the machine gate/up aim for when forked")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE layer / row-count sweeps reported beside the headline")
+    ap.add_argument("--extras", default="all", help="which side figures to run: all, or a comma list of moe_layer, "
+                    "dense_rows, stacked_layer, glue, moe_block")
     ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")
     ap.add_argument("--sk-target", type=int, default=0, help="tuning: occupancy target of the K split (0 = default)")
     args = ap.parse_args()
