@@ -450,6 +450,62 @@ def glue_bench(dev) -> dict:
     return out
 
 
+def load_path_bench(dev, pack: bool = True) -> dict:
+    """Checkpoint -> device: one gate_proj-sized projection (4 copies, about 200 MB) written as a safetensors file in
+    the temporary directory, then read by byte range, uploaded and tiled.  GB/s of file bytes, whole and for the shard
+    rank 1 of 4 owns; whether reads went around the page cache depends on the box's file system."""
+
+    import tempfile
+    import time as _time
+
+    import torch
+
+    from tensorfold_b200 import synthetic
+    from tensorfold_b200.cuda import checkpoint
+    from tensorfold_b200.cuda.kernels import qmm
+
+    n, k = synthetic.DENSE_27B["gate_proj"]
+    w, sc, bi = synthetic.affine_weight(2048, k, BITS, GS, seed=77)
+    reps = -(-n // 2048)
+    tensors = {"weight": w.repeat(reps, 1)[:n].contiguous(), "scales": sc.repeat(reps, 1)[:n].contiguous(),
+               "biases": bi.repeat(reps, 1)[:n].contiguous()}
+    names = {torch.int32: "I32", torch.bfloat16: "BF16"}
+    out = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "layer.safetensors")
+        header, at = {}, 0
+        for i in range(4):
+            for key, t in tensors.items():
+                size = t.numel() * t.element_size()
+                header[f"l{i}.gate_proj.{key}"] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + size]}
+                at += size
+        text = json.dumps(header).encode()
+        with open(path, "wb") as f:
+            f.write(len(text).to_bytes(8, "little"))
+            f.write(text)
+            for i in range(4):
+                for t in tensors.values():
+                    f.write(t.view(torch.uint8).numpy().tobytes())
+        for label, kw in (("whole", {}), ("rank1_of_4_column", {"rank": 1, "world": 4, "parallel": "column"})):
+            spans = checkpoint.Spans()
+            ckpt = checkpoint.Checkpoint([path], spans)
+            on_gpu = torch.device(dev).type == "cuda"
+            if on_gpu:
+                torch.cuda.synchronize()
+            t0 = _time.perf_counter()
+            for i in range(4):
+                q = ckpt.linear(f"l{i}.gate_proj", device=dev, **kw)
+                if pack:
+                    q = qmm.pack(q.weight, q.scales, q.biases, GS)
+            if on_gpu:
+                torch.cuda.synchronize()
+            dt = _time.perf_counter() - t0
+            out[label] = {"file_mb": spans.bytes_read / 1e6, "ms": dt * 1e3, "gb_s": spans.bytes_read / dt / 1e9,
+                          "around_page_cache": bool(spans.direct)}
+            ckpt.close()
+    return out
+
+
 def run_b200(args) -> None:
     import torch
     import torch.distributed as dist
@@ -712,6 +768,7 @@ def run_b200(args) -> None:
         torch.cuda.empty_cache()
         extra("stacked_layer", lambda: stacked_layer_bench(dev))
         extra("glue", lambda: glue_bench(dev))
+        extra("load_path", lambda: load_path_bench(dev))
     if "all" in wanted or "moe_block" in wanted:
         extras["moe_block"] = moe_block_tp_bench(dev, rank, world)      # holds collectives: every rank runs it or none
 
@@ -802,7 +859,7 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE layer / row-count sweeps reported beside the headline")
     ap.add_argument("--extras", default="all", help="which side figures to run: all, or a comma list of moe_layer, "
-                    "dense_rows, stacked_layer, glue, moe_block")
+                    "dense_rows, stacked_layer, glue, load_path, moe_block")
     ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")
     ap.add_argument("--sk-target", type=int, default=0, help="tuning: occupancy target of the K split (0 = default)")
     args = ap.parse_args()
