@@ -10,7 +10,10 @@ Parity status
   were generated (``tests/golden/make_golden.py``): ``dequantize`` (families/qwen3_5/cuda/qmm.py:132-149),
   ``split_k`` / ``bucket`` (cuda/kernels/qmm.py:105-119), ``packed_shape`` / ``input_slice``
   (cuda/kernels/affine.py:9-27), ``max_items`` (cuda/experts.py:95-98), the partition map ``output_rows``
-  (families/qwen3_5/cuda/distributed.py:27-42) and ``sum_rank_partials`` (:259-264).
+  (families/qwen3_5/cuda/distributed.py:27-42), ``sum_rank_partials`` (:259-264), and the expert plan against the
+  ``want_plan`` the reference's own test expects (tests/cuda/test_experts.py:107-115).
+* The glue (``glue.py``) follows the plain-torch formulas the reference's glue test checks its kernels against
+  (tests/cuda/test_qwen27_glue.py:24-44); the Triton kernels themselves need a GPU and were not run: unpinned.
 * Pinned against the reference's Metal header expression ``code_at`` compiled as C++ (``oracle/build_ref.py`` builds
   ``oracle/_ref/code_at.so`` from kernels/qwen/dense/v1/affine_rows.py:11-24 where a reference checkout is present).
 * Parity unpinned against MLX's own ``quantized_matmul`` kernel output: MLX (pinned by the reference at

@@ -1,6 +1,7 @@
 """CPU restatement of the row-wise glue (test infrastructure only, like the rest of ``oracle``): float64 arithmetic on
 the bf16 inputs, outputs rounded to bf16.  Follows families/qwen3_5/cuda/glue.py:10-29 (``_add_rmsnorm``) and
-:130-143 (``_swiglu``) of the reference."""
+:130-143 (``_swiglu``) of the reference, and the plain-torch formulas its test checks them against
+(tests/cuda/test_qwen27_glue.py:24-44)."""
 
 from __future__ import annotations
 

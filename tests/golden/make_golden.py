@@ -5,7 +5,9 @@ Run once where a checkout of the reference is available:
     python tests/golden/make_golden.py /path/to/reference
 
 It calls only pure-Python/torch-CPU functions of the reference (no GPU, no Triton launch): ``dequantize``, ``split_k``,
-``bucket``, ``packed_shape``, ``input_slice``, ``max_items``, ``output_rows`` and ``sum_rank_partials``.  The outputs are
+``bucket``, ``packed_shape``, ``input_slice``, ``max_items``, ``output_rows`` and ``sum_rank_partials``, and the expected
+expert plan ``want_plan`` of the reference's own test (tests/cuda/test_experts.py:107-115), taken out of that file by
+name because the module around it needs a GPU to import.  The outputs are
 small and committed; the tests compare the CPU oracle (and, on a GPU, the kernels) against them, so nothing at test time
 needs the reference.
 """
@@ -88,6 +90,22 @@ def main(ref: str) -> None:
     # expert-table unpack nibble rule (cuda/experts.py:52-53): slot s of a block word holds input 2 (s % 4) + s // 4
     out["expert_slot_inputs"] = np.asarray([2 * (s % 4) + s // 4 for s in range(8)], dtype=np.int64)
     out["lane_offsets"] = np.asarray(r_qmm.OFFSETS, dtype=np.int64)
+
+    # the expert plan the reference's test expects (pairs grouped by expert in pair order, items of at most `tile`)
+    import ast
+
+    source = (Path(ref) / "tests" / "cuda" / "test_experts.py").read_text()
+    fn = next(node for node in ast.parse(source).body if isinstance(node, ast.FunctionDef) and node.name == "want_plan")
+    scope: dict = {"torch": torch}
+    exec(compile(ast.Module(body=[fn], type_ignores=[]), "want_plan", "exec"), scope)      # noqa: S102 - the reference's function
+    for tag, (rows, slots, e, tile) in {"a": (23, 7, 50, 16), "b": (300, 7, 50, 64), "c": (40, 9, 12, 16)}.items():
+        picks = torch.stack([torch.randperm(e, generator=g)[:slots] for _ in range(rows)]).to(torch.int32)
+        picks[:, 0] = 3                                        # one expert with a pair in every row
+        items, members, distinct = scope["want_plan"](picks, e, tile)
+        out[f"plan_{tag}_case"] = np.asarray([rows, slots, e, tile, distinct], dtype=np.int64)
+        out[f"plan_{tag}_picks"] = picks.numpy()
+        out[f"plan_{tag}_items"] = np.asarray(items, dtype=np.int64).reshape(-1, 3)
+        out[f"plan_{tag}_members"] = np.asarray(members, dtype=np.int64)
 
     dest = Path(__file__).with_name("reference_golden.npz")
     np.savez_compressed(dest, **out)

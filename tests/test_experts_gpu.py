@@ -116,6 +116,22 @@ def test_plan_groups_pairs_by_expert(rows, prefill):
     assert plan.members.cpu().tolist() == want_members.tolist()
 
 
+def test_plan_equals_the_references_expected_plan(golden):
+    """The plan kernel against the plans the reference's own test expects (golden vectors made from its ``want_plan``)."""
+
+    for tag in "abc":
+        rows, slots, e, tile, distinct = map(int, golden[f"plan_{tag}_case"])
+        picks = torch.from_numpy(golden[f"plan_{tag}_picks"]).to(torch.int32)
+        plan = experts.Plan(rows, slots, e, DEV, prefill=False)
+        plan.tile = tile
+        plan.items = torch.zeros((experts.max_items(rows * slots, e, tile), 3), dtype=torch.int32, device=DEV)
+        experts.route(picks.to(DEV), plan)
+        n = int(plan.counts[0])
+        assert n == len(golden[f"plan_{tag}_items"]) and int(plan.counts[1]) == distinct
+        assert plan.items[:n].cpu().tolist() == golden[f"plan_{tag}_items"].tolist()
+        assert plan.members.cpu().tolist() == golden[f"plan_{tag}_members"].tolist()
+
+
 @pytest.mark.parametrize("prefill", [False, True])
 @pytest.mark.parametrize("case", CASES)
 def test_matches_fp64(case, prefill):

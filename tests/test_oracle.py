@@ -124,3 +124,17 @@ def test_bf16_rounding_is_nearest_even():
     want = v.to(torch.bfloat16).float().numpy()
     np.testing.assert_array_equal(affine.bf16_round(v.numpy()), want)
     np.testing.assert_array_equal(affine.bf16_from_bits(affine.bf16_bits(v.numpy())), want)
+
+
+def test_plan_equals_the_references_expected_plan(golden):
+    """``oracle.moe.plan`` against the plans the reference's own test expects (``want_plan``, taken from the reference's
+    test file by the golden generator): items, members and the count of distinct experts."""
+
+    for tag in "abc":
+        rows, slots, e, tile, distinct = map(int, golden[f"plan_{tag}_case"])
+        picks = golden[f"plan_{tag}_picks"]
+        assert picks.shape == (rows, slots)
+        items, members, seen = moe.plan(picks, e, tile)
+        assert items.tolist() == golden[f"plan_{tag}_items"].tolist()
+        assert members.tolist() == golden[f"plan_{tag}_members"].tolist()
+        assert seen == distinct
