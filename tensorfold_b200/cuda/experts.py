@@ -143,6 +143,9 @@ def route(picks: torch.Tensor, plan: Plan) -> None:
 
 
 def _grouped(x, slots, table, n, k, ex, plan, out, rows, epi, limit):
+    if plan.experts > table.shape[0]:
+        # an item may name any expert below plan.experts: the kernels would read past the table
+        raise ValueError(f"the plan routes to {plan.experts} experts but the table holds {table.shape[0]}")
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != k or x.stride(1) != 1:
         raise ValueError(f"experts: inputs must be (rows, {k}) bf16 with unit-stride rows")
     if x.stride(0) % 8 or x.data_ptr() % 16:

@@ -79,10 +79,11 @@ class ExpertParallelMoE:
 
         rows = x.shape[0]
         logits = buf.logits[:rows]
+        form = buf.plan.prefill                                # prompt passes take the tensor-core router, as moe.moe does
         if self.has_shared_row:
-            moe.router(x, self.router, logits)
+            moe.router(x, self.router, logits, prefill=form)
         else:
-            moe.router(x, self.router, logits[:, :self.total])
+            moe.router(x, self.router, logits[:, :self.total], prefill=form)
             logits[:, self.total].zero_()
         moe.select_rows(logits, buf, self.top_k, self.total)
         pick, wts = buf.pick[:rows], buf.wts[:rows]
