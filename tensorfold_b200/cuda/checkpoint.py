@@ -235,6 +235,42 @@ class Checkpoint:
         return QLinear(weight, parts[1], parts[2], gs=gs, bits=bits)
 
 
+def expert_tables(ckpt: Checkpoint, prefix: str, projections: Sequence[str] = ("gate_proj", "up_proj", "down_proj"), *,
+                  device: torch.device | str = "cpu", rank: int = 0, world: int = 1):
+    """A routed layer's expert tables ``prefix.<projection>.weight / .scales / .biases`` of shape [E, ...] as the
+    experts rank ``rank`` of ``world`` owns, [rank E / world, (rank + 1) E / world): the experts are the tensors' first
+    dimension, so a rank's share is one contiguous byte range per tensor and only that is read.  Returns
+    ({projection: (words, scales, biases)}, first): what ``tp.shard_experts`` cuts from the whole tables
+    (reference: families/qwen3_5_moe/cuda/weights.py:32-46 reads them whole)."""
+
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("rank outside the world")
+    tables, first = {}, 0
+    for proj in projections:
+        names = [f"{prefix}.{proj}.{part}" for part in ("weight", "scales", "biases")]
+        for name in names:
+            if name not in ckpt:
+                raise KeyError(name)
+        e = ckpt.index[names[0]].shape[0]
+        if any(ckpt.index[name].shape[0] != e for name in names) or e % world:
+            raise ValueError(f"{prefix}.{proj}: {e} experts do not divide across {world} ranks")
+        first = rank * e // world
+        parts = [ckpt.rows(name, first, (rank + 1) * e // world, device) for name in names]
+        words = parts[0].view(torch.int32) if parts[0].dtype == torch.uint32 else parts[0]
+        tables[proj] = (words, parts[1], parts[2])
+    return tables, first
+
+
+def load_experts(ckpt: Checkpoint, prefix: str, device: torch.device | str, gs: int = 64, *, rank: int = 0, world: int = 1,
+                 limit: float = 0.0):
+    """The rank's experts of a SwiGLU layer, uploaded and tiled for the grouped kernels: (``experts.Experts``, first)."""
+
+    from . import experts
+
+    tables, first = expert_tables(ckpt, prefix, device=device, rank=rank, world=world)
+    return experts.make([tables["gate_proj"], tables["up_proj"]], tables["down_proj"], gs, limit=limit), first
+
+
 def load_packed(ckpt: Checkpoint, prefix: str, device: torch.device | str, **kw):
     """The rank's shard of a projection, uploaded and tiled for the kernels (``kernels.qmm.pack``)."""
 
@@ -244,4 +280,4 @@ def load_packed(ckpt: Checkpoint, prefix: str, device: torch.device | str, **kw)
     return qmm.pack(q.weight, q.scales, q.biases, q.gs, bits=q.bits)
 
 
-__all__ = ["ALIGN", "PIECE", "Spans", "read_header", "Entry", "Checkpoint", "load_packed"]
+__all__ = ["ALIGN", "PIECE", "Spans", "read_header", "Entry", "Checkpoint", "expert_tables", "load_experts", "load_packed"]

@@ -162,3 +162,32 @@ def test_broken_files_are_refused(tmp_path):
     odd.write_bytes(struct.pack("<Q", len(text)) + text + b"\x00")
     with pytest.raises(ValueError):
         checkpoint.Checkpoint([odd])
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_a_ranks_expert_tables_are_what_shard_experts_cuts(tmp_path, world):
+    from tensorfold_b200.cuda import tp
+
+    e, ni, d, gs = 8, 64, 128, 64
+    stack = lambda n, k, seed: tuple(torch.stack([synthetic.affine_weight(n, k, 4, gs, seed=seed * 100 + i)[j] for i in range(e)])
+                                    for j in range(3))
+    gate, up, down = stack(ni, d, 1), stack(ni, d, 2), stack(d, ni, 3)
+    tensors = {}
+    for proj, table in (("gate_proj", gate), ("up_proj", up), ("down_proj", down)):
+        for part, t in zip(("weight", "scales", "biases"), table):
+            tensors[f"layers.3.mlp.switch_mlp.{proj}.{part}"] = t.view(torch.uint32) if part == "weight" else t
+    path = tmp_path / "moe.safetensors"
+    write_safetensors(path, tensors, pad=2)
+    for rank in range(world):
+        spans = checkpoint.Spans()
+        got, first = checkpoint.expert_tables(checkpoint.Checkpoint([path], spans), "layers.3.mlp.switch_mlp", rank=rank, world=world)
+        (want_gate, want_up), want_down, want_first = tp.shard_experts([gate, up], down, rank, world)
+        assert first == want_first
+        for proj, want in (("gate_proj", want_gate), ("up_proj", want_up), ("down_proj", want_down)):
+            for a, b in zip(got[proj], want):
+                assert a.shape == b.shape and torch.equal(a.view(torch.uint8), b.contiguous().view(torch.uint8))
+        assert spans.bytes_read == sum(t.numel() * t.element_size() for t in tensors.values()) // world
+    with pytest.raises(ValueError):
+        checkpoint.expert_tables(checkpoint.Checkpoint([path]), "layers.3.mlp.switch_mlp", rank=0, world=3)
+    with pytest.raises(KeyError):
+        checkpoint.expert_tables(checkpoint.Checkpoint([path]), "layers.4.mlp.switch_mlp")
