@@ -821,6 +821,9 @@ def run_b200(args) -> None:
         os._exit(0)
 
 
+CASE_SETS = {"qkv_set": ("q_proj", "k_proj", "v_proj"), "gate_up_set": ("gate_proj", "up_proj")}
+
+
 def run_case(args) -> None:
     """A small fixed case for profiler captures: one projection of the layer, three distinct weight copies (larger than
     L2 together), six launches at --rows rows."""
@@ -830,8 +833,21 @@ def run_case(args) -> None:
     from tensorfold_b200 import synthetic
     from tensorfold_b200.cuda.kernels import qmm
 
-    n, k = synthetic.DENSE_27B[args.case]
     dev = "cuda"
+    if args.case in CASE_SETS:                               # a set of projections of one input in one persistent launch
+        names = CASE_SETS[args.case]
+        k = synthetic.DENSE_27B[names[0]][1]
+        copies = []
+        for i in range(3):
+            ws = [synthetic.affine_weight(*synthetic.DENSE_27B[name], BITS, GS, seed=10 * i + j) for j, name in enumerate(names)]
+            copies.append([qmm.pack(w[0].to(dev), w[1].to(dev), w[2].to(dev), GS) for w in ws])
+        x = synthetic.activations(args.rows, k, 0).to(dev)
+        for i in range(6):
+            y = qmm.matmul_set(x, copies[i % 3])[0]
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "rows": args.rows, "launches": 6, "max_abs": float(y.float().abs().max())}))
+        return
+    n, k = synthetic.DENSE_27B[args.case]
     qs = []
     for i in range(3):
         w = synthetic.affine_weight(n, k, BITS, GS, seed=i)

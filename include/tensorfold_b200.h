@@ -41,7 +41,8 @@ int tf_init(int device);
 int tf_device_error(int device, void* stream, int* code);
 
 /* Performance knobs that never change a result bit.  key "qmm_lanes": 128-column super-blocks a thread block streams side
- * by side (1, 2 or 4; 0 = default).  No counterpart in the reference. */
+ * by side (1, 2 or 4; 0 = default); "stream_lanes": the same for tf_qmm_set's persistent kernel; "stream_blocks": blocks
+ * of that kernel an SM may hold (0 = as many as fit).  No counterpart in the reference. */
 int tf_tune(const char* key, int value);
 
 /* ---- shape-only planning (host functions) -------------------------------------------------------------------- */
@@ -94,6 +95,21 @@ int tf_group_sums(const void* x, int64_t ldx, int m, int k, int gs, float* xs, v
 int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled, int64_t sb_stride, int n, int k,
            int bits, int gs, int sk, void* out, int64_t ldo, int out_f32, float* part, int reduce, int pdl,
            void* stream);
+
+/* tf_qmm for decode and verify windows (1 to 16 rows) over a SET of up to 4 projections that read the same rows of x
+ * (q/k/v, gate/up, or one projection alone): one persistent launch streams all of them, and every output row has the
+ * bits tf_qmm gives for the same projection and slice count.  Host arrays of nproj entries: tiled, sb_stride (entries
+ * 0 or the array NULL: dense), n, sk, out, ldo.  out_f32 applies to every projection.
+ *   scratch  device memory of tf_qmm_set_scratch_bytes(nproj, n, sk) bytes, 256-byte aligned: the K slices meet
+ *            there (it stays in L2).  Its first 64 KB are counters that must be ZERO before the first call; every call
+ *            leaves them zero (unless tf_device_error reports a lost wait: clear the scratch then).  Calls that share
+ *            scratch must not overlap on the GPU: one scratch area per stream that runs sets side by side.
+ * Replaces a run of the pybind qmm(...) calls of cuda/kernels/qmm.cpp:14-44 that the family engines issue for
+ * projections of one input (families/qwen3_5/cuda/qmm_fast.py:49-64), with the bits of those separate calls. */
+int64_t tf_qmm_set_scratch_bytes(int nproj, const int* n, const int* sk);
+int tf_qmm_set(const void* x, int64_t ldx, int m, const float* xs, int k, int bits, int gs, int nproj,
+               const void* const* tiled, const int64_t* sb_stride, const int* n, const int* sk, void* const* out,
+               const int64_t* ldo, int out_f32, void* scratch, int64_t scratch_bytes, int pdl, void* stream);
 
 /* Dense projection with an activation epilogue (one K slice): epi 1 = bf16(relu(bf16 v)^2); epi 2 = SwiGLU over a
  * tf_pack_pair weight, bf16(bf16(silu(bf16 gate)) * bf16 up) with both clipped first when limit > 0 (out then has n / 2

@@ -3,7 +3,7 @@
     python -m tensorfold_b200.build [--force]
 
 One object per translation unit, compiled in parallel; the matmul template is instantiated once per bit width
-(``qmm_inst.cu`` with ``-DTF_BITS=b``).
+(``qmm_inst.cu`` and ``qmm_stream_inst.cu`` with ``-DTF_BITS=b``).
 """
 
 from __future__ import annotations
@@ -25,8 +25,9 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 def _units() -> list[tuple[Path, Path, list[str]]]:
     units = [(CSRC / "qmm_inst.cu", OBJ / f"qmm_b{b}.o", [f"-DTF_BITS={b}"]) for b in BITS]
+    units += [(CSRC / "qmm_stream_inst.cu", OBJ / f"qmm_stream_b{b}.o", [f"-DTF_BITS={b}"]) for b in BITS]
     for src in sorted(CSRC.glob("*.cu")):
-        if src.name != "qmm_inst.cu":
+        if src.name not in ("qmm_inst.cu", "qmm_stream_inst.cu"):
             units.append((src, OBJ / (src.stem + ".o"), []))
     return units
 

@@ -2,6 +2,7 @@
 // load-time repack and its inverse, group sums, slice reduction.
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
@@ -9,6 +10,7 @@
 
 #include "../../include/tensorfold_b200.h"
 #include "qmm_launch.h"
+#include "qmm_stream_launch.h"
 
 namespace tf {
 
@@ -37,9 +39,18 @@ constexpr int MAX_DEVICES = 64;
 struct DeviceState {
   bool ready = false;
   int* err = nullptr;
+  int sms = 0;
+  signed char resident[6][3][2][3] = {};   // blocks of a streaming kernel an SM holds: [bits][group][row tile][lanes]
 };
 DeviceState g_devices[MAX_DEVICES];
 int g_lanes_pref = 0;                 // tuning knob (tf_tune): preferred slice lanes per block, 0 = default
+int g_stream_lanes = 0;               // tuning knob: super-blocks a streaming block holds side by side, 0 = default
+int g_stream_blocks = 0;              // tuning knob: streaming blocks an SM may hold, 0 = as many as fit
+
+constexpr int BIT_WIDTHS[6] = {2, 3, 4, 5, 6, 8};
+int bits_index(int bits) { return bits == 8 ? 5 : bits - 2; }
+int gs_index(int gs) { return gs == 32 ? 0 : gs == 64 ? 1 : 2; }
+int kw_index(int kw) { return kw == 1 ? 0 : kw == 2 ? 1 : 2; }
 std::mutex g_init_mutex;
 
 }  // namespace
@@ -242,6 +253,44 @@ cudaError_t launch_bits(const QmmParams& p, int bits, int gs, int mt, int kw, cu
   }
 }
 
+cudaError_t stream_launch_bits(const CUtensorMap& tmx, const StreamParams& p, int bits, int gs, int mt, int kw, int grid,
+                               cudaStream_t s, bool pdl) {
+  switch (bits) {
+    case 2: return qmm_stream_launch_b2(tmx, p, gs, mt, kw, grid, s, pdl);
+    case 3: return qmm_stream_launch_b3(tmx, p, gs, mt, kw, grid, s, pdl);
+    case 4: return qmm_stream_launch_b4(tmx, p, gs, mt, kw, grid, s, pdl);
+    case 5: return qmm_stream_launch_b5(tmx, p, gs, mt, kw, grid, s, pdl);
+    case 6: return qmm_stream_launch_b6(tmx, p, gs, mt, kw, grid, s, pdl);
+    default: return qmm_stream_launch_b8(tmx, p, gs, mt, kw, grid, s, pdl);
+  }
+}
+
+int stream_resident_bits(int bits, int gs, int mt, int kw) {
+  switch (bits) {
+    case 2: return qmm_stream_resident_b2(gs, mt, kw);
+    case 3: return qmm_stream_resident_b3(gs, mt, kw);
+    case 4: return qmm_stream_resident_b4(gs, mt, kw);
+    case 5: return qmm_stream_resident_b5(gs, mt, kw);
+    case 6: return qmm_stream_resident_b6(gs, mt, kw);
+    default: return qmm_stream_resident_b8(gs, mt, kw);
+  }
+}
+
+// Scratch of a set: a counter area of fixed size first (4 ints per super-block; fixed, so that no call's slices ever
+// land where another call's counters live: the counters must stay zero between calls), then the slices of every
+// projection with more than one K slice.
+constexpr int64_t SET_COUNTER_BYTES = 64 * 1024;            // 4096 super-blocks a set: 524,288 output columns
+
+int64_t set_counter_bytes(int nproj, const int* n) {
+  int64_t ints = 0;
+  for (int i = 0; i < nproj; ++i) ints += static_cast<int64_t>((n[i] + SB_COLS - 1) / SB_COLS) * 4;
+  return ints * 4 <= SET_COUNTER_BYTES ? SET_COUNTER_BYTES : -1;
+}
+
+int64_t set_part_bytes(int n, int sk) {
+  return sk > 1 ? static_cast<int64_t>((n + SB_COLS - 1) / SB_COLS) * sk * STREAM_PART_FLOATS * 4 : 0;
+}
+
 int grid_for(int64_t total, int threads) {
   const int64_t blocks = (total + threads - 1) / threads;
   return static_cast<int>(blocks < 1 ? 1 : (blocks > 148 * 32 ? 148 * 32 : blocks));
@@ -291,12 +340,29 @@ int tf_init(int device) {
   if (e == cudaSuccess) e = qmm_configure_b6();
   if (e == cudaSuccess) e = qmm_configure_b8();
   if (e == cudaSuccess) e = prefill_configure();
+  if (e == cudaSuccess) e = qmm_stream_configure_b2();
+  if (e == cudaSuccess) e = qmm_stream_configure_b3();
+  if (e == cudaSuccess) e = qmm_stream_configure_b4();
+  if (e == cudaSuccess) e = qmm_stream_configure_b5();
+  if (e == cudaSuccess) e = qmm_stream_configure_b6();
+  if (e == cudaSuccess) e = qmm_stream_configure_b8();
+  int sms = 0;
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (e == cudaSuccess) {
+    for (int b = 0; b < 6; ++b)
+      for (int g = 0; g < 3; ++g)
+        for (int m = 0; m < 2; ++m)
+          for (int k = 0; k < 3; ++k)
+            g_devices[device].resident[b][g][m][k] =
+                static_cast<signed char>(stream_resident_bits(BIT_WIDTHS[b], 32 << g, m + 1, 1 << k));
+  }
   int* err = nullptr;
   if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_error_word);
   if (e == cudaSuccess) e = cudaMemset(err, 0, sizeof(int));
   cudaSetDevice(prev);
   if (e != cudaSuccess) return cuda_fail(e, "tf_init");
   g_devices[device].err = err;
+  g_devices[device].sms = sms;
   g_devices[device].ready = true;
   return TF_OK;
 }
@@ -314,6 +380,14 @@ int tf_device_error(int device, void* stream, int* code) {
 int tf_tune(const char* key, int value) {
   if (key != nullptr && std::string(key) == "qmm_lanes" && (value == 0 || value == 1 || value == 2 || value == 4)) {
     g_lanes_pref = value;
+    return TF_OK;
+  }
+  if (key != nullptr && std::string(key) == "stream_lanes" && (value == 0 || value == 1 || value == 2 || value == 4)) {
+    g_stream_lanes = value;
+    return TF_OK;
+  }
+  if (key != nullptr && std::string(key) == "stream_blocks" && value >= 0 && value <= 8) {
+    g_stream_blocks = value;
     return TF_OK;
   }
   return fail(TF_ERR_ARG, "tf_tune: unknown key or value");
@@ -406,6 +480,10 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
   int kw = g_lanes_pref > 0 ? g_lanes_pref : (((nsb + 1) / 2) * sk >= 256 ? 2 : 1);    // measured on B200
   if (kw > max_lanes(mt)) kw = max_lanes(mt);
   const bool slices_out = sk > 1 && (!reduce || sk > 8);
+  if (slices_out && !part) return fail(TF_ERR_ARG, "tf_qmm: part is required when the slices leave the kernel (reduce = 0, or more than 8 slices)");
+  const bool out_used = !slices_out || reduce;
+  if (out_used && (!out || ldo < n)) return fail(TF_ERR_ARG, "tf_qmm: out is null or its rows are shorter than n (ldo >= n)");
+  if (sb_stride < 0) return fail(TF_ERR_ARG, "tf_qmm: negative super-block stride");
   if (slices_out && reduce && ldo != n) return fail(TF_ERR_ARG, "tf_qmm: more than 8 slices need a contiguous out (ldo == n)");
   if (m > 65535 * 8) return fail(TF_ERR_ARG, "tf_qmm: too many rows");
   DeviceState* st = nullptr;
@@ -432,6 +510,92 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
   if (e != cudaSuccess) return cuda_fail(e, "tf_qmm launch");
   if (slices_out && reduce) return tf_reduce_slices(part, sk, static_cast<int64_t>(m) * n, out, out_f32, stream);
   return TF_OK;
+}
+
+int64_t tf_qmm_set_scratch_bytes(int nproj, const int* n, const int* sk) {
+  if (nproj < 1 || nproj > STREAM_MAX_PROJ || !n || !sk) return TF_ERR_ARG;
+  int64_t total = set_counter_bytes(nproj, n);
+  if (total < 0) return TF_ERR_ARG;
+  for (int i = 0; i < nproj; ++i) {
+    if (n[i] < 1 || sk[i] < 1) return TF_ERR_ARG;
+    total += set_part_bytes(n[i], sk[i]);
+  }
+  return total;
+}
+
+int tf_qmm_set(const void* x, int64_t ldx, int m, const float* xs, int k, int bits, int gs, int nproj,
+               const void* const* tiled, const int64_t* sb_stride, const int* n, const int* sk, void* const* out,
+               const int64_t* ldo, int out_f32, void* scratch, int64_t scratch_bytes, int pdl, void* stream) {
+  if (!format_ok(bits, gs)) return fail(TF_ERR_ARG, "tf_qmm_set: %d bits / groups of %d is not an affine format", bits, gs);
+  if (nproj < 1 || nproj > STREAM_MAX_PROJ) return fail(TF_ERR_ARG, "tf_qmm_set: 1 to %d projections a set, not %d", STREAM_MAX_PROJ, nproj);
+  if (m < 1 || m > 16) return fail(TF_ERR_ARG, "tf_qmm_set: 1 to 16 rows, not %d (larger windows go through tf_qmm)", m);
+  if (k < gs || k % gs) return fail(TF_ERR_ARG, "tf_qmm_set: K = %d must be a positive multiple of the group", k);
+  if (!x || !tiled || !n || !sk || !out || !ldo) return fail(TF_ERR_ARG, "tf_qmm_set: null pointer");
+  if (reinterpret_cast<uintptr_t>(x) % 16 || (m > 1 && ldx % 8) || ldx < k)
+    return fail(TF_ERR_ALIGN, "tf_qmm_set: x rows must start on 16-byte boundaries (ldx %% 8 == 0, ldx >= k)");
+  const int kg = k / gs;
+  int64_t need = set_counter_bytes(nproj, n);
+  if (need < 0) return fail(TF_ERR_ARG, "tf_qmm_set: a set holds at most 4096 super-blocks of 128 columns");
+  for (int i = 0; i < nproj; ++i) {
+    if (n[i] < 1 || sk[i] < 1 || kg % sk[i])
+      return fail(TF_ERR_ARG, "tf_qmm_set: projection %d: n = %d, %d slices over %d groups", i, n[i], sk[i], kg);
+    if (!tiled[i] || !out[i] || ldo[i] < n[i]) return fail(TF_ERR_ARG, "tf_qmm_set: projection %d: null pointer or short out rows", i);
+    if (reinterpret_cast<uintptr_t>(tiled[i]) % 16) return fail(TF_ERR_ALIGN, "tf_qmm_set: tiled weights must be 16-byte aligned");
+    need += set_part_bytes(n[i], sk[i]);
+  }
+  if (!scratch || reinterpret_cast<uintptr_t>(scratch) % 256 || scratch_bytes < need)
+    return fail(TF_ERR_ARG, "tf_qmm_set: scratch must be 256-byte aligned and hold tf_qmm_set_scratch_bytes = %lld bytes",
+                static_cast<long long>(need));
+  DeviceState* st = nullptr;
+  if (int rc = current_state(&st)) return rc;
+
+  const int mt = mt_for_rows(m), unitw = unit_words(bits, gs);
+  // super-blocks a block streams side by side: two (two blocks an SM) unless that leaves SMs without work
+  int64_t units = 0;
+  for (int i = 0; i < nproj; ++i) units += static_cast<int64_t>((n[i] + SB_COLS - 1) / SB_COLS) * sk[i];
+  int kw = g_stream_lanes > 0 ? g_stream_lanes : (units >= 2 * st->sms ? 2 : 1);
+  int resident = st->resident[bits_index(bits)][gs_index(gs)][mt - 1][kw_index(kw)];
+  if (resident < 1) return fail(TF_ERR_STATE, "tf_qmm_set: the streaming kernel does not fit an SM of this device");
+  if (g_stream_blocks > 0 && g_stream_blocks < resident) resident = g_stream_blocks;
+
+  // longer slices first, so the blocks that get one item more get a short one
+  int order[STREAM_MAX_PROJ];
+  for (int i = 0; i < nproj; ++i) order[i] = i;
+  for (int i = 1; i < nproj; ++i)
+    for (int j = i; j > 0 && sk[order[j]] < sk[order[j - 1]]; --j) std::swap(order[j], order[j - 1]);
+
+  StreamParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.xs = xs;
+  p.M = m, p.K = k, p.KG = kg;
+  p.nproj = nproj;
+  p.err = st->err;
+  int* counters = static_cast<int*>(scratch);
+  uint8_t* parts = static_cast<uint8_t*>(scratch) + set_counter_bytes(nproj, n);
+  int items = 0;
+  for (int q = 0; q < nproj; ++q) {
+    const int i = order[q];
+    StreamProj& pr = p.proj[q];
+    pr.w = static_cast<const uint32_t*>(tiled[i]);
+    pr.sb_stride = sb_stride && sb_stride[i] > 0 ? sb_stride[i] : static_cast<int64_t>(kg) * unitw;
+    pr.out = out[i];
+    pr.ldo = ldo[i];
+    pr.N = n[i], pr.sk = sk[i];
+    pr.nsb = (n[i] + SB_COLS - 1) / SB_COLS;
+    pr.out_f32 = out_f32;
+    pr.count = counters;
+    counters += pr.nsb * 4;
+    pr.part = reinterpret_cast<float*>(parts);
+    parts += set_part_bytes(n[i], sk[i]);
+    pr.item0 = items;
+    items += (pr.nsb + kw - 1) / kw * pr.sk;
+  }
+  p.items = items;
+  CUtensorMap tmx = {};
+  if (int rc = encode_rows(&tmx, x, m == 1 ? k : ldx, m, k, 8 * mt)) return rc;
+  const int grid = std::min(items, st->sms * resident);
+  const cudaError_t e = stream_launch_bits(tmx, p, bits, gs, mt, kw, grid, static_cast<cudaStream_t>(stream), pdl != 0);
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_qmm_set launch");
 }
 
 int tf_qmm_act(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int bits, int gs,

@@ -116,21 +116,33 @@ TF_HD uint32_t lane_code(int bits, int gs, const uint32_t* words, int p, int hal
 // most 6 bits here) sits in the low mantissa bits of 0x4300 = 128.0.  8-bit codes come as two nibble planes: HIGH picks
 // the upper nibble, which the kernel multiplies by 16 x instead of x.  With p a compile-time constant (unrolled loops)
 // this is one shift and one three-input logic op per plane.
+#if defined(__CUDA_ARCH__)
+// (a & mask) | orv as ONE three-input logic instruction (left to itself the compiler emits an AND and an OR when both
+// constants are immediates: twice the instructions in the matmul's innermost loop).
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));
+  return r;
+}
+#else
+inline uint32_t and_or(uint32_t a, uint32_t mask, uint32_t orv) { return (a & mask) | orv; }
+#endif
+
 template <int BITS, int GS, bool HIGH = false>
 TF_HD uint32_t pair_reg(const uint32_t* wd, int p) {
   constexpr int WA = Fmt<BITS>::WA, WB = Fmt<BITS>::WB, NP = pairs_per_lane(GS), WORDS_A = NP * WA / 16, PPA = 16 / WA;
   constexpr uint32_t MAGIC = 0x43004300u, MASK_A = ((1u << WA) - 1u) * 0x00010001u;
   if constexpr (Fmt<BITS>::SPLIT) {
     const uint32_t v = wd[(HIGH ? WORDS_A : 0) + p / 4] >> ((p % 4) * 4);
-    return (v & 0x000F000Fu) | MAGIC;
+    return and_or(v, 0x000F000Fu, MAGIC);
   } else {
-    uint32_t r = ((wd[p / PPA] >> ((p % PPA) * WA)) & MASK_A) | MAGIC;
+    uint32_t r = and_or(wd[p / PPA] >> ((p % PPA) * WA), MASK_A, MAGIC);
     if constexpr (WB > 0) {
       constexpr int PPB = 16 / WB;
       constexpr uint32_t MASK_B = (((1u << WB) - 1u) << WA) * 0x00010001u;
       const int sh = (p % PPB) * WB - WA;
       const uint32_t u = wd[WORDS_A + p / PPB];
-      r |= (sh >= 0 ? (u >> sh) : (u << (-sh))) & MASK_B;
+      r = and_or(sh >= 0 ? (u >> sh) : (u << (-sh)), MASK_B, r);
     }
     return r;
   }

@@ -112,6 +112,59 @@ __device__ __forceinline__ bool mbar_wait_probed(bool ready, uint64_t* bar, uint
   return mbar_wait(bar, parity, abort_flag);
 }
 
+// ---- the same barrier operations on 32-bit shared-memory addresses (no generic-to-shared conversion per call) ----
+__device__ __forceinline__ void mbar32_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar32_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar32_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
+// The slow path of a wait, kept out of line so the loops that call it stay short: polls with a suspend hint until the
+// phase completes, WAIT_POLLS polls have passed or another warp of the block has given up (abort word != 0).
+static __device__ __noinline__ bool mbar32_wait_slow(uint32_t bar, uint32_t parity, uint32_t abort_word) {
+  bool ok = false;
+  for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity), "r"(20000u)
+                 : "memory");
+    if (done) {
+      ok = true;
+      break;
+    }
+    if ((i & 255u) == 255u) {
+      uint32_t gone;
+      asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(gone) : "r"(abort_word));
+      if (gone) break;
+    }
+  }
+  return __all_sync(0xFFFFFFFFu, ok);
+}
+// Bounded wait by a whole warp: one probe inline, the polling loop out of line.  False (for all lanes) when it gave up.
+__device__ __forceinline__ bool mbar32_wait(uint32_t bar, uint32_t parity, uint32_t abort_word) {
+  if (__all_sync(0xFFFFFFFFu, mbar32_try_wait(bar, parity))) return true;
+  return mbar32_wait_slow(bar, parity, abort_word);
+}
+__device__ __forceinline__ void bulk_load32(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_2d32(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+               "l"(map), "r"(bar), "r"(x), "r"(y)
+               : "memory");
+}
+
 // Bulk asynchronous copy global -> shared of `bytes` (a multiple of 16; both addresses 16-byte aligned),
 // completing on an mbarrier.  Every CTA fetches its own data.
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -167,6 +220,37 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint3
   uint32_t r;
   asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));      // (a & mask) | orv
   return r;
+}
+
+// Loads from a 32-bit shared-memory address (the generic-pointer form costs 64-bit address arithmetic per load).
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
+}
+
+// (d0, d1) = (a0, a1) * (b0, b1) + (d0, d1): two IEEE fp32 fused multiply-adds in one instruction (each half rounds
+// exactly as fmaf does, so results carry the same bits as two scalar fmas).
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmov.b64 rd, {%0, %1};\n"
+      "fma.rn.f32x2 rd, ra, rb, rd;\nmov.b64 {%0, %1}, rd;\n}"
+      : "+f"(d0), "+f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
 
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }

@@ -6,6 +6,8 @@ argument meaning and errors; the arithmetic runs in ``libtensorfold_b200.so``.
 
 from __future__ import annotations
 
+import ctypes
+import os
 from dataclasses import dataclass
 
 import torch
@@ -157,6 +159,8 @@ def matmul(x: torch.Tensor, q: Q4, xs: torch.Tensor | None = None, *, sk: int | 
             raise ValueError("matmul: part must hold (SK, M, n) fp32")
     if q.weight.dim() != 3 or q.weight.stride(2) != 1 or q.weight.stride(1) != q.weight.shape[2]:
         raise ValueError("matmul: the tiled weight may be sliced by super-blocks of 128 columns only")
+    if STREAM and m <= STREAM_ROWS and part is None and (reduce or sk == 1):
+        return matmul_set(x, [q], xs, sks=[sk], f32=f32, outs=[out], pdl=pdl)[0]     # same bits, persistent launch
     _lib.check(_lib.lib().tf_qmm(
         x.data_ptr(), x.stride(0), m, xs.data_ptr() if xs is not None else None, q.weight.data_ptr(),
         q.weight.stride(0), q.n, q.k, q.bits, q.gs, sk, out.data_ptr() if out is not None else None,
@@ -165,6 +169,99 @@ def matmul(x: torch.Tensor, q: Q4, xs: torch.Tensor | None = None, *, sk: int | 
     if sk == 1 or reduce:
         return out
     return part.reshape(-1)[:sk * m * q.n].view(sk, m, q.n)
+
+
+STREAM = os.environ.get("TENSORFOLD_B200_STREAM", "1") != "0"      # decode windows run the persistent kernel (same bits)
+STREAM_ROWS = 16
+SET_MAX = 4
+SCRATCH_BYTES = 16 << 20          # one scratch area: room for a gate/up set of 17408 rows each in 4 K slices
+SCRATCH_AREAS = 4                 # areas made on a device's first call: the calling stream's and three side streams'
+_set_scratch: dict = {}           # (device index, stream) -> the stream's scratch area
+_free_areas: dict = {}            # device index -> areas not yet handed to a stream
+
+
+def _scratch_for(device: torch.device, stream: int, need: int) -> torch.Tensor:
+    """The scratch area of (device, stream) where the K slices of a set meet: zeroed once, left zero by every call.
+
+    Areas are made eagerly (four on a device's first call, more when a fifth stream shows up or a set needs more room)
+    and only handed out during a stream capture: a graph must not own memory that later calls use, so a capture that
+    would need a new allocation is refused with a message saying which eager call to make first."""
+
+    key = (device.index, stream)
+    buf = _set_scratch.get(key)
+    if buf is not None and buf.numel() >= need:
+        return buf
+    capturing = torch.cuda.is_current_stream_capturing()
+    free = _free_areas.setdefault(device.index, [])
+    if not free and not capturing and not any(k[0] == device.index for k in _set_scratch):
+        free.extend(torch.zeros((SCRATCH_BYTES,), dtype=torch.uint8, device=device) for _ in range(SCRATCH_AREAS))
+    fits = [i for i, area in enumerate(free) if area.numel() >= need]
+    if buf is None and fits:
+        buf = free.pop(fits[0])
+    elif capturing:
+        raise RuntimeError("matmul_set: this call needs a new scratch area, which cannot be made while the stream is "
+                           "capturing; run it once eagerly (any stream of this device) before the capture")
+    else:
+        buf = torch.zeros((max(need, SCRATCH_BYTES),), dtype=torch.uint8, device=device)
+    _set_scratch[key] = buf
+    return buf
+
+
+def reset_scratch() -> None:
+    """Forget every scratch area (after ``device_error`` reported a lost wait their counters may be non-zero)."""
+
+    _set_scratch.clear()
+    _free_areas.clear()
+
+
+def matmul_set(x: torch.Tensor, qs, xs: torch.Tensor | None = None, *, sks=None, f32: bool = False, outs=None,
+               pdl: bool = False) -> list:
+    """Several projections of the SAME rows (q/k/v, gate/up) in one persistent launch: [x @ q.T for q in qs], each with
+    the bits ``matmul(x, q, sk=sk)`` gives.  1 to 16 rows, up to 4 weights of one format and K.  Not in the reference,
+    whose engines issue these as separate calls (families/qwen3_5/cuda/qmm_fast.py:49-64)."""
+
+    qs = list(qs)
+    if not 1 <= len(qs) <= SET_MAX:
+        raise ValueError(f"matmul_set: 1 to {SET_MAX} weights a set")
+    q0 = qs[0]
+    if any((q.k, q.gs, q.bits) != (q0.k, q0.gs, q0.bits) for q in qs):
+        raise ValueError("matmul_set: the weights of a set share K, group and bit width")
+    x = _rows(x, q0.k, "matmul_set")
+    m = x.shape[0]
+    if m > STREAM_ROWS:
+        raise ValueError(f"matmul_set: at most {STREAM_ROWS} rows (use matmul for larger windows)")
+    stream = _lib.stream_of(x)
+    kg = q0.k // q0.gs
+    if xs is not None and (xs.dtype != torch.float32 or xs.shape != (m, kg) or not xs.is_contiguous()):
+        raise ValueError(f"matmul_set: xs must be contiguous ({m}, {kg}) fp32")
+    sks = [sk or default_split(q.n, q.k, q.gs) for q, sk in zip(qs, sks or [None] * len(qs))]
+    outs = list(outs) if outs is not None else [None] * len(qs)
+    dtype = torch.float32 if f32 else torch.bfloat16
+    for i, q in enumerate(qs):
+        if q.weight.device != x.device:
+            raise ValueError("matmul_set: x and the weights must share a CUDA device")
+        if sks[i] < 1 or kg % sks[i]:
+            raise ValueError("matmul_set: K must split into whole groups a slice")
+        if q.weight.dim() != 3 or q.weight.stride(2) != 1 or q.weight.stride(1) != q.weight.shape[2]:
+            raise ValueError("matmul_set: the tiled weight may be sliced by super-blocks of 128 columns only")
+        if outs[i] is None:
+            outs[i] = torch.empty((m, q.n), dtype=dtype, device=x.device)
+        elif outs[i].shape != (m, q.n) or outs[i].dtype != dtype or outs[i].stride(1) != 1:
+            raise ValueError("matmul_set: out must be (M, n) of the requested dtype with unit-stride rows")
+    count = len(qs)
+    ints, longs, ptrs = ctypes.c_int * count, ctypes.c_int64 * count, ctypes.c_void_p * count
+    n_arr, sk_arr = ints(*[q.n for q in qs]), ints(*sks)
+    lib = _lib.lib()
+    need = lib.tf_qmm_set_scratch_bytes(count, n_arr, sk_arr)
+    if need < 0:
+        raise ValueError("matmul_set: bad shapes")
+    scratch = _scratch_for(x.device, stream, need)
+    _lib.check(lib.tf_qmm_set(
+        x.data_ptr(), x.stride(0), m, xs.data_ptr() if xs is not None else None, q0.k, q0.bits, q0.gs, count,
+        ptrs(*[q.weight.data_ptr() for q in qs]), longs(*[q.weight.stride(0) for q in qs]), n_arr, sk_arr,
+        ptrs(*[o.data_ptr() for o in outs]), longs(*[o.stride(0) for o in outs]), int(f32), scratch.data_ptr(),
+        scratch.numel(), int(pdl), stream), "matmul_set")
+    return outs
 
 
 def prefill_matmul(x: torch.Tensor, q: Q4, *, f32: bool = False, tile: int = 0,
