@@ -113,6 +113,10 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
  * cuda/kernels/qmm.cpp:14-44 for decode windows, and a run of such calls that the family engines issue for projections
  * of one input (families/qwen3_5/cuda/qmm_fast.py:49-64). */
 int64_t tf_qmm_set_scratch_bytes(int nproj, const int* n, const int* sk);
+/* The launch geometry tf_qmm_set picks for such a set on the current device (host function; any pointer may be NULL):
+ * super-blocks a thread block streams side by side, blocks an SM holds, blocks of the persistent grid.  Geometry never
+ * changes a result bit.  No counterpart in the reference. */
+int tf_qmm_set_geometry(int bits, int gs, int nproj, const int* n, const int* sk, int* lanes, int* blocks_per_sm, int* grid);
 int tf_qmm_set(const void* x, int64_t ldx, int m, const float* xs, int k, int bits, int gs, int nproj,
                const void* const* tiled, const int64_t* sb_stride, const int* n, const int* sk, void* const* out,
                const int64_t* ldo, int out_f32, int slices_out, void* scratch, int64_t scratch_bytes, int pdl,

@@ -15,10 +15,10 @@
 // its m16n8k16 A fragments, and the register pattern of such a fragment is also the pattern tcgen05.st.16x128b writes:
 // a consumer warp dequantises a group of its 32 columns in registers ((word >> shift) & mask | magic, one shift and
 // one logic instruction per two weights) and stores the 16 registers of each 16-column tile straight into tensor
-// memory as the MMA's A operand (lane = column, 32-bit column = two inputs).  One thread of the MMA warp then issues
-// the group's MMAs against the rows of x in shared memory (the B operand: a [64 inputs x 16 rows] tensor-map box in
-// the 128-byte swizzle) and commits them to a barrier; the consumer warps read P' back with tcgen05.ld (one column a
-// thread, 16 rows) and apply the affine step.  Two A and two P' buffers per 128-column lane alternate, so a warp
+// memory as the MMA's A operand (lane = column, 32-bit column = two inputs).  The last of a lane's four warps to finish
+// its stores (a counter in shared memory tells) issues the group's MMAs from one thread, against the rows of x in
+// shared memory (the B operand: a [64 inputs x 16 rows] tensor-map box in the 128-byte swizzle), and commits them to
+// a barrier; the consumer warps read P' back with tcgen05.ld (one column a thread, 16 rows) and apply the affine step.  Two A and two P' buffers per 128-column lane alternate, so a warp
 // dequantises group n + 1 while the tensor core works on group n and before it folds in group n.
 //
 // Schedule.  The grid is persistent; work items (projection, KW adjacent 128-column super-blocks, K slice) are dealt
@@ -34,6 +34,9 @@
 #pragma once
 
 #include "qmm_tiled.cuh"
+#ifdef TF_WAIT_STATS
+#include <cstdio>
+#endif
 
 namespace tf {
 
@@ -94,8 +97,8 @@ struct StreamGeo {
   static constexpr int BUDGET = (BLOCKS == 3 ? 72 : BLOCKS == 2 ? 110 : 220) * 1024;
   static constexpr int NST_A = BUDGET / STAGE;
   static constexpr int NST = NST_A < 3 ? 3 : (NST_A > 12 ? 12 : NST_A);
-  static constexpr int NBAR = 3 * NST + 4 * KW;             // full, empty, sums per stage; a_full, d_full per lane buffer
-  static constexpr int BAR_BYTES = NBAR * 8 + 16;           // + abort word, tensor-memory base
+  static constexpr int NBAR = 3 * NST + 2 * KW;             // full, empty, sums per stage; d_full per lane buffer
+  static constexpr int BAR_BYTES = NBAR * 8 + 2 * KW * 4 + 16;   // + store counters per lane buffer, abort word, tensor-memory base
   static constexpr int SMEM_USED = NST * STAGE + BAR_BYTES + 1024;
   static constexpr int SMEM_FLOOR = BLOCKS == 1 ? 116 * 1024 : BLOCKS == 2 ? 76 * 1024 : 0;   // keeps a further block out
   static constexpr int SMEM = SMEM_USED > SMEM_FLOOR ? SMEM_USED : SMEM_FLOOR;
@@ -139,32 +142,12 @@ __device__ __forceinline__ StreamItem stream_item(const StreamParams& p, int i) 
   return it;
 }
 
-// tcgen05.st.16x128b.xN: registers 2 i and 2 i + 1 of thread T go to lanes T / 4 and T / 4 + 8, column 4 i + T % 4 ...
-// the pattern of m16n8k16 A fragments (two column groups of four to a 16-input step) side by side.
-template <int NREG>
-__device__ __forceinline__ void tmem_store_frag(uint32_t taddr, const uint32_t (&r)[NREG]) {
-  static_assert(NREG == 8 || NREG == 16 || NREG == 32, "a group of 32, 64 or 128 inputs");
-  if constexpr (NREG == 8) {
-    asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
-                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-  } else if constexpr (NREG == 16) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(
-            taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
-        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-  } else {
-    asm volatile(
-        "tcgen05.st.sync.aligned.16x128b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
-        "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
-        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
-        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
-        "r"(r[31])
-        : "memory");
-  }
+// tcgen05.st.16x128b.x2: registers 0..3 of thread T go to lanes T / 4, T / 4 + 8 (registers 0, 1) and the same lanes four
+// columns on (registers 2, 3), column T % 4: the register pattern of one m16n8k16 A fragment (16 columns x 16 inputs).
+// Four registers a store keep the operands where the dequantisation left them (wider stores made the compiler copy).
+__device__ __forceinline__ void tmem_store_frag(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+               : "memory");
 }
 
 // P' of one column: 16 fp32 values (one per row of x) from the thread's own tensor-memory lane.
@@ -192,12 +175,14 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
   const uint32_t full32 = smem32 + NST * Geo::STAGE;        // weights and x of a stage have landed
   const uint32_t empty32 = full32 + NST * 8;                // every consumer warp is done with a stage
   const uint32_t sums32 = empty32 + NST * 8;                // the stage's group sums are written
-  const uint32_t afull32 = sums32 + NST * 8;                // [kw][2]: the four warps of a lane have stored a group's A operand
-  const uint32_t dfull32 = afull32 + KW * 16;               // [kw][2]: the group's MMAs have completed
-  const uint32_t abort32 = dfull32 + KW * 16;               // non-zero once a warp of the block has given up a wait
+  const uint32_t dfull32 = sums32 + NST * 8;                // [kw][2]: the group's MMAs have completed
+  const uint32_t stored32 = dfull32 + KW * 16;              // [kw][2] counters: warps of the lane that have stored a group's A operand
+  const uint32_t abort32 = stored32 + KW * 8;               // non-zero once a warp of the block has given up a wait
   const uint32_t tslot32 = abort32 + 4;                     // tensor-memory base address, written by tcgen05.alloc
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // the warp index through a shuffle: the compiler then knows it is the same in every lane, keeps what derives from it
+  // (roles, tensor-memory and barrier addresses) in uniform registers and branches on it without divergence handling
+  const int tid = threadIdx.x, warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0), lane = tid & 31;
   if (tid == 0) {
     for (int i = 0; i < NST; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full32 + 8 * i), "r"(2) : "memory");    // weights' bytes + bytes of x
@@ -205,8 +190,8 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sums32 + 8 * i), "r"(1) : "memory");
     }
     for (int i = 0; i < 2 * KW; ++i) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(afull32 + 8 * i), "r"(4) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(dfull32 + 8 * i), "r"(1) : "memory");
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(stored32 + 4 * i), "r"(0) : "memory");
     }
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(abort32), "r"(0) : "memory");
     mbar_fence_init();
@@ -218,7 +203,7 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = lds32(tslot32);
+  const uint32_t tmem = __shfl_sync(0xFFFFFFFFu, lds32(tslot32), 0);
   pdl_launch_dependents();
 
   auto give_up = [&](int code) {
@@ -263,13 +248,14 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
     }
     pdl_wait();                                             // x may be the previous kernel's output
     bool ok = true;
+    uint32_t polls_empty = 0;
     int gst = 0, slot = 0;
     uint32_t phase = 1;                                     // parity of the `empty` phase that frees the slot (first round: none)
     for (int i = first_item; i < p.items && ok; i += step) {
       const StreamItem it = stream_item<KW, G>(p, i);
       for (int st = 0; st < it.nst; ++st, ++gst) {
         if (gst >= NST) {                                   // the stage goes where stage gst - NST was
-          ok = mbar32_wait(empty32 + 8 * slot, phase, abort32);
+          ok = mbar32_wait(empty32 + 8 * slot, phase, abort32, 256, &polls_empty);
           if (!ok) {
             give_up(ERR_WAIT_EMPTY);
             break;
@@ -283,126 +269,59 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
     if (!ok) {
       for (int i = 0; i < 64; ++i) __nanosleep(20000);      // copies in flight land before the shared memory is released
     }
+#ifdef TF_WAIT_STATS
+    if (lane == 0 && blockIdx.x < 2) printf("block %d copy warp: polls empty %u stages %d\n", blockIdx.x, polls_empty, gst);
+#endif
   } else if (warp == AUX_WARP) {
-    // ------------------------------------------------------------------ sums + MMA warp
-    // Two jobs walk the same sequence of stages: the group sums of x (whole warp: x against a tile of ones on the
-    // legacy tensor path, the bits tf_group_sums gives; they also tell the consumers that a stage has landed) run at
-    // least one stage ahead of the MMA issue (one thread: a group's MMAs once the lane's four warps have stored its A
-    // operand).  D (128 columns x 16 rows, fp32) = A (tensor memory: lane = column, 32-bit column = two inputs) x B (the
-    // rows of x in shared memory, K-major, 128-byte swizzle); bf16 inputs, M = 128, N = 16.
-    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-    struct Cursor {
-      int i, st, slot, index;                                // item, stage in the item, ring slot, stages since the start
-      uint32_t phase;
-      bool valid;
-      StreamItem it;
-    };
-    auto start = [&](Cursor& c) {
-      c.i = first_item, c.st = 0, c.slot = 0, c.index = 0, c.phase = 0;
-      c.valid = c.i < p.items;
-      if (c.valid) c.it = stream_item<KW, G>(p, c.i);
-    };
-    auto advance = [&](Cursor& c) {
-      ++c.index;
-      if (++c.slot == NST) c.slot = 0, c.phase ^= 1;
-      if (++c.st == c.it.nst) {
-        c.st = 0, c.i += step;
-        c.valid = c.i < p.items;
-        if (c.valid) c.it = stream_item<KW, G>(p, c.i);
-      }
-    };
-    const uint32_t xrow = (lane & 7) * XHALF_ROW;
-    const uint32_t sw0 = (((lane >> 3) ^ (lane & 7)) << 4), sw1 = (((4 | (lane >> 3)) ^ (lane & 7)) << 4);
-    // the group sums of the cursor's stage (its full barrier has completed)
-    auto sums_stage = [&](const Cursor& c) {
-      const int ng = min(G, c.it.per - c.st * G);
-      const uint32_t sp32 = smem32 + c.slot * Geo::STAGE, xs32 = sp32 + Geo::XS_OFF;
-      if (p.xs != nullptr) {
-        const int g0 = c.it.g_first + c.st * G;
-        for (int e = lane; e < ng * ROWS; e += 32) {
-          const int u = e / ROWS, r = e % ROWS;
-          const float v = r < p.M ? p.xs[static_cast<int64_t>(r) * p.KG + g0 + u] : 0.f;
-          asm volatile("st.shared.f32 [%0], %1;" ::"r"(xs32 + (u * ROWS + r) * 4), "f"(v) : "memory");
-        }
-      } else {
-#pragma unroll
-        for (int u = 0; u < G; ++u) {
-          if (u >= ng) break;
-#pragma unroll
-          for (int mt = 0; mt < 2; ++mt) {
-            float d[4];
-            ones_mma_group<GS, Geo::XHALF>(d, sp32 + Geo::X_OFF, xrow, sw0, sw1, mt, u * GS);
-            if (lane < 4)
-              asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xs32 + (u * ROWS + mt * 8 + 2 * lane) * 4), "f"(d[0]), "f"(d[1])
-                           : "memory");
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar32_arrive(sums32 + 8 * c.slot);     // also tells the consumers that the stage has landed
-    };
-
+    // ------------------------------------------------------------------ sums warp: group sums of x, once per block
+    // (x against a tile of ones on the legacy tensor path: the bits tf_group_sums gives; the arrival also tells the
+    // consumers that the stage has landed)
     pdl_wait();                                              // xs may be the previous kernel's output
     bool ok = true;
-    uint32_t nk[KW];                                         // groups issued so far, per lane (its consumers count the same)
-#pragma unroll
-    for (int kw = 0; kw < KW; ++kw) nk[kw] = 0;
-    Cursor cs, cm;
-    start(cs);
-    start(cm);
-    while (cm.valid && ok) {
-      if (cs.valid && cs.index == cm.index) {                // the MMAs of this stage need its sums first
-        ok = mbar32_wait(full32 + 8 * cs.slot, cs.phase, abort32);
+    uint32_t polls_full = 0;
+    int slot = 0;
+    uint32_t phase = 0;
+    const uint32_t xrow = (lane & 7) * XHALF_ROW;
+    const uint32_t sw0 = (((lane >> 3) ^ (lane & 7)) << 4), sw1 = (((4 | (lane >> 3)) ^ (lane & 7)) << 4);
+    for (int i = first_item; i < p.items && ok; i += step) {
+      const StreamItem it = stream_item<KW, G>(p, i);
+      for (int st = 0; st < it.nst; ++st) {
+        ok = mbar32_wait(full32 + 8 * slot, phase, abort32, 128, &polls_full);
         if (!ok) {
           give_up(ERR_WAIT_FULL);
           break;
         }
-        sums_stage(cs);
-        advance(cs);
-      }
-      // one more stage of sums while the consumers dequantise, if its data is already here (never a whole ring ahead)
-      if (cs.valid && cs.index - cm.index < NST - 1 && __all_sync(0xFFFFFFFFu, mbar32_try_wait(full32 + 8 * cs.slot, cs.phase))) {
-        sums_stage(cs);
-        advance(cs);
-      }
-      const int ng = min(G, cm.it.per - cm.st * G);
-      const uint32_t xb = smem32 + cm.slot * Geo::STAGE + Geo::X_OFF;
-      for (int u = 0; u < ng && ok; ++u) {
-        const uint32_t k0 = u * GS;                          // the group's inputs inside the stage
-#pragma unroll
-        for (int kw = 0; kw < KW; ++kw) {
-          if (kw >= cm.it.lanes || !ok) continue;
-          const uint32_t buf = nk[kw] & 1, par = (nk[kw] >> 1) & 1;
-          ++nk[kw];
-          ok = mbar32_wait(afull32 + 8 * (2 * kw + buf), par, abort32);
-          if (!ok) {
-            give_up(ERR_WAIT_FULL);
-            break;
+        const int ng = min(G, it.per - st * G);
+        const uint32_t sp32 = smem32 + slot * Geo::STAGE, xs32 = sp32 + Geo::XS_OFF;
+        if (p.xs != nullptr) {
+          const int g0 = it.g_first + st * G;
+          for (int e = lane; e < ng * ROWS; e += 32) {
+            const int u = e / ROWS, r = e % ROWS;
+            const float v = r < p.M ? p.xs[static_cast<int64_t>(r) * p.KG + g0 + u] : 0.f;
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(xs32 + (u * ROWS + r) * 4), "f"(v) : "memory");
           }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (lane == 0) {
-            const uint32_t a_t = tmem + kw * Geo::LANE_COLS + buf * Geo::A_COLS;
-            const uint32_t d_t = tmem + kw * Geo::LANE_COLS + 2 * Geo::A_COLS + buf * Geo::D_COLS;
+        } else {
 #pragma unroll
-            for (int s = 0; s < S; ++s) {
-              // 64 inputs a swizzled tile, 32 bytes a 16-input step inside its 128-byte rows
-              const uint32_t kin = k0 + 16 * s;
-              const uint32_t baddr = xb + (kin >> 6) * Geo::XHALF + (kin & 63) * 2;
-              const uint32_t lo = ((baddr >> 4) & 0x3FFFu) | (1u << 16);
-              const uint32_t hi = 64u | (1u << 14) | (2u << 29);
-              const uint64_t bdesc = (static_cast<uint64_t>(hi) << 32) | lo;
-              asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(d_t),
-                           "r"(a_t + 8 * s), "l"(bdesc), "r"(IDESC), "r"(s > 0 ? 1 : 0)
-                           : "memory");
+          for (int u = 0; u < G; ++u) {
+            if (u >= ng) break;
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+              float d[4];
+              ones_mma_group<GS, Geo::XHALF>(d, sp32 + Geo::X_OFF, xrow, sw0, sw1, mt, u * GS);
+              if (lane < 4)
+                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xs32 + (u * ROWS + mt * 8 + 2 * lane) * 4), "f"(d[0]), "f"(d[1])
+                             : "memory");
             }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(dfull32 + 8 * (2 * kw + buf))
-                         : "memory");
           }
-          __syncwarp();
         }
+        __syncwarp();
+        if (lane == 0) mbar32_arrive(sums32 + 8 * slot);
+        if (++slot == NST) slot = 0, phase ^= 1;
       }
-      advance(cm);
     }
+#ifdef TF_WAIT_STATS
+    if (lane == 0 && blockIdx.x < 2) printf("block %d sums warp: polls full %u\n", blockIdx.x, polls_full);
+#endif
   } else {
     // ------------------------------------------------------------------ consumers: dequantise -> tensor memory, then P' -> acc
     const int kw = warp >> 2, tp = warp & 3;
@@ -414,16 +333,14 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
         Geo::W_OFF + kw * Geo::W_BYTES + (TILE_PAIRS * 32 * WPL + tp * 32 + (lane & 7) * 4 + (lane >> 4) * 2 + ((lane >> 3) & 1)) * 4;
     const uint32_t a_lane = tmem + (static_cast<uint32_t>(32 * tp) << 16) + kw * Geo::LANE_COLS;     // this warp's 32 tensor-memory lanes
 
-    float acc[ROWS];
-    struct Pending {                                         // the group whose MMAs are in flight
-      uint32_t sp32;                                         // its stage
-      int u;                                                 // its index inside the stage
-      uint32_t buf, par;                                     // its tensor-memory buffer and barrier parity
-      int slot;                                              // >= 0: it is the last group of that stage (release the slot after it)
-    };
+    // D (128 columns x 16 rows, fp32) = A (tensor memory: lane = column, 32-bit column = two inputs) x B (the rows of x in
+    // shared memory, K-major, 128-byte swizzle); bf16 inputs, M = 128, N = 16
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+    float acc[ROWS];                                        // the thread's column, one value a row of x
+    uint32_t polls_sums = 0, polls_dfull = 0;               // (counted in instrumented builds only)
 
-    // dequantise group u of the stage into the A buffer `buf` of this lane and tell the MMA warp
-    auto push_group = [&](uint32_t sp32, int u, uint32_t buf) {
+    // dequantise group u of the stage into the A buffer `buf` of this lane (the stores are left in flight)
+    auto push_issue = [&](uint32_t sp32, int u, uint32_t buf) {
       uint32_t wd[WPL];
       const uint32_t src = sp32 + w_off + u * (UNITW * 4);
       if constexpr (WPL % 4 == 0) {
@@ -444,43 +361,72 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
       }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        uint32_t a[4 * S];                                   // the A fragments of the 16-column tile h, step by step
+        const uint32_t tile = a_lane + (static_cast<uint32_t>(16 * h) << 16) + buf * Geo::A_COLS;
 #pragma unroll
-        for (int q = 0; q < 4 * S; ++q) a[q] = pair_reg<BITS, GS, false>(wd, h * 4 * S + q);
-        tmem_store_frag<4 * S>(a_lane + (static_cast<uint32_t>(16 * h) << 16) + buf * Geo::A_COLS, a);
+        for (int st = 0; st < S; ++st) {                      // one A fragment (16 columns x 16 inputs) a store
+          uint32_t a[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) a[j] = pair_reg<BITS, GS, false>(wd, (h * S + st) * 4 + j);
+          tmem_store_frag(tile + 8 * st, a);
+        }
       }
+    };
+    // the stores have landed: count this warp in; the lane's last warp issues the group's MMAs (one thread) and
+    // commits them to the buffer's barrier.  The counter only ever grows: every group adds four.
+    auto push_commit = [&](uint32_t sp32, int u, uint32_t buf) {
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar32_arrive(afull32 + 8 * (2 * kw + buf));
+      uint32_t seen = 0;
+      if (lane == 0)
+        asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(seen) : "r"(stored32 + 4 * (2 * kw + buf)) : "memory");
+      seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
+      if ((seen & 3u) == 3u) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (lane == 0) {
+          const uint32_t a_t = tmem + kw * Geo::LANE_COLS + buf * Geo::A_COLS;
+          const uint32_t d_t = tmem + kw * Geo::LANE_COLS + 2 * Geo::A_COLS + buf * Geo::D_COLS;
+          const uint32_t xb = sp32 + Geo::X_OFF;
+#pragma unroll
+          for (int st = 0; st < S; ++st) {
+            // 64 inputs a swizzled tile, 32 bytes a 16-input step inside its 128-byte rows
+            const uint32_t kin = u * GS + 16 * st;
+            const uint32_t baddr = xb + (kin >> 6) * Geo::XHALF + (kin & 63) * 2;
+            const uint32_t lo = ((baddr >> 4) & 0x3FFFu) | (1u << 16);
+            const uint32_t hi = 64u | (1u << 14) | (2u << 29);
+            const uint64_t bdesc = (static_cast<uint64_t>(hi) << 32) | lo;
+            asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(d_t),
+                         "r"(a_t + 8 * st), "l"(bdesc), "r"(IDESC), "r"(st > 0 ? 1 : 0)
+                         : "memory");
+          }
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(dfull32 + 8 * (2 * kw + buf))
+                       : "memory");
+        }
+        __syncwarp();
+      }
     };
 
     // fold a finished group into acc: acc[r] = fma(xs[r], b - C s, fma(P'[r], s, acc[r]))
-    auto fold_group = [&](const Pending& g0) -> bool {
-      if (!mbar32_wait(dfull32 + 8 * (2 * kw + g0.buf), g0.par, abort32)) return false;
+    // group m's MMAs have completed: its A buffer may be written again and its P' read
+    auto wait_group = [&](uint32_t m) -> bool {
+      if (!mbar32_wait(dfull32 + 8 * (2 * kw + (m & 1)), (m >> 1) & 1, abort32, 0, &polls_dfull)) return false;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      return true;
+    };
+    auto fold_group = [&](uint32_t sp32, int u, uint32_t buf) {
       float P[ROWS];
-      tmem_load_rows(a_lane + 2 * Geo::A_COLS + g0.buf * Geo::D_COLS, P);
-      const uint32_t sbw = lds32(g0.sp32 + sb_off + g0.u * (UNITW * 4));
+      tmem_load_rows(a_lane + 2 * Geo::A_COLS + buf * Geo::D_COLS, P);
+      const uint32_t sbw = lds32(sp32 + sb_off + u * (UNITW * 4));
       const float s = bf16_lo(sbw), c = fmaf(-OFFSET, s, bf16_hi(sbw));
-      const uint32_t xs32 = g0.sp32 + Geo::XS_OFF + g0.u * ROWS * 4;
+      const uint32_t xs32 = sp32 + Geo::XS_OFF + u * ROWS * 4;
 #pragma unroll
       for (int r4 = 0; r4 < ROWS; r4 += 4) {
         const uint4 xq = lds128(xs32 + r4 * 4);
-        const float x0 = __uint_as_float(xq.x), x1 = __uint_as_float(xq.y), x2 = __uint_as_float(xq.z), x3 = __uint_as_float(xq.w);
-#ifdef TF_NO_FMA2
-        acc[r4] = fmaf(x0, c, fmaf(P[r4], s, acc[r4]));
-        acc[r4 + 1] = fmaf(x1, c, fmaf(P[r4 + 1], s, acc[r4 + 1]));
-        acc[r4 + 2] = fmaf(x2, c, fmaf(P[r4 + 2], s, acc[r4 + 2]));
-        acc[r4 + 3] = fmaf(x3, c, fmaf(P[r4 + 3], s, acc[r4 + 3]));
-#else
-        fma2(acc[r4], acc[r4 + 1], P[r4], P[r4 + 1], s, s);
-        fma2(acc[r4], acc[r4 + 1], x0, x1, c, c);
-        fma2(acc[r4 + 2], acc[r4 + 3], P[r4 + 2], P[r4 + 3], s, s);
-        fma2(acc[r4 + 2], acc[r4 + 3], x2, x3, c, c);
-#endif
+        acc[r4] = fmaf(__uint_as_float(xq.x), c, fmaf(P[r4], s, acc[r4]));
+        acc[r4 + 1] = fmaf(__uint_as_float(xq.y), c, fmaf(P[r4 + 1], s, acc[r4 + 1]));
+        acc[r4 + 2] = fmaf(__uint_as_float(xq.z), c, fmaf(P[r4 + 2], s, acc[r4 + 2]));
+        acc[r4 + 3] = fmaf(__uint_as_float(xq.w), c, fmaf(P[r4 + 3], s, acc[r4 + 3]));
       }
-      return true;
     };
 
     struct OutProj {
@@ -503,21 +449,22 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
     // the output of a finished item: the slice itself, or (last warp in) the sum of the slices in slice order
     auto finish_item = [&](const StreamItem& it) {
       pdl_wait();                                           // nothing is written before the previous kernel is done
+      const float (&a)[ROWS] = acc;
       OutProj pr;
       pr.out = TF_PROJ_FIELD(p, it.p, out), pr.ldo = TF_PROJ_FIELD(p, it.p, ldo);
       pr.N = TF_PROJ_FIELD(p, it.p, N), pr.out_f32 = TF_PROJ_FIELD(p, it.p, out_f32);
       const int sb = it.sb0 + kw, n = sb * SB_COLS + tp * 32 + lane;
       if (p.slices_out) {                                   // fp32 [sk, rows_total, N]
         pr.out_f32 = 1, pr.ldo = pr.N;
-        store_out(pr, n, acc, static_cast<int64_t>(it.slice) * p.rows_total + p.row0);
+        store_out(pr, n, a, static_cast<int64_t>(it.slice) * p.rows_total + p.row0);
       } else if (it.sk == 1) {
-        store_out(pr, n, acc, p.row0);
+        store_out(pr, n, a, p.row0);
       } else {
         // rows 4 f .. 4 f + 3 of slice s: float4 index (((sb * sk + s) * 4 + tp) * 4 + f) * 32 + lane
         float* part = TF_PROJ_FIELD(p, it.p, part);
         float4* mine = reinterpret_cast<float4*>(part) + ((static_cast<int64_t>(sb) * it.sk + it.slice) * 4 + tp) * 128 + lane;
 #pragma unroll
-        for (int f = 0; f < 4; ++f) __stcg(mine + f * 32, make_float4(acc[4 * f], acc[4 * f + 1], acc[4 * f + 2], acc[4 * f + 3]));
+        for (int f = 0; f < 4; ++f) __stcg(mine + f * 32, make_float4(a[4 * f], a[4 * f + 1], a[4 * f + 2], a[4 * f + 3]));
         __threadfence();                                    // the slice is visible before this warp counts itself in
         __syncwarp();
         int* counter = TF_PROJ_FIELD(p, it.p, count) + sb * 4 + tp;
@@ -548,66 +495,94 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
       }
     };
 
+    // Main loop.  Step n of a lane: wait for group n - 2's MMAs (its tensor-memory buffers are the ones group n takes),
+    // issue group n's dequantised stores, fold group n - 2 into acc while they fly, then hand group n to the tensor
+    // core.  Group n - 1's MMAs run through the whole step, so their round trip (last warp in, issue, execute, commit)
+    // hides behind a full dequantisation.  A stage's slot is released when its last group has been folded in; at the
+    // end of an item both groups in flight are folded, the item's output goes out and acc starts from zero.
     bool ok = true;
-    bool have_prev = false;
-    Pending prev = {};
-    StreamItem prev_item = {};
-    bool prev_ends_item = false;
     int slot = 0;
     uint32_t phase = 0;                                     // parity of the `sums` phase the current slot waits for
-    uint32_t n = 0;                                         // groups this lane has pushed so far (the MMA warp counts the same)
+    uint32_t n = 0;                                         // groups this lane has pushed so far
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
 
-    // retire the group in flight: fold it in, release its stage if it was the stage's last group, finish its item if it
-    // was the item's last (the idle lanes of a narrow item only release)
-    auto retire = [&]() -> bool {
-      const bool active = kw < prev_item.lanes;
-      if (active && !fold_group(prev)) return false;
-      if (prev.slot >= 0) {
+    struct Flight {                                         // a group whose MMAs may still be running
+      uint32_t sp32;                                        // its stage
+      int u;                                                // its index in the stage (-1: none)
+      int release;                                          // >= 0: the stage's slot, to release once the group is folded in
+    };
+    auto retire = [&](const Flight& f, uint32_t m) {        // fold group m (already waited for) and release what ends with it
+      fold_group(f.sp32, f.u, m & 1);
+      if (f.release >= 0) {
         __syncwarp();
-        if (lane == 0) mbar32_arrive(empty32 + 8 * prev.slot);
+        if (lane == 0) mbar32_arrive(empty32 + 8 * f.release);
       }
-      if (prev_ends_item) {
-        if (active) finish_item(prev_item);
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
-      }
-      return true;
     };
 
     for (int i = first_item; i < p.items && ok; i += step) {
       const StreamItem it = stream_item<KW, G>(p, i);
-      const bool active = kw < it.lanes;
+      if (kw >= it.lanes) {
+        // an idle lane of a narrow item: it only keeps the ring turning
+        for (int st = 0; st < it.nst && ok; ++st) {
+          ok = mbar32_wait(sums32 + 8 * slot, phase, abort32, 128);
+          if (!ok) {
+            give_up(ERR_WAIT_SUMS);
+            break;
+          }
+          if (lane == 0) mbar32_arrive(empty32 + 8 * slot);
+          if (++slot == NST) slot = 0, phase ^= 1;
+        }
+        continue;
+      }
+      Flight f1 = {0, -1, -1}, f2 = {0, -1, -1};            // groups n - 1 and n - 2
       for (int st = 0; st < it.nst && ok; ++st) {
         const uint32_t sp32 = smem32 + slot * Geo::STAGE;
-        ok = mbar32_wait(sums32 + 8 * slot, phase, abort32);
+        ok = mbar32_wait(sums32 + 8 * slot, phase, abort32, 0, &polls_sums);
         if (!ok) {
           give_up(ERR_WAIT_SUMS);
           break;
         }
         const int ng = min(G, it.per - st * G);
-        for (int u = 0; u < ng; ++u) {
-          const uint32_t buf = n & 1, par = (n >> 1) & 1;
-          if (active) {
-            push_group(sp32, u, buf);
-            ++n;
+#pragma unroll
+        for (int u = 0; u < G; ++u) {
+          if (u >= ng) break;
+          if (f2.u >= 0) {
+            ok = wait_group(n - 2);
+            if (!ok) break;
           }
-          if (have_prev && !retire()) {
-            give_up(ERR_WAIT_FULL);
-            ok = false;
-            break;
-          }
-          prev.sp32 = sp32, prev.u = u, prev.buf = buf, prev.par = par;
-          prev.slot = u == ng - 1 ? slot : -1;
-          prev_item = it;
-          prev_ends_item = st == it.nst - 1 && u == ng - 1;
-          have_prev = true;
+          push_issue(sp32, u, n & 1);
+          if (f2.u >= 0) retire(f2, n - 2);
+          push_commit(sp32, u, n & 1);
+          f2 = f1;
+          f1.sp32 = sp32, f1.u = u, f1.release = u == ng - 1 ? slot : -1;
+          ++n;
+        }
+        if (!ok) {
+          give_up(ERR_WAIT_FULL);
+          break;
         }
         if (++slot == NST) slot = 0, phase ^= 1;
       }
+      if (!ok) break;
+      // drain: the item's last two groups
+      if (f2.u >= 0) {
+        ok = wait_group(n - 2);
+        if (ok) retire(f2, n - 2);
+      }
+      if (ok) ok = wait_group(n - 1);
+      if (!ok) {
+        give_up(ERR_WAIT_FULL);
+        break;
+      }
+      retire(f1, n - 1);
+      finish_item(it);
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
     }
-    if (ok && have_prev && !retire()) give_up(ERR_WAIT_FULL);
+#ifdef TF_WAIT_STATS
+    if (lane == 0 && blockIdx.x < 2) printf("block %d warp %d: polls sums %u dfull %u groups %u\n", blockIdx.x, warp, polls_sums, polls_dfull, n);
+#endif
   }
 
   // ---------------------------------------------------------------------- tensor memory goes back on every path

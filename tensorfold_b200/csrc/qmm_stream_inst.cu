@@ -44,17 +44,20 @@ cudaError_t configure() {
   }
 }
 
-// blocks of that shape an SM holds: what the occupancy query says, never more than the tensor memory allows
+// Blocks of that shape an SM holds: the design figure.  The launch bounds guarantee the registers and the static
+// assertion the shared memory for that many; the runtime's occupancy query answers 1 for any kernel that allocates
+// tensor memory, whatever it allocates, so it only serves to tell whether the kernel can be launched at all.
 template <int GS, int KW>
 int resident() {
   using Geo = StreamGeo<TF_BITS, GS, KW>;
   if constexpr (!Geo::FITS) {
     return 0;
   } else {
+    static_assert(Geo::BLOCKS * (Geo::SMEM + 1024) <= 228 * 1024, "the resident blocks fit the shared memory of an SM");
     int blocks = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, qmm_stream_kernel<TF_BITS, GS, KW>, Geo::THREADS, Geo::SMEM) != cudaSuccess)
       return 0;
-    return blocks < Geo::BLOCKS ? blocks : Geo::BLOCKS;
+    return blocks < 1 ? 0 : Geo::BLOCKS;
   }
 }
 

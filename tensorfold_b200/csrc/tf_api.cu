@@ -520,6 +520,29 @@ int64_t tf_qmm_set_scratch_bytes(int nproj, const int* n, const int* sk) {
   return total;
 }
 
+int tf_qmm_set_geometry(int bits, int gs, int nproj, const int* n, const int* sk, int* lanes, int* blocks_per_sm, int* grid) {
+  if (!format_ok(bits, gs) || bits == 8 || nproj < 1 || nproj > STREAM_MAX_PROJ || !n || !sk)
+    return fail(TF_ERR_ARG, "tf_qmm_set_geometry: bad arguments");
+  DeviceState* st = nullptr;
+  if (int rc = current_state(&st)) return rc;
+  int64_t units = 0;
+  for (int i = 0; i < nproj; ++i) units += static_cast<int64_t>((n[i] + SB_COLS - 1) / SB_COLS) * sk[i];
+  int kw = g_stream_lanes > 0 ? g_stream_lanes : (units >= 2 * st->sms ? 2 : 1);
+  int resident = st->resident[bits_index(bits)][gs_index(gs)][kw_index(kw)];
+  while (resident < 1 && kw > 1) {
+    kw /= 2;
+    resident = st->resident[bits_index(bits)][gs_index(gs)][kw_index(kw)];
+  }
+  if (resident < 1) return fail(TF_ERR_STATE, "tf_qmm_set_geometry: the streaming kernel does not fit an SM of this device");
+  if (g_stream_blocks > 0 && g_stream_blocks < resident) resident = g_stream_blocks;
+  int64_t items = 0;
+  for (int i = 0; i < nproj; ++i) items += static_cast<int64_t>(((n[i] + SB_COLS - 1) / SB_COLS + kw - 1) / kw) * sk[i];
+  if (lanes) *lanes = kw;
+  if (blocks_per_sm) *blocks_per_sm = resident;
+  if (grid) *grid = static_cast<int>(std::min<int64_t>(items, static_cast<int64_t>(st->sms) * resident));
+  return TF_OK;
+}
+
 int tf_qmm_set(const void* x, int64_t ldx, int m, const float* xs, int k, int bits, int gs, int nproj,
                const void* const* tiled, const int64_t* sb_stride, const int* n, const int* sk, void* const* out,
                const int64_t* ldo, int out_f32, int slices_out, void* scratch, int64_t scratch_bytes, int pdl, void* stream) {

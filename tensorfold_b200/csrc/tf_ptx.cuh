@@ -127,11 +127,22 @@ __device__ __forceinline__ bool mbar32_try_wait(uint32_t bar, uint32_t parity) {
                : "memory");
   return ok != 0;
 }
-// The slow path of a wait, kept out of line so the loops that call it stay short: polls with a suspend hint until the
-// phase completes, WAIT_POLLS polls have passed or another warp of the block has given up (abort word != 0).
-static __device__ __noinline__ bool mbar32_wait_slow(uint32_t bar, uint32_t parity, uint32_t abort_word) {
+// Bounded wait by a whole warp: polls (each poll may suspend the warp in hardware for a while) until the phase
+// completes, WAIT_POLLS polls have passed or another warp of the block has given up (abort word != 0).  `nap` > 0 adds
+// that many nanoseconds of sleep between polls, for waits that are not latency-critical (a warp that polls flat out
+// takes issue slots from the warps that work).  False (for all lanes alike) when the wait gave up.
+#ifdef TF_WAIT_STATS
+#define TF_COUNT_POLL(polls) ++(polls)
+#else
+#define TF_COUNT_POLL(polls) (void)0
+#endif
+__device__ __forceinline__ bool mbar32_wait(uint32_t bar, uint32_t parity, uint32_t abort_word, uint32_t nap = 0,
+                                            uint32_t* polls = nullptr) {
+  if (__all_sync(0xFFFFFFFFu, mbar32_try_wait(bar, parity))) return true;
   bool ok = false;
+#pragma unroll 1
   for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+    if (polls) TF_COUNT_POLL(*polls);
     uint32_t done;
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
                  : "=r"(done)
@@ -141,6 +152,7 @@ static __device__ __noinline__ bool mbar32_wait_slow(uint32_t bar, uint32_t pari
       ok = true;
       break;
     }
+    if (nap) __nanosleep(nap);
     if ((i & 255u) == 255u) {
       uint32_t gone;
       asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(gone) : "r"(abort_word));
@@ -148,11 +160,6 @@ static __device__ __noinline__ bool mbar32_wait_slow(uint32_t bar, uint32_t pari
     }
   }
   return __all_sync(0xFFFFFFFFu, ok);
-}
-// Bounded wait by a whole warp: one probe inline, the polling loop out of line.  False (for all lanes) when it gave up.
-__device__ __forceinline__ bool mbar32_wait(uint32_t bar, uint32_t parity, uint32_t abort_word) {
-  if (__all_sync(0xFFFFFFFFu, mbar32_try_wait(bar, parity))) return true;
-  return mbar32_wait_slow(bar, parity, abort_word);
 }
 __device__ __forceinline__ void bulk_load32(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
@@ -251,6 +258,27 @@ __device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, f
       "fma.rn.f32x2 rd, ra, rb, rd;\nmov.b64 {%0, %1}, rd;\n}"
       : "+f"(d0), "+f"(d1)
       : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+
+// Two fp32 values in one 64-bit register, the operand form of fma.rn.f32x2.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// a * b + c on both halves, each an IEEE fp32 fused multiply-add (the bits of two fmaf calls)
+__device__ __forceinline__ uint64_t fma2p(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
 }
 
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
