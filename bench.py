@@ -25,9 +25,11 @@ if str(ROOT) not in sys.path:
 BITS, GS = 4, 64
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126 * 2 ** 20
-# DRAM bytes per launch of the dominant kernel: the ncu capture under profiles/ read 50.32 MB for gate_proj's 50.86 MB of
-# algorithmic bytes (ratio 0.99); scaled to the average launch of a step (traffic grows with the weight bytes).
-TRAFFIC_RATIO = 0.99
+# DRAM bytes per launch of the dominant kernel over its algorithmic bytes, from one ncu capture of a gate/up set launch
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch; traffic grows with the weight bytes, so a step's
+# launches scale by it).
+TRAFFIC_RATIO = 1.04
+SETS = (("q_proj", "k_proj", "v_proj"), ("o_proj",), ("gate_proj", "up_proj"), ("down_proj",))   # launches of a step
 
 
 def weight_bytes(n: int, k: int, bits: int = BITS, gs: int = GS) -> int:
@@ -118,11 +120,17 @@ def layer_shapes():
 # the reference arm and the CPU baseline: the oracle's restatement of the reference's CPU path, on the host cores
 # ----------------------------------------------------------------------------------------------------------------------
 
-SAMPLE = ("q_proj", "k_proj", "v_proj", "o_proj")        # attention projections: 41.3 MB of packed weights a step
+def host_threads() -> int:
+    """Threads the CPU arm uses: every core this process may run on, whatever OMP_NUM_THREADS a launcher exported."""
+
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 def cpu_pass(inputs, rows: int) -> None:
-    """One pass of the CPU restatement (dequantise to float32 then x.float() @ w.T, all host threads) over the sample."""
+    """One pass of the CPU restatement (dequantise to float32 then x.float() @ w.T, all host threads) over the layer."""
 
     from oracle import native
 
@@ -131,36 +139,83 @@ def cpu_pass(inputs, rows: int) -> None:
 
 
 def cpu_inputs(rows: int):
+    """The seven projections of one layer, as the B200 arm runs them."""
+
     from tensorfold_b200 import synthetic
 
     out = []
-    for name in SAMPLE:
-        n, k = synthetic.DENSE_27B[name]
+    for name, (n, k) in synthetic.DENSE_27B.items():
         words, scales, biases = synthetic.affine_weight(n, k, BITS, GS, seed=len(out))
         x = synthetic.activations(rows, k, len(out))
         out.append((words.numpy(), synthetic.bf16_bits(scales), synthetic.bf16_bits(biases), synthetic.bf16_bits(x)))
     return out
 
 
-def sample_bytes() -> int:
+def layer_bytes_total() -> int:
     from tensorfold_b200 import synthetic
 
-    return sum(weight_bytes(*synthetic.DENSE_27B[name]) for name in SAMPLE)
+    return sum(weight_bytes(n, k) for n, k in synthetic.DENSE_27B.values())
+
+
+def reference_torch_baseline(rows: int) -> dict:
+    """The reference's own CPU-runnable code for this op, where its checkout can be imported (TENSORFOLD_REFERENCE, or
+    /root/reference when present): ``dequantize`` (families/qwen3_5/cuda/qmm.py:132-149) then ``x.float() @ w.T``, timed
+    both ways on one projection (q_proj), all host threads.  Also records whether MLX (the reference's named CPU
+    baseline, ``mx.quantized_matmul`` on mx.cpu) can be imported on this box."""
+
+    import importlib
+
+    out = {}
+    try:
+        importlib.import_module("mlx.core")
+        out["mlx"] = "importable"
+    except Exception as exc:                                 # noqa: BLE001
+        out["mlx"] = f"MLX unavailable on this box ({type(exc).__name__})"
+    root = os.environ.get("TENSORFOLD_REFERENCE") or ("/root/reference" if os.path.isdir("/root/reference/src/tensorfold") else "")
+    if not root:
+        out["reference_torch"] = "reference checkout not present on this box"
+        return out
+    try:
+        import torch
+
+        sys.path.insert(0, os.path.join(root, "src"))
+        ref = importlib.import_module("tensorfold.families.qwen3_5.cuda.qmm")
+        from tensorfold_b200 import synthetic
+
+        torch.set_num_threads(host_threads())
+        n, k = synthetic.DENSE_27B["q_proj"]
+        words, scales, biases = synthetic.affine_weight(n, k, BITS, GS, seed=0)
+        x = synthetic.activations(rows, k, 0)
+        t0 = time.perf_counter()
+        w = ref.dequantize(words, scales, biases, GS, BITS)
+        t1 = time.perf_counter()
+        y = x.float() @ w.float().T
+        t2 = time.perf_counter()
+        del y
+        out["reference_torch"] = {"projection": "q_proj", "dequantize_plus_matmul_gb_s": weight_bytes(n, k) / (t2 - t0) / 1e9,
+                                  "matmul_on_dequantised_gb_s": weight_bytes(n, k) / (t2 - t1) / 1e9, "threads": host_threads()}
+    except Exception as exc:                                 # noqa: BLE001
+        out["reference_torch"] = f"reference import failed: {type(exc).__name__}: {exc}"[:200]
+    return out
 
 
 def cpu_baseline(rows: int, budget_s: float = 15.0) -> dict:
     from oracle import native
 
+    native.set_threads(host_threads())
     inputs = cpu_inputs(rows)
     cpu_pass(inputs, rows)                               # warm the pages
     t0, reps = time.perf_counter(), 0
-    while reps < 3 or (time.perf_counter() - t0 < budget_s and reps < 50):
+    while reps < 2 or (time.perf_counter() - t0 < budget_s and reps < 50):
         cpu_pass(inputs, rows)
         reps += 1
     dt = (time.perf_counter() - t0) / reps
-    return {"value": sample_bytes() / dt / 1e9, "unit": "GB/s", "cores": native.threads(), "kind": "port",
-            "sample": f"q/k/v/o projections of one dense-27B layer at M={rows} ({sample_bytes() / 1e6:.1f} MB of packed "
-                      f"weights), {reps} passes of oracle/affine_ref.c (dequantise to float32, float32 dot, OpenMP)"}
+    total = layer_bytes_total()
+    out = {"value": total / dt / 1e9, "unit": "GB/s", "cores": native.threads(), "kind": "port",
+           "sample": f"all seven projections of one dense-27B layer at M={rows} ({total / 1e6:.1f} MB of packed "
+                     f"weights), {reps} passes of oracle/affine_ref.c (dequantise to float32, float32 dot, OpenMP)"}
+    out.update(reference_torch_baseline(rows))
+    return out
 
 
 def run_reference(args) -> None:
@@ -169,6 +224,7 @@ def run_reference(args) -> None:
         return
     from oracle import native
 
+    native.set_threads(host_threads())                   # not the one thread a torchrun launcher exports
     inputs = cpu_inputs(args.rows)
     for _ in range(min(args.warmup, 2)):
         cpu_pass(inputs, args.rows)
@@ -176,15 +232,22 @@ def run_reference(args) -> None:
     for _ in range(args.steps):
         cpu_pass(inputs, args.rows)
     dt = time.perf_counter() - t0
-    value = sample_bytes() * args.steps / dt / 1e9
-    sample = (f"each step = q/k/v/o projections of one dense-27B layer at M={args.rows} "
-              f"({sample_bytes() / 1e6:.1f} MB packed weights) on the host cores")
+    total = layer_bytes_total()
+    value = total * args.steps / dt / 1e9
+    sample = (f"each step = the seven projections of one dense-27B layer at M={args.rows} "
+              f"({total / 1e6:.1f} MB packed weights) on the host cores")
+    from tensorfold_b200 import synthetic
+
+    baseline = {"value": value, "unit": "GB/s", "cores": native.threads(), "kind": "port", "sample": sample}
+    baseline.update(reference_torch_baseline(args.rows))
     print(json.dumps({
         "impl": "reference", "metric": "affine_4bit_g64_qmm_weight_gbps", "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"dense27b_layer_projections_4bit_g64_M{args.rows}", "rows": args.rows, "sample": sample},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": native.threads(), "kind": "port", "sample": sample},
+        "config": {"workload": f"dense27b_layer_projections_4bit_g64_M{args.rows}", "rows": args.rows, "bits": BITS, "group": GS,
+                   "projections": {name: list(shape) for name, shape in synthetic.DENSE_27B.items()},
+                   "weight_bytes_per_step": total, "sample": sample},
+        "cpu_baseline": baseline,
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -192,6 +255,19 @@ def run_reference(args) -> None:
 # ----------------------------------------------------------------------------------------------------------------------
 # the B200 arm
 # ----------------------------------------------------------------------------------------------------------------------
+
+_side_stream = []
+
+
+def side_stream():
+    """The one stream the side figures capture on (each stream that runs the decode kernel holds a scratch area)."""
+
+    import torch
+
+    if not _side_stream:
+        _side_stream.append(torch.cuda.Stream())
+    return _side_stream[0]
+
 
 def graph_time(fn, steps: int, stream, reps: int = 5):
     """Capture `steps` calls of fn(i) in one CUDA graph on `stream`; returns (graph, [ms per replay])."""
@@ -246,7 +322,7 @@ def moe_layer_bench(dev, rows_list=(16, 2048)) -> dict:
     wr = (torch.randn((e + 1, d), generator=g) * 0.05).to(torch.bfloat16).to(dev)
     layer = moe.Routed(wr, ex, top_k, shared)
     out = {}
-    stream = torch.cuda.Stream()
+    stream = side_stream()
     per_expert = 3 * weight_bytes(ni, d)
     for rows in rows_list:
         xs = [synthetic.activations(rows, d, 40 + i).to(dev) for i in range(4)]       # different routings in turn
@@ -267,8 +343,18 @@ def moe_layer_bench(dev, rows_list=(16, 2048)) -> dict:
     return out
 
 
+def layer_sets(xs, layer, ys, splits, pdl: bool) -> None:
+    """One layer as the four launches of its dataflow: q/k/v in one persistent launch, o_proj, gate/up in one, down_proj."""
+
+    from tensorfold_b200.cuda.kernels import qmm
+
+    for names in SETS:
+        qmm.matmul_set(xs[names[0]], [layer[n] for n in names], sks=[splits[n] for n in names], outs=[ys[n] for n in names], pdl=pdl)
+
+
 def dense_rows_bench(dev, layers, shapes, ring, splits) -> dict:
-    """The same layer at other row counts: weight GB/s at M = 1, 4, 16 and TFLOP/s at M = 2048 (through ``matmul``)."""
+    """The same layer at other row counts: weight GB/s at M = 1, 4, 8, 16 (four set launches a layer) and TFLOP/s at
+    M = 2048 (through ``matmul``: the row-exact decode arithmetic) and through the tcgen05 prefill kernel."""
 
     import torch
 
@@ -276,23 +362,28 @@ def dense_rows_bench(dev, layers, shapes, ring, splits) -> dict:
     from tensorfold_b200.cuda.kernels import qmm
 
     layer_bytes = sum(weight_bytes(n, k) for _, (n, k) in shapes)
-    stream = torch.cuda.Stream()
+    peak, _ = measured_peaks()
+    stream = side_stream()
     out = {}
-    for rows in (1, 4, 16, 2048):
+    for rows in (1, 4, 8, 16, 2048):
         xs = {name: synthetic.activations(rows, k, 3).to(dev) for name, (n, k) in shapes}
         ys = {name: torch.empty((rows, n), dtype=torch.bfloat16, device=dev) for name, (n, k) in shapes}
 
         def fn(i):
-            for name, _ in shapes:
-                qmm.matmul(xs[name], layers[i % ring][name], out=ys[name], pdl=True, sk=splits[name])
+            if rows <= 16:
+                layer_sets(xs, layers[i % ring], ys, splits, True)
+            else:
+                for name, _ in shapes:
+                    qmm.matmul(xs[name], layers[i % ring][name], out=ys[name], pdl=True, sk=splits[name])
 
-        for i in range(2):
-            fn(i)
+        with torch.cuda.stream(stream):
+            for i in range(2):
+                fn(i)
         torch.cuda.synchronize()
         steps = 2 * ring if rows <= 16 else 2
         _, times = graph_time(fn, steps, stream)
         us = sorted(times)[len(times) // 2] * 1e3 / steps
-        entry = {"us_per_layer": us, "weight_gb_s": layer_bytes / us / 1e3}
+        entry = {"us_per_layer": us, "weight_gb_s": layer_bytes / us / 1e3, "of_measured_hbm": layer_bytes / us / 1e3 / peak}
         if rows >= 256:
             flops = 2 * rows * sum(n * k for _, (n, k) in shapes)
             entry["tflops"] = flops / us / 1e6                               # the row-exact decode arithmetic at M rows
@@ -311,44 +402,82 @@ def dense_rows_bench(dev, layers, shapes, ring, splits) -> dict:
     return out
 
 
-def stacked_layer_bench(dev, rows_list=(1, 16)) -> dict:
-    """The same layer with the projections that share an input stacked at load time (q|k|v and gate|up, the reference's
-    ``qmm_fast.stack``): four launches a layer instead of seven.  Stacking changes K splits, hence bits, so it is a
-    load-time decision; reported beside the headline, which keeps the seven separate projections."""
+def single_matmul_bench(dev, n: int, k: int, bits: int, gs: int, rows_list, seed: int = 0) -> dict:
+    """One projection at the given row counts over a ring of weight copies larger than L2: microseconds a call, packed
+    weight GB/s and the fraction of the measured HBM peak."""
 
     import torch
 
     from tensorfold_b200 import synthetic
     from tensorfold_b200.cuda.kernels import qmm
 
-    shapes = dict(layer_shapes())
-    stacks = {"qkv": ("q_proj", "k_proj", "v_proj"), "o": ("o_proj",), "gate_up": ("gate_proj", "up_proj"), "down": ("down_proj",)}
-    layer_bytes = sum(weight_bytes(n, k) for n, k in shapes.values())
-    ring = max(2, -(-4 * L2_BYTES // layer_bytes))
-    layers = []
-    for li in range(ring):
-        packed = {}
-        for si, (sname, parts) in enumerate(stacks.items()):
-            ws = [synthetic.affine_weight(*shapes[p], BITS, GS, seed=5000 + 100 * li + 10 * si + j) for j, p in enumerate(parts)]
-            packed[sname] = qmm.pack(torch.cat([w[0] for w in ws]).to(dev), torch.cat([w[1] for w in ws]).to(dev),
-                                     torch.cat([w[2] for w in ws]).to(dev), GS)
-        layers.append(packed)
-    stream = torch.cuda.Stream()
+    peak, _ = measured_peaks()
+    nbytes = weight_bytes(n, k, bits, gs)
+    ring = max(3, -(-3 * L2_BYTES // nbytes))
+    w = synthetic.affine_weight(n, k, bits, gs, seed=seed)
+    base = qmm.pack(w[0].to(dev), w[1].to(dev), w[2].to(dev), gs, bits=bits)
+    copies = [base] + [qmm.Q4(base.weight.clone(), None, None, n, k, gs, bits) for _ in range(ring - 1)]
+    stream = side_stream()
     out = {}
     for rows in rows_list:
-        xs = {s: synthetic.activations(rows, layers[0][s].k, 3).to(dev) for s in stacks}
-        ys = {s: torch.empty((rows, layers[0][s].n), dtype=torch.bfloat16, device=dev) for s in stacks}
-
-        def fn(i):
-            for s in stacks:
-                qmm.matmul(xs[s], layers[i % ring][s], out=ys[s], pdl=True)
-
-        for i in range(2):
-            fn(i)
+        x = synthetic.activations(rows, k, 3).to(dev)
+        y = torch.empty((rows, n), dtype=torch.bfloat16, device=dev)
+        fn = lambda i: qmm.matmul(x, copies[i % ring], out=y, pdl=True)
+        with torch.cuda.stream(stream):
+            fn(0), fn(1)
         torch.cuda.synchronize()
         _, times = graph_time(fn, 4 * ring, stream)
         us = sorted(times)[len(times) // 2] * 1e3 / (4 * ring)
-        out[f"M{rows}"] = {"us_per_layer": us, "weight_gb_s": layer_bytes / us / 1e3, "launches_per_layer": len(stacks)}
+        out[f"M{rows}"] = {"us": us, "weight_gb_s": nbytes / us / 1e3, "of_measured_hbm": nbytes / us / 1e3 / peak}
+    del copies
+    torch.cuda.empty_cache()
+    return out
+
+
+def cfg0_bench(dev) -> dict:
+    """The CPU-runnable reference configuration: one 4096 x 4096 affine 4-bit / group-64 matmul at M = 4 (seed 0)."""
+
+    return single_matmul_bench(dev, 4096, 4096, BITS, GS, (4,), seed=0)
+
+
+def cfg3_bench(dev) -> dict:
+    """The mixed-width sweep on a 4096 -> 14336 projection: 2, 3, 5, 6 and 8 bits x groups of 32, 64, 128 at M = 1, 16."""
+
+    out = {}
+    for bits in (2, 3, 5, 6, 8):
+        for gs in (32, 64, 128):
+            out[f"b{bits}_g{gs}"] = single_matmul_bench(dev, 14336, 4096, bits, gs, (1, 16), seed=bits * 10 + gs)
+    return out
+
+
+def lm_head_bench(dev) -> dict:
+    """The 248,320-row head of the dense 27B model as one matmul (715 MB of packed weights: larger than L2 by itself)."""
+
+    import torch
+
+    from tensorfold_b200 import synthetic
+    from tensorfold_b200.cuda.kernels import qmm
+
+    peak, _ = measured_peaks()
+    n, k, block = 248320, 5120, 8192
+    w = synthetic.affine_weight(block, k, BITS, GS, seed=91)
+    part = qmm.pack(w[0].to(dev), w[1].to(dev), w[2].to(dev), GS)
+    reps = -(-n // block)
+    weight = part.weight.repeat(reps, 1, 1)[: -(-n // 128)].contiguous()      # distinct memory for every super-block
+    head = qmm.Q4(weight, None, None, n, k, GS, BITS)
+    nbytes = weight_bytes(n, k)
+    stream = side_stream()
+    out = {}
+    for rows in (1, 16):
+        x = synthetic.activations(rows, k, 3).to(dev)
+        y = torch.empty((rows, n), dtype=torch.bfloat16, device=dev)
+        fn = lambda i: qmm.matmul(x, head, out=y, pdl=True)
+        with torch.cuda.stream(stream):
+            fn(0)
+        torch.cuda.synchronize()
+        _, times = graph_time(fn, 4, stream)
+        us = sorted(times)[len(times) // 2] * 1e3 / 4
+        out[f"M{rows}"] = {"us": us, "weight_gb_s": nbytes / us / 1e3, "of_measured_hbm": nbytes / us / 1e3 / peak}
     return out
 
 
@@ -418,7 +547,7 @@ def glue_bench(dev) -> dict:
     from tensorfold_b200.families.qwen3_5.cuda import glue
 
     peak, _ = measured_peaks()
-    stream = torch.cuda.Stream()
+    stream = side_stream()
     d, n = 5120, 17408
     out = {"add_rmsnorm": {}, "swiglu": {}}
     for rows in (16, 2048):
@@ -573,56 +702,40 @@ def run_b200(args) -> None:
     torch.cuda.synchronize()
 
     if args.lanes:
-        _lib.check(_lib.lib().tf_tune(b"qmm_lanes", args.lanes), "tune")
-    branches = not args.no_branches
-    paired = ("gate_proj", "up_proj") if branches else ()    # forked as an equal pair: each aims for half the machine
-    splits = {name: (qmm.split_k(nout[name], kin[name], GS, args.sk_target) if args.sk_target
-                     else qmm.default_split(nout[name], kin[name], GS, share=args.pair_share if name in paired else 1)) for name, _ in shapes}
+        _lib.check(_lib.lib().tf_tune(b"stream_lanes", args.lanes), "tune")
+    splits = {}                                              # a load-time decision per projection: its set fills the lanes once
+    for names in SETS:
+        counts = qmm.set_splits([(nout[n], kin[n]) for n in names], GS)
+        splits.update({n: (qmm.split_k(nout[n], kin[n], GS, args.sk_target) if args.sk_target else c) for n, c in zip(names, counts)})
+    row_parallel = ("o_proj", "down_proj") if world > 1 else ()
+    partial = {name: torch.empty((rows, nout[name]), dtype=torch.float32, device=dev) for name in row_parallel}
     reduced = {}
 
     def step(i: int, pdl: bool) -> None:
+        """One layer as the launches of its dataflow: q/k/v (one persistent launch), o_proj (attention sits between them
+        in a model), gate/up (one launch), down_proj.  With several ranks the sets are column-parallel and o/down
+        row-parallel: an fp32 partial, then the rank-ordered reduction with one rounding."""
+
         layer = layers[i % ring]
-
-        def mm(name: str, p: bool):
-            return lambda: qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=p, sk=splits[name])
-
-        def row_parallel(name: str):                        # bf16 partial, then the rank-ordered reduction
-            qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=False, sk=splits[name])
-            reduced[name] = tp.ordered_all_reduce(dev_y[name])
-
-        if branches:
-            # the layer's dataflow: q/k/v read the same rows and so do gate/up, so each set runs side by side; o_proj
-            # waits for the first set (attention sits between them in a model), down_proj for the second.  With
-            # several ranks only the column-parallel sets fork; the collectives stay on the main stream.
-            chain = pdl and not args.no_chain_pdl          # main-stream launches overlap their predecessor's tail
-            qmm.fork_join([mm("q_proj", pdl), mm("k_proj", False), mm("v_proj", False)])
-            if world > 1:
-                row_parallel("o_proj")
+        for names in SETS:
+            if names[0] in row_parallel:
+                qmm.matmul(dev_x[names[0]], layer[names[0]], f32=True, out=partial[names[0]], pdl=False, sk=splits[names[0]])
+                reduced[names[0]] = tp.ordered_all_reduce(partial[names[0]])
             else:
-                mm("o_proj", chain)()
-            qmm.fork_join([mm("gate_proj", chain), mm("up_proj", False)])
-            if world > 1:
-                row_parallel("down_proj")
-            else:
-                mm("down_proj", chain)()
-            return
-        for name, _ in shapes:
-            if world > 1 and name not in column:            # row-parallel: bf16 partial, rank-ordered reduction
-                qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=False, sk=splits[name])
-                reduced[name] = tp.ordered_all_reduce(dev_y[name])
-            else:
-                qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=pdl and world == 1, sk=splits[name])
+                qmm.matmul_set(dev_x[names[0]], [layer[n] for n in names], sks=[splits[n] for n in names],
+                               outs=[dev_y[n] for n in names], pdl=pdl and world == 1)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(max(args.warmup, 3)):                     # eager warm-up (also the first, configuring, calls)
-        step(i, False)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, 3)):                 # eager warm-up (also the first, configuring, calls)
+            step(i, False)
     barrier()
 
-    stream = torch.cuda.Stream()
     pdl = not args.no_pdl and world == 1
 
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
@@ -639,14 +752,12 @@ def run_b200(args) -> None:
         raise KeyError(last_name)
 
     def e2e_step(i: int) -> None:
-        """One layer with its copies overlapped: q/k/v's rows go in first, the other inputs while q/k/v run; each set's
-        results leave for the host while the next set computes.  Every byte of the step still crosses in the step."""
+        """One layer with its copies overlapped: q/k/v's rows go in first, the other inputs while q/k/v run; each
+        launch's results leave for the host while the next one computes.  Every byte of the step still crosses in the
+        step."""
 
         layer = layers[i % ring]
         main = torch.cuda.current_stream()
-
-        def mm(name: str):
-            return lambda: qmm.matmul(dev_x[name], layer[name], out=dev_y[name], pdl=False, sk=splits[name])
 
         def after(stream_to, fn):                           # fn on stream_to once everything queued on main is done
             ev = torch.cuda.Event()
@@ -655,25 +766,19 @@ def run_b200(args) -> None:
             with torch.cuda.stream(stream_to):
                 fn()
 
-        def result(first_name, last_name):
-            lo, hi = span(y_sizes, first_name, last_name)
-            after(copy_out, lambda: host_y_slab[lo:hi].copy_(dev_y_slab[lo:hi], non_blocking=True))
-
         lo, hi = span(x_sizes, "q_proj", "v_proj")
         rest = span(x_sizes, "o_proj", "down_proj")
         after(copy_in, lambda: dev_x_slab[rest[0]:rest[1]].copy_(host_x_slab[rest[0]:rest[1]], non_blocking=True))
         staged = torch.cuda.Event()
         staged.record(copy_in)
         dev_x_slab[lo:hi].copy_(host_x_slab[lo:hi], non_blocking=True)
-        qmm.fork_join([mm("q_proj"), mm("k_proj"), mm("v_proj")])
-        result("q_proj", "v_proj")
-        main.wait_event(staged)
-        mm("o_proj")()
-        result("o_proj", "o_proj")
-        qmm.fork_join([mm("gate_proj"), mm("up_proj")])
-        result("gate_proj", "up_proj")
-        mm("down_proj")()
-        result("down_proj", "down_proj")
+        for si, names in enumerate(SETS):
+            if si == 1:
+                main.wait_event(staged)
+            qmm.matmul_set(dev_x[names[0]], [layer[n] for n in names], sks=[splits[n] for n in names],
+                           outs=[dev_y[n] for n in names], pdl=False)
+            a, b = span(y_sizes, names[0], names[-1])
+            after(copy_out, lambda a=a, b=b: host_y_slab[a:b].copy_(dev_y_slab[a:b], non_blocking=True))
         done = torch.cuda.Event()
         done.record(copy_out)
         main.wait_event(done)
@@ -683,7 +788,7 @@ def run_b200(args) -> None:
         with torch.cuda.stream(stream):
             with torch.cuda.graph(graph, stream=stream):
                 for i in range(first, first + count):
-                    if with_copies and world == 1 and branches:
+                    if with_copies and world == 1:
                         e2e_step(i)
                         continue
                     if with_copies:
@@ -761,20 +866,21 @@ def run_b200(args) -> None:
             extras[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     if world == 1:
-        extra("moe_layer", lambda: moe_layer_bench(dev))
-        extra("dense_rows", lambda: dense_rows_bench(dev, layers, shapes, ring,
-                                                     {name: qmm.default_split(nout[name], kin[name], GS) for name, _ in shapes}))
+        extra("dense_rows", lambda: dense_rows_bench(dev, layers, shapes, ring, splits))
         del layers
         torch.cuda.empty_cache()
-        extra("stacked_layer", lambda: stacked_layer_bench(dev))
+        extra("cfg0", lambda: cfg0_bench(dev))
+        extra("cfg3", lambda: cfg3_bench(dev))
+        extra("lm_head", lambda: lm_head_bench(dev))
+        extra("moe_layer", lambda: moe_layer_bench(dev))
         extra("glue", lambda: glue_bench(dev))
         extra("load_path", lambda: load_path_bench(dev))
     if "all" in wanted or "moe_block" in wanted:
         extras["moe_block"] = moe_block_tp_bench(dev, rank, world)      # holds collectives: every rank runs it or none
 
-    launches = args.steps * (len(shapes) + (2 if world > 1 else 0))
+    per_step = len(SETS)                                     # launches of this library a step (the collectives are NCCL's)
+    launches = args.steps * (per_step + 2 * len(row_parallel))           # + the rank-ordered sum kernels
     io_bytes = sum(2 * rows * (n + k) for _, (n, k) in shapes)
-    algo_bytes_step = layer_bytes + io_bytes
     value = layer_bytes * args.steps / (ms * 1e-3) / 1e9     # the whole layer's weights, all ranks together
     peak, peak_kind = measured_peaks()
     achieved = (layer_bytes / world + io_bytes) * args.steps / (ms * 1e-3) / 1e9      # per GPU
@@ -790,17 +896,18 @@ def run_b200(args) -> None:
                        "l2": f"steps cycle a ring of {ring} distinct layers ({ring * layer_bytes / world / 1e6:.0f} MB of weights "
                              "a GPU, larger than the 126 MB L2), so no flush is needed",
                        "launch": "CUDA graph of the timed steps" + (", programmatic dependent launch" if pdl else "")
-                                 + ("; q/k/v side by side, then o, then gate/up side by side, then down (graph branches)"
-                                    if branches else ""),
+                                 + "; four persistent launches a layer, in dataflow order: q/k/v, o, gate/up, down",
                        "parallelism": "single GPU" if world == 1 else
-                       f"tp{world}: q/k/v/gate/up column-parallel, o/down row-parallel with a rank-ordered bf16 reduction",
+                       f"tp{world}: q/k/v/gate/up column-parallel, o/down row-parallel (fp32 partials, rank-ordered sum, one rounding)",
                        "k_slices": splits, "lanes": args.lanes},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "traffic": TRAFFIC_RATIO * (layer_bytes / world + io_bytes) / len(shapes),
-                         "kernel": "qmm_tiled_kernel<4,64,%d,*>" % (1 if rows <= 8 else 2 if rows <= 16 else 4 if rows <= 32 else 8),
-                         "bytes_per_launch": (layer_bytes / world + io_bytes) / len(shapes),
-                         "us_per_launch": ms * 1e3 / (args.steps * len(shapes)), "per": "GPU"},
+                         "peak_kind": peak_kind, "traffic": TRAFFIC_RATIO * (layer_bytes / world + io_bytes) / per_step,
+                         "kernel": "qmm_stream_kernel<4,64,%d,*>" % (1 if rows <= 8 else 2),
+                         "bytes_per_launch": (layer_bytes / world + io_bytes) / per_step,
+                         "us_per_launch": ms * 1e3 / (args.steps * per_step), "launches_per_step": per_step,
+                         "note": "the launches of a step run one after another on one stream, so the step time over "
+                                 "their count is the kernel's average duration", "per": "GPU"},
             "median_of_9": {"ms_per_step": med / args.steps, "value": layer_bytes * args.steps / (med * 1e-3) / 1e9},
             "e2e": {"value": layer_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": sum(2 * rows * kin[name] for name, _ in shapes),
@@ -869,20 +976,13 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--case", default="", help="profiler case: run six launches of one projection (e.g. gate_proj) and exit")
     ap.add_argument("--prefill", action="store_true", help="with --case: the prefill arithmetic (tcgen05 kernel)")
-    ap.add_argument("--no-branches", action="store_true", help="launch the seven projections one after another")
-    ap.add_argument("--no-chain-pdl", action="store_true", help="with branches: programmatic launch for q_proj only")
-    ap.add_argument("--pair-share", type=int, default=2, help="tuning: share of the machine gate/up aim for when forked")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE layer / row-count sweeps reported beside the headline")
     ap.add_argument("--extras", default="all", help="which side figures to run: all, or a comma list of moe_layer, "
-                    "dense_rows, stacked_layer, glue, load_path, moe_block")
-    ap.add_argument("--lanes", type=int, default=0, help="tuning: K slices a thread block streams (0 = default)")
+                    "dense_rows, cfg0, cfg3, lm_head, glue, load_path, moe_block")
+    ap.add_argument("--lanes", type=int, default=0, help="tuning: super-blocks a thread block streams side by side (0 = default)")
     ap.add_argument("--sk-target", type=int, default=0, help="tuning: occupancy target of the K split (0 = default)")
     args = ap.parse_args()
-    if os.environ.get("TF_BENCH_WATCHDOG"):                  # debugging aid: dump every thread's stack and exit if stuck
-        import faulthandler
-
-        faulthandler.dump_traceback_later(int(os.environ["TF_BENCH_WATCHDOG"]), exit=True)
     if args.case:
         run_case(args)
     elif args.impl == "reference":

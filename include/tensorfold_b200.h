@@ -86,7 +86,7 @@ int tf_group_sums(const void* x, int64_t ldx, int m, int k, int gs, float* xs, v
  *   sk       K slices (>= 1, divides k / gs); sums are added in slice order
  *   out      [m, n] bf16 (out_f32 = 0) or fp32, row stride ldo elements; ignored when reduce = 0 and sk > 1
  *   part     [sk, m, n] fp32, required when reduce = 0 with sk > 1, or when sk > 8 (up to 8 slices are summed on
- *            chip; more pass through part), else may be NULL
+ *            chip; more pass through part and a second kernel), else may be NULL
  *   reduce   1: out receives the sum of the slices; 0: the slices stay in part (out untouched)
  *   pdl      1: launch with programmatic stream serialisation, so this call's weight prefetch overlaps the tail of the
  *            previous kernel in the stream (it still waits for that kernel before reading x or writing out)
@@ -96,31 +96,25 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
            int bits, int gs, int sk, void* out, int64_t ldo, int out_f32, float* part, int reduce, int pdl,
            void* stream);
 
-/* The decode / verify matmul on the 5th-generation tensor cores, over a SET of up to 4 projections that read the same
- * rows of x (q/k/v, gate/up, or one projection alone): one persistent launch per 16 rows streams all of them (wider
- * windows run as 16-row launches, so a row's bits never depend on m).  Per K slice and group in order: P' = the group's
- * sum of x * (q + 128) from tcgen05.mma chained over 16-input steps, acc = fma(xs, b - 128 s, fma(P', s, acc)); slices
- * added in slice order, one rounding.  These are not tf_qmm's bits (that kernel chains mma.sync instructions): a
- * model keeps one of the two entry points for a weight.  Widths 2, 3, 4, 5 and 6 (8-bit codes: TF_ERR_UNSUPPORTED, use
- * tf_qmm).  Host arrays of nproj entries: tiled, sb_stride (entries 0 or the array NULL: dense), n, sk, out, ldo.
- *   out_f32    applies to every projection
- *   slices_out 1: out[i] receives the slices as fp32 [sk[i], m, n[i]] (contiguous, ldo unused) and nothing is summed
- *   scratch    device memory of tf_qmm_set_scratch_bytes(nproj, n, sk) bytes, 256-byte aligned: the K slices meet
- *              there (it stays in L2).  Its first 64 KB are counters that must be ZERO before the first call; every call
- *              leaves them zero (unless tf_device_error reports a lost wait: clear the scratch then).  Calls that share
- *              scratch must not overlap on the GPU: one scratch area per stream that runs sets side by side.
- * Replaces the pybind function qmm(x, xs, w, scales, biases, out, part, n, sk, gs, bm, f32, reduce) of
- * cuda/kernels/qmm.cpp:14-44 for decode windows, and a run of such calls that the family engines issue for projections
- * of one input (families/qwen3_5/cuda/qmm_fast.py:49-64). */
+/* tf_qmm for decode and verify windows (1 to 16 rows) over a SET of up to 4 projections that read the same rows of x
+ * (q/k/v, gate/up, or one projection alone): one persistent launch streams all of them, and every output row has the
+ * bits tf_qmm gives for the same projection and slice count.  Host arrays of nproj entries: tiled, sb_stride (entries
+ * 0 or the array NULL: dense), n, sk, out, ldo.  out_f32 applies to every projection.
+ *   scratch  device memory of tf_qmm_set_scratch_bytes(nproj, n, sk) bytes, 256-byte aligned: the K slices meet
+ *            there (it stays in L2).  Its first 64 KB are counters that must be ZERO before the first call; every call
+ *            leaves them zero (unless tf_device_error reports a lost wait: clear the scratch then).  Calls that share
+ *            scratch must not overlap on the GPU: one scratch area per stream that runs sets side by side.
+ * Replaces a run of the pybind qmm(...) calls of cuda/kernels/qmm.cpp:14-44 that the family engines issue for
+ * projections of one input (families/qwen3_5/cuda/qmm_fast.py:49-64), with the bits of those separate calls. */
 int64_t tf_qmm_set_scratch_bytes(int nproj, const int* n, const int* sk);
-/* The launch geometry tf_qmm_set picks for such a set on the current device (host function; any pointer may be NULL):
- * super-blocks a thread block streams side by side, blocks an SM holds, blocks of the persistent grid.  Geometry never
- * changes a result bit.  No counterpart in the reference. */
-int tf_qmm_set_geometry(int bits, int gs, int nproj, const int* n, const int* sk, int* lanes, int* blocks_per_sm, int* grid);
+/* The launch geometry tf_qmm_set picks for such a set of m rows on the current device (host function; any pointer may be
+ * NULL): super-blocks a thread block streams side by side, blocks an SM holds, blocks of the persistent grid.  Geometry
+ * never changes a result bit.  No counterpart in the reference. */
+int tf_qmm_set_geometry(int m, int bits, int gs, int nproj, const int* n, const int* sk, int* lanes, int* blocks_per_sm,
+                        int* grid);
 int tf_qmm_set(const void* x, int64_t ldx, int m, const float* xs, int k, int bits, int gs, int nproj,
                const void* const* tiled, const int64_t* sb_stride, const int* n, const int* sk, void* const* out,
-               const int64_t* ldo, int out_f32, int slices_out, void* scratch, int64_t scratch_bytes, int pdl,
-               void* stream);
+               const int64_t* ldo, int out_f32, void* scratch, int64_t scratch_bytes, int pdl, void* stream);
 
 /* Dense projection with an activation epilogue (one K slice): epi 1 = bf16(relu(bf16 v)^2); epi 2 = SwiGLU over a
  * tf_pack_pair weight, bf16(bf16(silu(bf16 gate)) * bf16 up) with both clipped first when limit > 0 (out then has n / 2

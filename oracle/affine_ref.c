@@ -107,3 +107,8 @@ int oracle_threads(void) {
 #endif
   return t;
 }
+
+/* Threads the parallel loops use from now on (a launcher may have exported OMP_NUM_THREADS=1 for its workers). */
+void oracle_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+}

@@ -43,6 +43,8 @@ def port():
     lib.oracle_qmm_f64.argtypes = (vp, i64, vp, vp, vp, i64, i64, i32, i32, vp)
     lib.oracle_qmm_f32.argtypes = (vp, i64, vp, vp, vp, i64, i64, i32, i32, vp)
     lib.oracle_threads.restype = i32
+    lib.oracle_set_threads.argtypes = (i32,)
+    lib.oracle_set_threads.restype = None
     return lib
 
 
@@ -74,3 +76,9 @@ def qmm_f32(x_bits, words, s_bits, b_bits, gs: int, bits: int) -> np.ndarray:
 
 def threads() -> int:
     return int(port().oracle_threads())
+
+
+def set_threads(n: int) -> None:
+    """Use ``n`` OpenMP threads from now on, whatever OMP_NUM_THREADS said when the process started."""
+
+    port().oracle_set_threads(int(n))

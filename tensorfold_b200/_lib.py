@@ -30,9 +30,9 @@ SIGNATURES = {
     "tf_qmm": (_i32, (_vp, _i64, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i32, _vp, _i32, _i32,
                       _vp)),
     "tf_qmm_set_scratch_bytes": (_i64, (_i32, _vp, _vp)),
-    "tf_qmm_set_geometry": (_i32, (_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp)),
-    "tf_qmm_set": (_i32, (_vp, _i64, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _i64,
-                          _i32, _vp)),
+    "tf_qmm_set_geometry": (_i32, (_i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp)),
+    "tf_qmm_set": (_i32, (_vp, _i64, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _i32,
+                          _vp)),
     "tf_pack_pair": (_i32, (_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp)),
     "tf_qmm_act": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _i64, _i32, ctypes.c_float, _i32, _vp)),
     "tf_moe_plan_blocks": (_i32, (_i32,)),

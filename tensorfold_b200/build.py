@@ -25,7 +25,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 def _units() -> list[tuple[Path, Path, list[str]]]:
     units = [(CSRC / "qmm_inst.cu", OBJ / f"qmm_b{b}.o", [f"-DTF_BITS={b}"]) for b in BITS]
-    units += [(CSRC / "qmm_stream_inst.cu", OBJ / f"qmm_stream_b{b}.o", [f"-DTF_BITS={b}"]) for b in BITS if b != 8]
+    units += [(CSRC / "qmm_stream_inst.cu", OBJ / f"qmm_stream_b{b}.o", [f"-DTF_BITS={b}"]) for b in BITS]
     for src in sorted(CSRC.glob("*.cu")):
         if src.name not in ("qmm_inst.cu", "qmm_stream_inst.cu"):
             units.append((src, OBJ / (src.stem + ".o"), []))

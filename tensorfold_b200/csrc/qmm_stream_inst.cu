@@ -1,91 +1,86 @@
-// Instantiates qmm_stream_kernel for one bit width (TF_BITS) over every group size and lane count (1, 2 or 4
-// super-blocks a block) that fits an SM's shared and tensor memory.
+// Instantiates qmm_stream_kernel for one bit width (TF_BITS) over every group size, row tile (8 or 16 rows) and lane
+// count (1, 2 or 4 super-blocks a block).
 #include "qmm_stream_launch.h"
 
 #ifndef TF_BITS
-#error "compile with -DTF_BITS=<2|3|4|5|6>"
+#error "compile with -DTF_BITS=<2|3|4|5|6|8>"
 #endif
 
 namespace tf {
 
 namespace {
 
-template <int GS, int KW>
+template <int GS, int MT, int KW>
 cudaError_t launch(const CUtensorMap& tmx, const StreamParams& p, int grid, cudaStream_t stream, bool pdl) {
-  using Geo = StreamGeo<TF_BITS, GS, KW>;
-  if constexpr (!Geo::FITS) {
-    return cudaErrorInvalidConfiguration;
-  } else {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(Geo::THREADS);
-    cfg.dynamicSmemBytes = Geo::SMEM;
-    cfg.stream = stream;
-    cudaLaunchAttribute attrs[1];
-    int na = 0;
-    if (pdl) {
-      attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attrs[na].val.programmaticStreamSerializationAllowed = 1;
-      ++na;
-    }
-    cfg.attrs = attrs;
-    cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, qmm_stream_kernel<TF_BITS, GS, KW>, tmx, p);
+  using Geo = StreamGeo<TF_BITS, GS, MT, KW>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(Geo::THREADS);
+  cfg.dynamicSmemBytes = Geo::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  int na = 0;
+  if (pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
   }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, qmm_stream_kernel<TF_BITS, GS, MT, KW>, tmx, p);
 }
 
-template <int GS, int KW>
+template <int GS, int MT, int KW>
 cudaError_t configure() {
-  using Geo = StreamGeo<TF_BITS, GS, KW>;
-  if constexpr (!Geo::FITS) {
-    return cudaSuccess;
-  } else {
-    return cudaFuncSetAttribute(qmm_stream_kernel<TF_BITS, GS, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo::SMEM);
-  }
+  return cudaFuncSetAttribute(qmm_stream_kernel<TF_BITS, GS, MT, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              StreamGeo<TF_BITS, GS, MT, KW>::SMEM);
 }
 
-// Blocks of that shape an SM holds: the design figure.  The launch bounds guarantee the registers and the static
-// assertion the shared memory for that many; the runtime's occupancy query answers 1 for any kernel that allocates
-// tensor memory, whatever it allocates, so it only serves to tell whether the kernel can be launched at all.
-template <int GS, int KW>
+template <int GS, int MT, int KW>
 int resident() {
-  using Geo = StreamGeo<TF_BITS, GS, KW>;
-  if constexpr (!Geo::FITS) {
+  using Geo = StreamGeo<TF_BITS, GS, MT, KW>;
+  int blocks = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, qmm_stream_kernel<TF_BITS, GS, MT, KW>, Geo::THREADS, Geo::SMEM) !=
+      cudaSuccess)
     return 0;
-  } else {
-    static_assert(Geo::BLOCKS * (Geo::SMEM + 1024) <= 228 * 1024, "the resident blocks fit the shared memory of an SM");
-    int blocks = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, qmm_stream_kernel<TF_BITS, GS, KW>, Geo::THREADS, Geo::SMEM) != cudaSuccess)
-      return 0;
-    return blocks < 1 ? 0 : Geo::BLOCKS;
+  return blocks;
+}
+
+#define TF_STREAM_CASES(CALL)          \
+  switch (mt * 10 + kw) {              \
+    case 11: return CALL(GS, 1, 1);    \
+    case 12: return CALL(GS, 1, 2);    \
+    case 14: return CALL(GS, 1, 4);    \
+    case 21: return CALL(GS, 2, 1);    \
+    case 22: return CALL(GS, 2, 2);    \
+    case 24: return CALL(GS, 2, 4);    \
+    default: break;                    \
   }
+
+template <int GS>
+cudaError_t launch_gs(const CUtensorMap& tmx, const StreamParams& p, int mt, int kw, int grid, cudaStream_t stream, bool pdl) {
+#define TF_CALL(G_, M_, K_) launch<G_, M_, K_>(tmx, p, grid, stream, pdl)
+  TF_STREAM_CASES(TF_CALL)
+#undef TF_CALL
+  return cudaErrorInvalidValue;
 }
 
 template <int GS>
-cudaError_t launch_gs(const CUtensorMap& tmx, const StreamParams& p, int kw, int grid, cudaStream_t stream, bool pdl) {
-  switch (kw) {
-    case 1: return launch<GS, 1>(tmx, p, grid, stream, pdl);
-    case 2: return launch<GS, 2>(tmx, p, grid, stream, pdl);
-    case 4: return launch<GS, 4>(tmx, p, grid, stream, pdl);
-    default: return cudaErrorInvalidValue;
-  }
-}
-
-template <int GS>
-int resident_gs(int kw) {
-  switch (kw) {
-    case 1: return resident<GS, 1>();
-    case 2: return resident<GS, 2>();
-    case 4: return resident<GS, 4>();
-    default: return 0;
-  }
+int resident_gs(int mt, int kw) {
+#define TF_CALL(G_, M_, K_) resident<G_, M_, K_>()
+  TF_STREAM_CASES(TF_CALL)
+#undef TF_CALL
+  return 0;
 }
 
 template <int GS>
 cudaError_t configure_gs() {
-  cudaError_t e = configure<GS, 1>();
-  if (e == cudaSuccess) e = configure<GS, 2>();
-  if (e == cudaSuccess) e = configure<GS, 4>();
+  cudaError_t e = configure<GS, 1, 1>();
+  if (e == cudaSuccess) e = configure<GS, 1, 2>();
+  if (e == cudaSuccess) e = configure<GS, 1, 4>();
+  if (e == cudaSuccess) e = configure<GS, 2, 1>();
+  if (e == cudaSuccess) e = configure<GS, 2, 2>();
+  if (e == cudaSuccess) e = configure<GS, 2, 4>();
   return e;
 }
 
@@ -94,21 +89,21 @@ cudaError_t configure_gs() {
 #define TF_CAT2(a, b) a##b
 #define TF_CAT(a, b) TF_CAT2(a, b)
 
-cudaError_t TF_CAT(qmm_stream_launch_b, TF_BITS)(const CUtensorMap& tmx, const StreamParams& p, int gs, int kw, int grid,
+cudaError_t TF_CAT(qmm_stream_launch_b, TF_BITS)(const CUtensorMap& tmx, const StreamParams& p, int gs, int mt, int kw, int grid,
                                                  cudaStream_t stream, bool pdl) {
   switch (gs) {
-    case 32: return launch_gs<32>(tmx, p, kw, grid, stream, pdl);
-    case 64: return launch_gs<64>(tmx, p, kw, grid, stream, pdl);
-    case 128: return launch_gs<128>(tmx, p, kw, grid, stream, pdl);
+    case 32: return launch_gs<32>(tmx, p, mt, kw, grid, stream, pdl);
+    case 64: return launch_gs<64>(tmx, p, mt, kw, grid, stream, pdl);
+    case 128: return launch_gs<128>(tmx, p, mt, kw, grid, stream, pdl);
     default: return cudaErrorInvalidValue;
   }
 }
 
-int TF_CAT(qmm_stream_resident_b, TF_BITS)(int gs, int kw) {
+int TF_CAT(qmm_stream_resident_b, TF_BITS)(int gs, int mt, int kw) {
   switch (gs) {
-    case 32: return resident_gs<32>(kw);
-    case 64: return resident_gs<64>(kw);
-    case 128: return resident_gs<128>(kw);
+    case 32: return resident_gs<32>(mt, kw);
+    case 64: return resident_gs<64>(mt, kw);
+    case 128: return resident_gs<128>(mt, kw);
     default: return 0;
   }
 }

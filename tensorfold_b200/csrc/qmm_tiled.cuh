@@ -198,8 +198,9 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
   const int sb0 = blockIdx.x * KW;                          // lane kw streams super-block sb0 + kw (if it exists)
   const int lanes_here = min(KW, nsb - sb0);
   const int slice = blockIdx.z;
-  const int per = p.KG / p.sk;                              // groups of a slice
-  const int g_first = slice * per;
+  // slice s covers groups [s KG / sk, (s + 1) KG / sk): a function of the shape only; sizes differ by at most one group
+  const int g_first = static_cast<int>(static_cast<int64_t>(slice) * p.KG / p.sk);
+  const int per = static_cast<int>(static_cast<int64_t>(slice + 1) * p.KG / p.sk) - g_first;
   const int nstages = (per + G - 1) / G;
   const bool grouped = p.items != nullptr;
   int m0 = blockIdx.y * ROWS, rows_here, first = 0;

@@ -40,7 +40,7 @@ struct DeviceState {
   bool ready = false;
   int* err = nullptr;
   int sms = 0;
-  signed char resident[6][3][3] = {};      // blocks of a streaming kernel an SM holds: [bits][group][lanes] (0: none)
+  signed char resident[6][3][2][3] = {};   // blocks of a streaming kernel an SM holds: [bits][group][row tile][lanes]
 };
 DeviceState g_devices[MAX_DEVICES];
 int g_lanes_pref = 0;                 // tuning knob (tf_tune): preferred slice lanes per block, 0 = default
@@ -180,13 +180,17 @@ __global__ void group_sums_kernel(const __nv_bfloat16* __restrict__ x, int64_t l
   }
 }
 
-__global__ void reduce_slices_kernel(const float* __restrict__ part, int sk, int64_t total, void* out, int out_f32) {
+// out[r, c] = round(part[0][r, c] + part[1][r, c] + ...): slices [sk, total] fp32 with rows of n values, added in slice
+// order; out rows ldo elements apart.
+__global__ void reduce_slices_kernel(const float* __restrict__ part, int sk, int64_t total, int n, int64_t ldo, void* out,
+                                     int out_f32) {
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     float acc = part[i];
     for (int s = 1; s < sk; ++s) acc = acc + part[static_cast<int64_t>(s) * total + i];
-    if (out_f32) reinterpret_cast<float*>(out)[i] = acc;
-    else reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(acc);
+    const int64_t o = ldo == n ? i : (i / n) * ldo + i % n;
+    if (out_f32) reinterpret_cast<float*>(out)[o] = acc;
+    else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -253,26 +257,26 @@ cudaError_t launch_bits(const QmmParams& p, int bits, int gs, int mt, int kw, cu
   }
 }
 
-cudaError_t stream_launch_bits(const CUtensorMap& tmx, const StreamParams& p, int bits, int gs, int kw, int grid, cudaStream_t s,
-                               bool pdl) {
+cudaError_t stream_launch_bits(const CUtensorMap& tmx, const StreamParams& p, int bits, int gs, int mt, int kw, int grid,
+                               cudaStream_t s, bool pdl) {
   switch (bits) {
-    case 2: return qmm_stream_launch_b2(tmx, p, gs, kw, grid, s, pdl);
-    case 3: return qmm_stream_launch_b3(tmx, p, gs, kw, grid, s, pdl);
-    case 4: return qmm_stream_launch_b4(tmx, p, gs, kw, grid, s, pdl);
-    case 5: return qmm_stream_launch_b5(tmx, p, gs, kw, grid, s, pdl);
-    case 6: return qmm_stream_launch_b6(tmx, p, gs, kw, grid, s, pdl);
-    default: return cudaErrorInvalidValue;
+    case 2: return qmm_stream_launch_b2(tmx, p, gs, mt, kw, grid, s, pdl);
+    case 3: return qmm_stream_launch_b3(tmx, p, gs, mt, kw, grid, s, pdl);
+    case 4: return qmm_stream_launch_b4(tmx, p, gs, mt, kw, grid, s, pdl);
+    case 5: return qmm_stream_launch_b5(tmx, p, gs, mt, kw, grid, s, pdl);
+    case 6: return qmm_stream_launch_b6(tmx, p, gs, mt, kw, grid, s, pdl);
+    default: return qmm_stream_launch_b8(tmx, p, gs, mt, kw, grid, s, pdl);
   }
 }
 
-int stream_resident_bits(int bits, int gs, int kw) {
+int stream_resident_bits(int bits, int gs, int mt, int kw) {
   switch (bits) {
-    case 2: return qmm_stream_resident_b2(gs, kw);
-    case 3: return qmm_stream_resident_b3(gs, kw);
-    case 4: return qmm_stream_resident_b4(gs, kw);
-    case 5: return qmm_stream_resident_b5(gs, kw);
-    case 6: return qmm_stream_resident_b6(gs, kw);
-    default: return 0;
+    case 2: return qmm_stream_resident_b2(gs, mt, kw);
+    case 3: return qmm_stream_resident_b3(gs, mt, kw);
+    case 4: return qmm_stream_resident_b4(gs, mt, kw);
+    case 5: return qmm_stream_resident_b5(gs, mt, kw);
+    case 6: return qmm_stream_resident_b6(gs, mt, kw);
+    default: return qmm_stream_resident_b8(gs, mt, kw);
   }
 }
 
@@ -345,13 +349,16 @@ int tf_init(int device) {
   if (e == cudaSuccess) e = qmm_stream_configure_b4();
   if (e == cudaSuccess) e = qmm_stream_configure_b5();
   if (e == cudaSuccess) e = qmm_stream_configure_b6();
+  if (e == cudaSuccess) e = qmm_stream_configure_b8();
   int sms = 0;
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (e == cudaSuccess) {
     for (int b = 0; b < 6; ++b)
       for (int g = 0; g < 3; ++g)
-        for (int k = 0; k < 3; ++k)
-          g_devices[device].resident[b][g][k] = static_cast<signed char>(stream_resident_bits(BIT_WIDTHS[b], 32 << g, 1 << k));
+        for (int m = 0; m < 2; ++m)
+          for (int k = 0; k < 3; ++k)
+            g_devices[device].resident[b][g][m][k] =
+                static_cast<signed char>(stream_resident_bits(BIT_WIDTHS[b], 32 << g, m + 1, 1 << k));
   }
   int* err = nullptr;
   if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_error_word);
@@ -465,7 +472,7 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
   if (!format_ok(bits, gs)) return fail(TF_ERR_ARG, "tf_qmm: %d bits / groups of %d is not an affine format", bits, gs);
   if (m < 1 || n < 1 || k < gs || k % gs) return fail(TF_ERR_ARG, "tf_qmm: bad shape m=%d n=%d k=%d", m, n, k);
   const int kg = k / gs;
-  if (sk < 1 || kg % sk) return fail(TF_ERR_ARG, "tf_qmm: K must split into whole groups a slice (groups %d, slices %d)", kg, sk);
+  if (sk < 1 || sk > kg) return fail(TF_ERR_ARG, "tf_qmm: 1 to %d K slices (one group at least a slice), not %d", kg, sk);
   if (!x || !tiled) return fail(TF_ERR_ARG, "tf_qmm: null pointer");
   if (reinterpret_cast<uintptr_t>(x) % 16 || (m > 1 && ldx % 8) || ldx < k)
     return fail(TF_ERR_ALIGN, "tf_qmm: x rows must start on 16-byte boundaries (ldx %% 8 == 0, ldx >= k)");
@@ -481,7 +488,6 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
   const bool out_used = !slices_out || reduce;
   if (out_used && (!out || ldo < n)) return fail(TF_ERR_ARG, "tf_qmm: out is null or its rows are shorter than n (ldo >= n)");
   if (sb_stride < 0) return fail(TF_ERR_ARG, "tf_qmm: negative super-block stride");
-  if (slices_out && reduce && ldo != n) return fail(TF_ERR_ARG, "tf_qmm: more than 8 slices need a contiguous out (ldo == n)");
   if (m > 65535 * 8) return fail(TF_ERR_ARG, "tf_qmm: too many rows");
   DeviceState* st = nullptr;
   if (int rc = current_state(&st)) return rc;
@@ -505,7 +511,12 @@ int tf_qmm(const void* x, int64_t ldx, int m, const float* xs, const void* tiled
   p.err = st->err;
   const cudaError_t e = launch_bits(p, bits, gs, mt, kw, static_cast<cudaStream_t>(stream), pdl != 0);
   if (e != cudaSuccess) return cuda_fail(e, "tf_qmm launch");
-  if (slices_out && reduce) return tf_reduce_slices(part, sk, static_cast<int64_t>(m) * n, out, out_f32, stream);
+  if (slices_out && reduce) {                               // more slices than a cluster holds: summed by a second kernel
+    const int64_t total = static_cast<int64_t>(m) * n;
+    reduce_slices_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(part, sk, total, n, ldo, out, out_f32);
+    const cudaError_t e2 = cudaGetLastError();
+    return e2 == cudaSuccess ? TF_OK : cuda_fail(e2, "tf_qmm slice sum");
+  }
   return TF_OK;
 }
 
@@ -520,19 +531,17 @@ int64_t tf_qmm_set_scratch_bytes(int nproj, const int* n, const int* sk) {
   return total;
 }
 
-int tf_qmm_set_geometry(int bits, int gs, int nproj, const int* n, const int* sk, int* lanes, int* blocks_per_sm, int* grid) {
-  if (!format_ok(bits, gs) || bits == 8 || nproj < 1 || nproj > STREAM_MAX_PROJ || !n || !sk)
+int tf_qmm_set_geometry(int m, int bits, int gs, int nproj, const int* n, const int* sk, int* lanes, int* blocks_per_sm,
+                        int* grid) {
+  if (!format_ok(bits, gs) || m < 1 || m > 16 || nproj < 1 || nproj > STREAM_MAX_PROJ || !n || !sk)
     return fail(TF_ERR_ARG, "tf_qmm_set_geometry: bad arguments");
   DeviceState* st = nullptr;
   if (int rc = current_state(&st)) return rc;
+  const int mt = mt_for_rows(m);
   int64_t units = 0;
   for (int i = 0; i < nproj; ++i) units += static_cast<int64_t>((n[i] + SB_COLS - 1) / SB_COLS) * sk[i];
-  int kw = g_stream_lanes > 0 ? g_stream_lanes : (units >= 2 * st->sms ? 2 : 1);
-  int resident = st->resident[bits_index(bits)][gs_index(gs)][kw_index(kw)];
-  while (resident < 1 && kw > 1) {
-    kw /= 2;
-    resident = st->resident[bits_index(bits)][gs_index(gs)][kw_index(kw)];
-  }
+  const int kw = g_stream_lanes > 0 ? g_stream_lanes : (units > 3 * st->sms ? 2 : 1);
+  int resident = st->resident[bits_index(bits)][gs_index(gs)][mt - 1][kw_index(kw)];
   if (resident < 1) return fail(TF_ERR_STATE, "tf_qmm_set_geometry: the streaming kernel does not fit an SM of this device");
   if (g_stream_blocks > 0 && g_stream_blocks < resident) resident = g_stream_blocks;
   int64_t items = 0;
@@ -545,25 +554,23 @@ int tf_qmm_set_geometry(int bits, int gs, int nproj, const int* n, const int* sk
 
 int tf_qmm_set(const void* x, int64_t ldx, int m, const float* xs, int k, int bits, int gs, int nproj,
                const void* const* tiled, const int64_t* sb_stride, const int* n, const int* sk, void* const* out,
-               const int64_t* ldo, int out_f32, int slices_out, void* scratch, int64_t scratch_bytes, int pdl, void* stream) {
+               const int64_t* ldo, int out_f32, void* scratch, int64_t scratch_bytes, int pdl, void* stream) {
   if (!format_ok(bits, gs)) return fail(TF_ERR_ARG, "tf_qmm_set: %d bits / groups of %d is not an affine format", bits, gs);
-  if (bits == 8) return fail(TF_ERR_UNSUPPORTED, "tf_qmm_set: 8-bit codes run through tf_qmm");
   if (nproj < 1 || nproj > STREAM_MAX_PROJ) return fail(TF_ERR_ARG, "tf_qmm_set: 1 to %d projections a set, not %d", STREAM_MAX_PROJ, nproj);
-  if (m < 1) return fail(TF_ERR_ARG, "tf_qmm_set: at least one row");
+  if (m < 1 || m > 16) return fail(TF_ERR_ARG, "tf_qmm_set: 1 to 16 rows, not %d (larger windows go through tf_qmm)", m);
   if (k < gs || k % gs) return fail(TF_ERR_ARG, "tf_qmm_set: K = %d must be a positive multiple of the group", k);
-  if (!x || !tiled || !n || !sk || !out || (!slices_out && !ldo)) return fail(TF_ERR_ARG, "tf_qmm_set: null pointer");
+  if (!x || !tiled || !n || !sk || !out || !ldo) return fail(TF_ERR_ARG, "tf_qmm_set: null pointer");
   if (reinterpret_cast<uintptr_t>(x) % 16 || (m > 1 && ldx % 8) || ldx < k)
     return fail(TF_ERR_ALIGN, "tf_qmm_set: x rows must start on 16-byte boundaries (ldx %% 8 == 0, ldx >= k)");
   const int kg = k / gs;
   int64_t need = set_counter_bytes(nproj, n);
   if (need < 0) return fail(TF_ERR_ARG, "tf_qmm_set: a set holds at most 4096 super-blocks of 128 columns");
   for (int i = 0; i < nproj; ++i) {
-    if (n[i] < 1 || sk[i] < 1 || kg % sk[i])
+    if (n[i] < 1 || sk[i] < 1 || sk[i] > kg)
       return fail(TF_ERR_ARG, "tf_qmm_set: projection %d: n = %d, %d slices over %d groups", i, n[i], sk[i], kg);
-    if (!tiled[i] || !out[i] || (!slices_out && ldo[i] < n[i]))
-      return fail(TF_ERR_ARG, "tf_qmm_set: projection %d: null pointer or short out rows", i);
+    if (!tiled[i] || !out[i] || ldo[i] < n[i]) return fail(TF_ERR_ARG, "tf_qmm_set: projection %d: null pointer or short out rows", i);
     if (reinterpret_cast<uintptr_t>(tiled[i]) % 16) return fail(TF_ERR_ALIGN, "tf_qmm_set: tiled weights must be 16-byte aligned");
-    if (!slices_out) need += set_part_bytes(n[i], sk[i]);
+    need += set_part_bytes(n[i], sk[i]);
   }
   if (!scratch || reinterpret_cast<uintptr_t>(scratch) % 256 || scratch_bytes < need)
     return fail(TF_ERR_ARG, "tf_qmm_set: scratch must be 256-byte aligned and hold tf_qmm_set_scratch_bytes = %lld bytes",
@@ -571,16 +578,12 @@ int tf_qmm_set(const void* x, int64_t ldx, int m, const float* xs, int k, int bi
   DeviceState* st = nullptr;
   if (int rc = current_state(&st)) return rc;
 
-  const int unitw = unit_words(bits, gs);
-  // super-blocks a block streams side by side: two (two blocks an SM) unless that leaves SMs without work
+  const int mt = mt_for_rows(m), unitw = unit_words(bits, gs);
+  // super-blocks a block streams side by side: one while single-lane blocks (three an SM) hold the set in one wave, else two
   int64_t units = 0;
   for (int i = 0; i < nproj; ++i) units += static_cast<int64_t>((n[i] + SB_COLS - 1) / SB_COLS) * sk[i];
-  int kw = g_stream_lanes > 0 ? g_stream_lanes : (units >= 2 * st->sms ? 2 : 1);
-  int resident = st->resident[bits_index(bits)][gs_index(gs)][kw_index(kw)];
-  while (resident < 1 && kw > 1) {                          // wide groups leave no room for four lanes: fewer
-    kw /= 2;
-    resident = st->resident[bits_index(bits)][gs_index(gs)][kw_index(kw)];
-  }
+  int kw = g_stream_lanes > 0 ? g_stream_lanes : (units > 3 * st->sms ? 2 : 1);
+  int resident = st->resident[bits_index(bits)][gs_index(gs)][mt - 1][kw_index(kw)];
   if (resident < 1) return fail(TF_ERR_STATE, "tf_qmm_set: the streaming kernel does not fit an SM of this device");
   if (g_stream_blocks > 0 && g_stream_blocks < resident) resident = g_stream_blocks;
 
@@ -591,10 +594,10 @@ int tf_qmm_set(const void* x, int64_t ldx, int m, const float* xs, int k, int bi
     for (int j = i; j > 0 && sk[order[j]] < sk[order[j - 1]]; --j) std::swap(order[j], order[j - 1]);
 
   StreamParams p = {};
-  p.K = k, p.KG = kg;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.xs = xs;
+  p.M = m, p.K = k, p.KG = kg;
   p.nproj = nproj;
-  p.slices_out = slices_out ? 1 : 0;
-  p.rows_total = m;
   p.err = st->err;
   int* counters = static_cast<int*>(scratch);
   uint8_t* parts = static_cast<uint8_t*>(scratch) + set_counter_bytes(nproj, n);
@@ -605,31 +608,23 @@ int tf_qmm_set(const void* x, int64_t ldx, int m, const float* xs, int k, int bi
     pr.w = static_cast<const uint32_t*>(tiled[i]);
     pr.sb_stride = sb_stride && sb_stride[i] > 0 ? sb_stride[i] : static_cast<int64_t>(kg) * unitw;
     pr.out = out[i];
-    pr.ldo = slices_out ? n[i] : ldo[i];
+    pr.ldo = ldo[i];
     pr.N = n[i], pr.sk = sk[i];
     pr.nsb = (n[i] + SB_COLS - 1) / SB_COLS;
     pr.out_f32 = out_f32;
     pr.count = counters;
     counters += pr.nsb * 4;
     pr.part = reinterpret_cast<float*>(parts);
-    if (!slices_out) parts += set_part_bytes(n[i], sk[i]);
+    parts += set_part_bytes(n[i], sk[i]);
     pr.item0 = items;
     items += (pr.nsb + kw - 1) / kw * pr.sk;
   }
   p.items = items;
+  CUtensorMap tmx = {};
+  if (int rc = encode_rows(&tmx, x, m == 1 ? k : ldx, m, k, 8 * mt)) return rc;
   const int grid = std::min(items, st->sms * resident);
-  // a window wider than 16 rows runs as 16-row launches over the same weights: every row keeps its bits
-  for (int row0 = 0; row0 < m; row0 += STREAM_ROWS) {
-    const int rows = std::min(STREAM_ROWS, m - row0);
-    p.x = static_cast<const __nv_bfloat16*>(x) + static_cast<int64_t>(row0) * ldx;
-    p.xs = xs ? xs + static_cast<int64_t>(row0) * kg : nullptr;
-    p.M = rows, p.row0 = row0;
-    CUtensorMap tmx = {};
-    if (int rc = encode_rows(&tmx, p.x, rows == 1 ? k : ldx, rows, k, STREAM_ROWS)) return rc;
-    const cudaError_t e = stream_launch_bits(tmx, p, bits, gs, kw, grid, static_cast<cudaStream_t>(stream), pdl != 0 || row0 > 0);
-    if (e != cudaSuccess) return cuda_fail(e, "tf_qmm_set launch");
-  }
-  return TF_OK;
+  const cudaError_t e = stream_launch_bits(tmx, p, bits, gs, mt, kw, grid, static_cast<cudaStream_t>(stream), pdl != 0);
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_qmm_set launch");
 }
 
 int tf_qmm_act(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_stride, int n, int k, int bits, int gs,
@@ -714,7 +709,7 @@ int tf_sum_ranks(const void* parts, int world, int64_t total, int parts_bf16, vo
 
 int tf_reduce_slices(const float* part, int sk, int64_t total, void* out, int out_f32, void* stream) {
   if (!part || !out || sk < 1 || total < 1) return fail(TF_ERR_ARG, "tf_reduce_slices: bad arguments");
-  reduce_slices_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(part, sk, total, out, out_f32);
+  reduce_slices_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(part, sk, total, 1, 1, out, out_f32);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_reduce_slices");
 }

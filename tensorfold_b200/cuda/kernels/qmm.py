@@ -84,15 +84,29 @@ def split_k(n: int, k: int, gs: int = 64, target: int = 192) -> int:
     return sk
 
 
-LANE_TARGET = 600      # 64-column tiles x slices this build aims for (measured on B200: about four blocks per SM)
+LANES = 592            # 128-column lanes the persistent decode kernel streams side by side on a B200: 148 SMs x 4
+MIN_GROUPS = 6         # groups a K slice should hold at least (three pipeline stages of 128 inputs at groups of 64)
 
 
-def default_split(n: int, k: int, gs: int = 64, share: int = 1) -> int:
-    """The K slices ``matmul`` uses when it is given none: ``split_k`` with this build's occupancy target.  ``share`` > 1
-    is for a launch that runs side by side with ``share - 1`` others of its size (``fork_join`` of gate and up): each
-    aims for its share of the machine, which means fewer, longer slices."""
+def default_split(n: int, k: int, gs: int = 64, share: float = 1.0) -> int:
+    """The K slices ``matmul`` uses when it is given none: a function of the shape only (never of the row count), chosen
+    so that the projection's (128-column block, slice) units fill the machine's lanes once: LANES / blocks, at least
+    MIN_GROUPS groups a slice.  Slices need not divide the groups evenly (slice s covers groups
+    [s G / sk, (s + 1) G / sk)).  ``share`` is for projections an engine always launches as a set (q/k/v, gate/up):
+    the set's 128-column blocks over this projection's, so that the SET fills the lanes once (2 for gate or up)."""
 
-    return split_k(n, k, gs, max(1, LANE_TARGET // max(1, share)))
+    blocks, groups = -(-n // 128), k // gs
+    sk = int(LANES // max(1.0, blocks * share))
+    return max(1, min(sk, groups // MIN_GROUPS if groups >= MIN_GROUPS else 1))
+
+
+def set_splits(shapes, gs: int = 64) -> list[int]:
+    """K slices for projections an engine always launches together (``matmul_set``): [(n, k), ...] -> one slice count
+    each, so that the set's units fill the lanes once.  A load-time decision, like stacking: a projection's bits depend
+    on its slice count, so it must use the same count wherever it runs."""
+
+    blocks = [-(-n // 128) for n, _ in shapes]
+    return [default_split(n, k, gs, share=sum(blocks) / b) for (n, k), b in zip(shapes, blocks)]
 
 
 def bucket(m: int) -> int:
@@ -144,28 +158,23 @@ def matmul(x: torch.Tensor, q: Q4, xs: torch.Tensor | None = None, *, sk: int | 
     if xs is not None and (xs.dtype != torch.float32 or xs.shape != (m, kg) or not xs.is_contiguous()):
         raise ValueError(f"matmul: xs must be contiguous ({m}, {kg}) fp32")
     sk = sk or default_split(q.n, q.k, q.gs)
-    if sk < 1 or kg % sk:
-        raise ValueError("matmul: K must split into whole groups a slice")
+    if sk < 1 or sk > kg:
+        raise ValueError("matmul: 1 to K / gs slices (a slice holds one group at least)")
     slices = sk > 1 and not reduce
     if out is None:
         if not slices:
             out = torch.empty((m, q.n), dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
     elif out.shape != (m, q.n) or out.dtype != (torch.float32 if f32 else torch.bfloat16) or out.stride(1) != 1:
         raise ValueError("matmul: out must be (M, n) of the requested dtype with unit-stride rows")
-    streamed = STREAM and q.bits != 8      # the tcgen05 kernel: every width but 8-bit, every row count
-    if sk > 1 and (not reduce or (sk > 8 and not streamed)):
+    if sk > 1 and (not reduce or sk > 8):
         if part is None:
             part = torch.empty((sk, m, q.n), dtype=torch.float32, device=x.device)
         elif part.dtype != torch.float32 or not part.is_contiguous() or part.numel() < sk * m * q.n:
             raise ValueError("matmul: part must hold (SK, M, n) fp32")
     if q.weight.dim() != 3 or q.weight.stride(2) != 1 or q.weight.stride(1) != q.weight.shape[2]:
         raise ValueError("matmul: the tiled weight may be sliced by super-blocks of 128 columns only")
-    if streamed:
-        if sk > 1 and not reduce:
-            slices = part.reshape(-1)[:sk * m * q.n].view(sk, m, q.n)
-            _launch_set(x, [q], xs, [sk], [slices], True, True, pdl)
-            return slices
-        return matmul_set(x, [q], xs, sks=[sk], f32=f32, outs=[out], pdl=pdl)[0]
+    if STREAM and m <= STREAM_ROWS and part is None and (reduce or sk == 1):
+        return matmul_set(x, [q], xs, sks=[sk], f32=f32, outs=[out], pdl=pdl)[0]     # same bits, persistent launch
     _lib.check(_lib.lib().tf_qmm(
         x.data_ptr(), x.stride(0), m, xs.data_ptr() if xs is not None else None, q.weight.data_ptr(),
         q.weight.stride(0), q.n, q.k, q.bits, q.gs, sk, out.data_ptr() if out is not None else None,
@@ -176,7 +185,8 @@ def matmul(x: torch.Tensor, q: Q4, xs: torch.Tensor | None = None, *, sk: int | 
     return part.reshape(-1)[:sk * m * q.n].view(sk, m, q.n)
 
 
-STREAM = os.environ.get("TENSORFOLD_B200_STREAM", "1") != "0"      # every width but 8-bit runs the tcgen05 kernel
+STREAM = os.environ.get("TENSORFOLD_B200_STREAM", "1") != "0"      # decode windows run the persistent kernel (same bits)
+STREAM_ROWS = 16
 SET_MAX = 4
 SCRATCH_BYTES = 16 << 20          # one scratch area: room for a gate/up set of 17408 rows each in 4 K slices
 SCRATCH_AREAS = 4                 # areas made on a device's first call: the calling stream's and three side streams'
@@ -218,30 +228,11 @@ def reset_scratch() -> None:
     _free_areas.clear()
 
 
-def _launch_set(x, qs, xs, sks, outs, f32: bool, slices: bool, pdl: bool) -> None:
-    count = len(qs)
-    q0 = qs[0]
-    stream = _lib.stream_of(x)
-    ints, longs, ptrs = ctypes.c_int * count, ctypes.c_int64 * count, ctypes.c_void_p * count
-    n_arr, sk_arr = ints(*[q.n for q in qs]), ints(*sks)
-    lib = _lib.lib()
-    need = lib.tf_qmm_set_scratch_bytes(count, n_arr, sk_arr)
-    if need < 0:
-        raise ValueError("matmul_set: bad shapes")
-    scratch = _scratch_for(x.device, stream, need)
-    _lib.check(lib.tf_qmm_set(
-        x.data_ptr(), x.stride(0), x.shape[0], xs.data_ptr() if xs is not None else None, q0.k, q0.bits, q0.gs, count,
-        ptrs(*[q.weight.data_ptr() for q in qs]), longs(*[q.weight.stride(0) for q in qs]), n_arr, sk_arr,
-        ptrs(*[o.data_ptr() for o in outs]), longs(*[o.stride(-2) for o in outs]), int(f32), int(slices),
-        scratch.data_ptr(), scratch.numel(), int(pdl), stream), "matmul_set")
-
-
 def matmul_set(x: torch.Tensor, qs, xs: torch.Tensor | None = None, *, sks=None, f32: bool = False, outs=None,
                pdl: bool = False) -> list:
-    """Several projections of the SAME rows (q/k/v, gate/up) in one persistent launch per 16 rows:
-    [x @ q.T for q in qs], each with the bits ``matmul(x, q, sk=sk)`` gives.  Up to 4 weights of one format and K
-    (not 8-bit).  Not in the reference, whose engines issue these as separate calls
-    (families/qwen3_5/cuda/qmm_fast.py:49-64)."""
+    """Several projections of the SAME rows (q/k/v, gate/up) in one persistent launch: [x @ q.T for q in qs], each with
+    the bits ``matmul(x, q, sk=sk)`` gives.  1 to 16 rows, up to 4 weights of one format and K.  Not in the reference,
+    whose engines issue these as separate calls (families/qwen3_5/cuda/qmm_fast.py:49-64)."""
 
     qs = list(qs)
     if not 1 <= len(qs) <= SET_MAX:
@@ -249,10 +240,11 @@ def matmul_set(x: torch.Tensor, qs, xs: torch.Tensor | None = None, *, sks=None,
     q0 = qs[0]
     if any((q.k, q.gs, q.bits) != (q0.k, q0.gs, q0.bits) for q in qs):
         raise ValueError("matmul_set: the weights of a set share K, group and bit width")
-    if q0.bits == 8:
-        raise ValueError("matmul_set: 8-bit weights run one by one through matmul")
     x = _rows(x, q0.k, "matmul_set")
     m = x.shape[0]
+    if m > STREAM_ROWS:
+        raise ValueError(f"matmul_set: at most {STREAM_ROWS} rows (use matmul for larger windows)")
+    stream = _lib.stream_of(x)
     kg = q0.k // q0.gs
     if xs is not None and (xs.dtype != torch.float32 or xs.shape != (m, kg) or not xs.is_contiguous()):
         raise ValueError(f"matmul_set: xs must be contiguous ({m}, {kg}) fp32")
@@ -262,15 +254,27 @@ def matmul_set(x: torch.Tensor, qs, xs: torch.Tensor | None = None, *, sks=None,
     for i, q in enumerate(qs):
         if q.weight.device != x.device:
             raise ValueError("matmul_set: x and the weights must share a CUDA device")
-        if sks[i] < 1 or kg % sks[i]:
-            raise ValueError("matmul_set: K must split into whole groups a slice")
+        if sks[i] < 1 or sks[i] > kg:
+            raise ValueError("matmul_set: 1 to K / gs slices (a slice holds one group at least)")
         if q.weight.dim() != 3 or q.weight.stride(2) != 1 or q.weight.stride(1) != q.weight.shape[2]:
             raise ValueError("matmul_set: the tiled weight may be sliced by super-blocks of 128 columns only")
         if outs[i] is None:
             outs[i] = torch.empty((m, q.n), dtype=dtype, device=x.device)
         elif outs[i].shape != (m, q.n) or outs[i].dtype != dtype or outs[i].stride(1) != 1:
             raise ValueError("matmul_set: out must be (M, n) of the requested dtype with unit-stride rows")
-    _launch_set(x, qs, xs, sks, outs, f32, False, pdl)
+    count = len(qs)
+    ints, longs, ptrs = ctypes.c_int * count, ctypes.c_int64 * count, ctypes.c_void_p * count
+    n_arr, sk_arr = ints(*[q.n for q in qs]), ints(*sks)
+    lib = _lib.lib()
+    need = lib.tf_qmm_set_scratch_bytes(count, n_arr, sk_arr)
+    if need < 0:
+        raise ValueError("matmul_set: bad shapes")
+    scratch = _scratch_for(x.device, stream, need)
+    _lib.check(lib.tf_qmm_set(
+        x.data_ptr(), x.stride(0), m, xs.data_ptr() if xs is not None else None, q0.k, q0.bits, q0.gs, count,
+        ptrs(*[q.weight.data_ptr() for q in qs]), longs(*[q.weight.stride(0) for q in qs]), n_arr, sk_arr,
+        ptrs(*[o.data_ptr() for o in outs]), longs(*[o.stride(0) for o in outs]), int(f32), scratch.data_ptr(),
+        scratch.numel(), int(pdl), stream), "matmul_set")
     return outs
 
 

@@ -84,14 +84,18 @@ def test_gloo_ranks_agree_bit_for_bit_and_sum_in_rank_order(tmp_path, world):
         assert torch.equal(summed.float(), torch.from_numpy(want))
 
 
-def test_default_split_share_asks_for_fewer_longer_slices():
-    """Launches forked in pairs (gate and up) aim for half the machine each: fewer K slices, never more."""
+def test_default_split_is_shape_only_and_fills_the_lanes_once():
+    """(128-column block, slice) units fill the persistent kernel's 592 lanes once, never with slices shorter than six
+    groups; projections launched as a set (gate and up) split by the set's blocks, so the SET fills the lanes once."""
 
     from tensorfold_b200.cuda.kernels import qmm
 
     assert qmm.default_split(17408, 5120) == 4 and qmm.default_split(17408, 5120, share=2) == 2
-    assert qmm.default_split(6144, 5120) == qmm.default_split(6144, 5120, share=1) == 8
-    for n, k in ((1024, 5120), (5120, 17408), (17408, 5120), (256, 512)):
+    assert qmm.default_split(5120, 17408) == 14 and qmm.default_split(5120, 6144) == 14
+    assert qmm.default_split(248320, 5120) == 1 and qmm.default_split(128, 128) == 1
+    for n, k in ((1024, 5120), (5120, 17408), (17408, 5120), (256, 512), (4096, 4096), (14336, 4096)):
         for share in (1, 2, 3, 4):
-            assert 1 <= qmm.default_split(n, k, share=share) <= qmm.default_split(n, k)
-            assert (k // 64) % qmm.default_split(n, k, share=share) == 0
+            sk = qmm.default_split(n, k, share=share)
+            assert 1 <= sk <= qmm.default_split(n, k)
+            assert sk == 1 or (k // 64) // sk >= 6
+            assert -(-n // 128) * sk * share <= qmm.LANES or sk == 1
