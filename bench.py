@@ -483,13 +483,15 @@ def lm_head_bench(dev) -> dict:
 
 def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict:
     """Tensor-parallel MoE decoder block: hidden 6144, 160 experts top 8 of width 1536 split by expert across the ranks,
-    attention o_proj 8192 -> 6144 row-parallel; both bf16 partials [M, 6144] are reduced in rank order over NVLink."""
+    attention o_proj 8192 -> 6144 row-parallel; both bf16 partials [M, 6144] are reduced in rank order over NVLink, by
+    the one-launch peer-memory reduction (``us``) and by the NCCL collectives plus a sum kernel (``us_collectives``).
+    ``phases_us``: the block's steps timed one by one on rank order (max over ranks each), with the peer reduction."""
 
     import torch
     import torch.distributed as dist
 
     from tensorfold_b200 import synthetic
-    from tensorfold_b200.cuda import experts, tp
+    from tensorfold_b200.cuda import experts, moe, tp
     from tensorfold_b200.cuda.kernels import qmm
 
     d, e, ni, top_k, ko = 6144, 160, 1536, 8, 8192
@@ -506,33 +508,83 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
     layer = tp.ExpertParallelMoE(wr, ex, top_k, rank * local_e, e)
     wo = synthetic.affine_weight(d, ko // world, BITS, GS, seed=30 + rank)
     o_proj = qmm.pack(*todev(wo), GS)
+    red = tp.PeerReducer(max(rows_list) * d, device=dev) if world > 1 else None
+
+    def biggest(us: float) -> float:
+        t = torch.tensor([us], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, iters=20) -> float:
+        for _ in range(3):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return biggest(a.elapsed_time(b) * 1e3 / iters)
+
     out = {}
     for rows in rows_list:
         prefill = rows > 128
         buf = layer.buffers(rows, dev, prefill=prefill)
         attn = synthetic.activations(rows, ko // world, 50 + rank).to(dev)
+        project = qmm.prefill_matmul if prefill else qmm.matmul
 
-        def block():
-            part = qmm.prefill_matmul(attn, o_proj) if prefill else qmm.matmul(attn, o_proj)
-            h = tp.ordered_all_reduce(part)
-            return layer.run(h, buf)
+        def block(reducer):
+            if reducer is None:
+                return layer.run(tp.ordered_all_reduce(project(attn, o_proj)), buf)
+            part = reducer.partial((rows, d))
+            project(attn, o_proj, out=part)
+            return layer.run(reducer.reduce(part), buf, reducer=reducer)
 
-        for _ in range(3):
-            block()
+        entry = {"us": timed(lambda: block(red)), "timing": "eager launches, CUDA events, max over ranks",
+                 "reduce": "peer memory, one launch" if red is not None else "none (one rank)"}
+        if red is not None:
+            entry["us_collectives"] = timed(lambda: block(None))
+
+        # the same block step by step (an event after every step; the sum exceeds the block by the events' gaps)
+        state = {}
+        part_of = (lambda: red.partial((rows, d))) if red is not None else (lambda: torch.empty((rows, d), dtype=torch.bfloat16, device=dev))
+        reduce_of = (lambda p: red.reduce(p)) if red is not None else (lambda p: p)
+        width = layer.experts.width
+
+        def route():
+            moe.router(state["h"], layer.router[:e], buf.logits[:rows, :e], prefill=prefill)
+            moe.select_local_rows(buf.logits[:rows], buf, top_k, e, layer.first, layer.experts.count)
+            experts.route(buf.pick[:rows], buf.plan)
+
+        steps = [("o_proj", lambda: state.__setitem__("p", project(attn, o_proj, out=part_of()))),
+                 ("reduce_attention", lambda: state.__setitem__("h", reduce_of(state["p"]))),
+                 ("route", route),
+                 ("gate_up", lambda: experts.gate_up(state["h"], layer.experts, buf.plan, buf.act.view(-1, width), rows)),
+                 ("down", lambda: experts.down(buf.act.view(-1, width), layer.experts, buf.plan, buf.y.view(-1, d), rows)),
+                 ("combine", lambda: state.__setitem__("p", moe.combine(buf.y[:rows], buf.wts[:rows], part_of()))),
+                 ("reduce_experts", lambda: reduce_of(state["p"]))]
+        iters = 10
+        marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(steps) + 1)] for _ in range(iters)]
+        for _, fn in steps:
+            fn()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-        iters = 20
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            block()
-        b.record()
+        for it in range(iters):
+            marks[it][0].record()
+            for i, (_, fn) in enumerate(steps):
+                fn()
+                marks[it][i + 1].record()
         torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) * 1e3 / iters], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        out[f"M{rows}"] = {"us": float(t.item()), "timing": "eager launches, CUDA events, max over ranks"}
+        entry["phases_us"] = {name: round(biggest(sum(m[i].elapsed_time(m[i + 1]) for m in marks) * 1e3 / iters), 1)
+                              for i, (name, _) in enumerate(steps)}
+        out[f"M{rows}"] = entry
+    if red is not None:
+        red.close()
     return out
 
 
@@ -708,7 +760,10 @@ def run_b200(args) -> None:
         counts = qmm.set_splits([(nout[n], kin[n]) for n in names], GS)
         splits.update({n: (qmm.split_k(nout[n], kin[n], GS, args.sk_target) if args.sk_target else c) for n, c in zip(names, counts)})
     row_parallel = ("o_proj", "down_proj") if world > 1 else ()
-    partial = {name: torch.empty((rows, nout[name]), dtype=torch.float32, device=dev) for name in row_parallel}
+    peer = args.reduce == "peer"                             # the one-launch reduction over peer memory, or NCCL + a sum kernel
+    reducers = {name: tp.PeerReducer(rows * nout[name], device=dev) for name in row_parallel} if peer else {}
+    partial = {name: (reducers[name].partial((rows, nout[name]), torch.float32) if peer else
+                      torch.empty((rows, nout[name]), dtype=torch.float32, device=dev)) for name in row_parallel}
     reduced = {}
 
     def step(i: int, pdl: bool) -> None:
@@ -720,7 +775,8 @@ def run_b200(args) -> None:
         for names in SETS:
             if names[0] in row_parallel:
                 qmm.matmul(dev_x[names[0]], layer[names[0]], f32=True, out=partial[names[0]], pdl=False, sk=splits[names[0]])
-                reduced[names[0]] = tp.ordered_all_reduce(partial[names[0]])
+                reduced[names[0]] = (reducers[names[0]].reduce(partial[names[0]]) if peer else
+                                     tp.ordered_all_reduce(partial[names[0]]))
             else:
                 qmm.matmul_set(dev_x[names[0]], [layer[n] for n in names], sks=[splits[n] for n in names],
                                outs=[dev_y[n] for n in names], pdl=pdl and world == 1)
@@ -878,8 +934,9 @@ def run_b200(args) -> None:
     if "all" in wanted or "moe_block" in wanted:
         extras["moe_block"] = moe_block_tp_bench(dev, rank, world)      # holds collectives: every rank runs it or none
 
-    per_step = len(SETS)                                     # launches of this library a step (the collectives are NCCL's)
-    launches = args.steps * (per_step + 2 * len(row_parallel))           # + the rank-ordered sum kernels
+    per_step = len(SETS)                                     # matmul launches a step
+    launches = args.steps * (per_step + len(row_parallel))   # + a reduction each (the peer-memory kernel, or the sum kernel
+                                                             #   behind NCCL's collectives)
     io_bytes = sum(2 * rows * (n + k) for _, (n, k) in shapes)
     value = layer_bytes * args.steps / (ms * 1e-3) / 1e9     # the whole layer's weights, all ranks together
     peak, peak_kind = measured_peaks()
@@ -898,7 +955,8 @@ def run_b200(args) -> None:
                        "launch": "CUDA graph of the timed steps" + (", programmatic dependent launch" if pdl else "")
                                  + "; four persistent launches a layer, in dataflow order: q/k/v, o, gate/up, down",
                        "parallelism": "single GPU" if world == 1 else
-                       f"tp{world}: q/k/v/gate/up column-parallel, o/down row-parallel (fp32 partials, rank-ordered sum, one rounding)",
+                       f"tp{world}: q/k/v/gate/up column-parallel, o/down row-parallel (fp32 partials, rank-ordered sum, one rounding; "
+                       + ("one launch a reduction over peer memory)" if peer else "NCCL all-gather and a sum kernel)"),
                        "k_slices": splits, "lanes": args.lanes},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -977,6 +1035,8 @@ def main() -> None:
     ap.add_argument("--case", default="", help="profiler case: run six launches of one projection (e.g. gate_proj) and exit")
     ap.add_argument("--prefill", action="store_true", help="with --case: the prefill arithmetic (tcgen05 kernel)")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--reduce", default="peer", choices=("peer", "collectives"),
+                    help="several ranks: the one-launch reduction over peer memory, or NCCL collectives and a sum kernel")
     ap.add_argument("--no-extras", action="store_true", help="skip the MoE layer / row-count sweeps reported beside the headline")
     ap.add_argument("--extras", default="all", help="which side figures to run: all, or a comma list of moe_layer, "
                     "dense_rows, cfg0, cfg3, lm_head, glue, load_path, moe_block")

@@ -36,9 +36,16 @@ const char* tf_last_error(void);
  * cuda/kernels/qmm.cu:251-255.  Idempotent. */
 int tf_init(int device);
 
-/* Reads and clears the device error word that kernels set when one of their bounded waits gave up (0 = none).
- * Synchronises `stream`.  host: *code. */
+/* Reads and clears the device error word that kernels set when one of their bounded waits gave up (0 = none; 1 a stage
+ * never arrived, 2 a stage was never released, 3 group sums never came, 4 a peer GPU never signalled, 5 a plan item
+ * named an expert outside the table).  Synchronises `stream`.  host: *code. */
 int tf_device_error(int device, void* stream, int* code);
+
+/* Launches a wait that nothing will satisfy, with a limit of `polls` polls (1 to 4096, about a microsecond each): the
+ * kernel gives up, returns, and tf_device_error then reports 1 (a stage never arrived).  This is how a host checks, on a
+ * healthy GPU and without faulting anything, that a lost copy would come back as an error code and leave the context
+ * usable.  No counterpart in the reference, whose kernels wait without a limit. */
+int tf_selftest_lost_wait(int polls, void* stream);
 
 /* Performance knobs that never change a result bit.  key "qmm_lanes": 128-column super-blocks a thread block streams side
  * by side (1, 2 or 4; 0 = default); "stream_lanes": the same for tf_qmm_set's persistent kernel; "stream_blocks": blocks
@@ -140,8 +147,9 @@ int tf_moe_plan(const int* picks, int pairs, int experts, int tile, int* members
  * entry point calls no cudaMalloc, cudaFree or any allocating library routine.
  *   limits   pairs <= 16384 and ceil(pairs / 1024) * experts <= 65536; anything larger is refused with TF_ERR_ARG and
  *            nothing is launched (use tf_moe_plan with your own scratch)
- *   set-up   the first call on each device looks up the array's device address (that device must be current); make that
- *            first call before starting a stream capture
+ *   set-up   tf_init(device) looks up the array's device address (and thereby loads the array, 320 KB, onto that GPU);
+ *            the call itself is then a plain look-up, so it may also run under stream capture.  Without tf_init for the
+ *            current device it returns TF_ERR_STATE
  *   sharing  all calls on a device use the one array and it keeps the last call's contents; nothing in it has to start
  *            at zero (every counter a call reads is written by that call first).  Two calls that overlap on the GPU
  *            (different streams, or two host threads) race on it: keep calls on a device ordered.
@@ -152,16 +160,19 @@ int tf_moe_plan_static(const int* picks, int pairs, int experts, int tile, int* 
  * (row pair / slots of x when slots > 0: the token gather; row pair when slots == 0) by that expert's weight and writes
  * row `pair` of out.  tiled: [experts][ceil(n / 128)][k / gs][unit] 4-bit units, expert_stride words apart.
  * epi 0: out fp32 (out_f32 = 1) or bf16; 1: relu^2 (bf16); 2: SwiGLU over gate/up-interleaved rows (bf16, n / 2 columns).
- * tile = pairs an item may hold (8, 16, 32, 64).  Replaces the pybind `run` and `prefill` of cuda/experts.cpp:57-82. */
-int tf_moe_experts(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int n, int k, int gs,
-                   const int* items, const int* counts, const int* members, int max_items, int tile, void* out, int64_t ldo,
-                   int out_f32, int epi, float limit, void* stream);
+ * tile = pairs an item may hold (8, 16, 32, 64).  experts = experts the table holds: an item that names another expert is
+ * skipped (nothing is read past the table) and tf_device_error reports 5, where the reference's TORCH_CHECKs refuse a
+ * plan built for another table before launching (cuda/experts.cpp:16-41).  Replaces the pybind `run` and `prefill` of
+ * cuda/experts.cpp:57-82. */
+int tf_moe_experts(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int experts, int n, int k,
+                   int gs, const int* items, const int* counts, const int* members, int max_items, int tile, void* out,
+                   int64_t ldo, int out_f32, int epi, float limit, void* stream);
 /* The same grouped projection in the prefill arithmetic (weights rounded once to bf16, one fp32 chain over K) on
  * tcgen05: the rows are first copied in member order into `sorted` ([pairs, k] bf16, caller scratch), then every item
  * (at most 128 pairs) runs as one tensor-memory tile per 128 output columns.  Plans for it use items of 128 pairs.
  * Replaces the pybind `prefill` of cuda/experts.cpp:69-82 (cuda/experts_prefill.cu:31-152). */
-int tf_moe_experts_prefill(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int n, int k,
-                           int gs, const int* items, const int* counts, const int* members, int pairs, int max_items,
+int tf_moe_experts_prefill(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int experts, int n,
+                           int k, int gs, const int* items, const int* counts, const int* members, int pairs, int max_items,
                            void* sorted, void* out, int64_t ldo, int out_f32, int epi, float limit, void* stream);
 /* logits[r, e] = fp32 dot of bf16 rows x[r] and w[e].  Replaces the Triton `_router` of cuda/moe.py:23-55. */
 int tf_moe_router(const void* x, int64_t ldx, int rows, int d, const void* w, int ne, float* out, int64_t ldo, void* stream);
@@ -176,6 +187,12 @@ int tf_moe_router_tiles(const void* x, int64_t ldx, int rows, int d, const void*
  * Replaces the Triton `_topk_rows` of cuda/moe.py:58-85. */
 int tf_moe_topk(const float* logits, int64_t ldl, int rows, int experts, int topk, int shared, int* pick, float* wts,
                 void* stream);
+/* The same choice for a rank that holds experts [first, first + count) of the layer: slots of those experts carry the
+ * local id (id - first) and their weight; every other slot, the shared one among them, carries id -1 and weight 0, so
+ * tf_moe_plan and tf_moe_combine leave it out.  logits[.., experts] is not read.  The expert-parallel form of this
+ * library; the reference splits every expert's width instead (families/nemotron_h/cuda/tp.py:38-51). */
+int tf_moe_topk_local(const float* logits, int64_t ldl, int rows, int experts, int topk, int shared, int first, int count,
+                      int* pick, float* wts, void* stream);
 /* out[r, :] = bf16(sum over slots, in slot order, of wts[r, k] * y[r, k, :]) in fp32; y fp32 or bf16 (y_bf16).
  * Replaces the Triton `_combine` of cuda/moe.py:130-150. */
 int tf_moe_combine(const void* y, int y_bf16, const float* wts, int rows, int slots, int d, void* out, void* stream);
@@ -192,6 +209,28 @@ int tf_affine_rows(const void* ids, int ids64, int rows, const void* words, cons
  * bf16 with parts_bf16), one rounding, so every rank ends with the same bits.  Generalises the two-rank
  * rank0.float() + rank1.float() of families/qwen3_5/cuda/distributed.py:281-284. */
 int tf_sum_ranks(const void* parts, int world, int64_t total, int parts_bf16, void* out, int out_f32, void* stream);
+
+/* ---- the same reduction in one launch over peer memory ------------------------------------------------------------
+ * Every rank (one process a GPU, 2, 4 or 8 of them on one NVLink box) allocates one buffer of the same size with
+ * tf_peer_alloc (zeroed; its first tf_peer_flag_bytes() bytes are the flags the ranks signal each other with), exports
+ * it (a 64-byte handle the host passes to the other processes by any means) and opens the others'.  tf_peer_reduce
+ * then sums the `total` elements at byte offset part_off of EVERY rank's buffer (fp32, or bf16 with parts_bf16) in
+ * rank order, fp32 adds, one rounding, into byte offset out_off of this rank's buffer: the bits of tf_sum_ranks over
+ * the gathered partials.  Every rank calls it once per reduction with the same arguments, after the kernel that wrote
+ * its partial, on the same stream.  two_shot: a rank sums only its 1/world share and stores it into every rank's
+ * result (less NVLink traffic for large partials; total a multiple of 8 * world); otherwise every rank reads all
+ * partials (total a multiple of 8).  polls: limit of each wait on a peer (0: about a second); a wait that runs out
+ * sets device error 4 (tf_device_error) and the kernel returns; the buffers must then be freed and made anew.
+ * grid_cap > 0 bounds the blocks (testing).  No counterpart in the reference, which reduces its two ranks with an
+ * all-gather and a torch add (families/qwen3_5/cuda/distributed.py:249-284). */
+size_t tf_peer_flag_bytes(void);
+int tf_peer_alloc(size_t bytes, void** ptr);
+int tf_peer_free(void* ptr);
+int tf_peer_export(void* ptr, void* handle64);
+int tf_peer_open(const void* handle64, void** ptr);
+int tf_peer_close(void* ptr);
+int tf_peer_reduce(void* const* bufs, int rank, int world, size_t part_off, size_t out_off, int64_t total, int parts_bf16,
+                   int out_f32, int two_shot, unsigned polls, int grid_cap, void* stream);
 
 /* Glue that feeds the matmuls (rows contiguous, bf16, 16-byte aligned; d a multiple of gs; one block a row, so a row's
  * bits do not depend on the row count).

@@ -1,0 +1,6 @@
+"""``tensorfold.families.qwen3_5.cuda.distributed`` of the reference, served by ``tensorfold_b200.families.qwen3_5.cuda.distributed``."""
+
+import importlib
+import sys
+
+sys.modules[__name__] = importlib.import_module("tensorfold_b200.families.qwen3_5.cuda.distributed")

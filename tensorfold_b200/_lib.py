@@ -38,13 +38,22 @@ SIGNATURES = {
     "tf_moe_plan_blocks": (_i32, (_i32,)),
     "tf_moe_plan": (_i32, (_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp)),
     "tf_moe_plan_static": (_i32, (_vp, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp)),
-    "tf_moe_experts": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _i64, _i32, _i32,
+    "tf_moe_experts": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _i64, _i32, _i32,
                               ctypes.c_float, _vp)),
-    "tf_moe_experts_prefill": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i32,
-                                      _i32, ctypes.c_float, _vp)),
+    "tf_moe_experts_prefill": (_i32, (_vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64,
+                                      _i32, _i32, ctypes.c_float, _vp)),
+    "tf_selftest_lost_wait": (_i32, (_i32, _vp)),
     "tf_moe_router": (_i32, (_vp, _i64, _i32, _i32, _vp, _i32, _vp, _i64, _vp)),
     "tf_moe_router_tiles": (_i32, (_vp, _i64, _i32, _i32, _vp, _i32, _vp, _i64, _vp)),
     "tf_moe_topk": (_i32, (_vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp)),
+    "tf_peer_flag_bytes": (ctypes.c_size_t, ()),
+    "tf_peer_alloc": (_i32, (ctypes.c_size_t, _vp)),
+    "tf_peer_free": (_i32, (_vp,)),
+    "tf_peer_export": (_i32, (_vp, _vp)),
+    "tf_peer_open": (_i32, (_vp, _vp)),
+    "tf_peer_close": (_i32, (_vp,)),
+    "tf_peer_reduce": (_i32, (_vp, _i32, _i32, ctypes.c_size_t, ctypes.c_size_t, _i64, _i32, _i32, _i32, ctypes.c_uint, _i32, _vp)),
+    "tf_moe_topk_local": (_i32, (_vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp)),
     "tf_moe_combine": (_i32, (_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp)),
     "tf_affine_rows": (_i32, (_vp, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp)),
     "tf_add_rmsnorm": (_i32, (_vp, _vp, _vp, _i32, _i32, ctypes.c_float, _vp, _vp, _vp, _i32, _vp)),
@@ -96,6 +105,10 @@ def stream_of(t) -> int:
     if not t.is_cuda:
         raise ValueError("operands must live on a CUDA device: this path has no CPU implementation")
     ensure_device(t.device.index)
+    if t.device.index != torch.cuda.current_device():
+        # the entry points take per-device state (error word, SM count, built-in scratch) from the CURRENT device
+        raise ValueError(f"operands live on cuda:{t.device.index} but cuda:{torch.cuda.current_device()} is current: "
+                         "call under torch.cuda.device(tensor.device)")
     return torch.cuda.current_stream(t.device).cuda_stream
 
 

@@ -289,8 +289,10 @@ __global__ void __launch_bounds__(128) router_tiles_staged_kernel(const __nv_bfl
 
 __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// With count > 0 the ids are rewritten for a rank that owns experts [first, first + count): local ids for those, -1 and a
+// zero weight for every other slot (the shared slot among them), so the planner and the combine leave them out.
 __global__ void topk_kernel(const float* __restrict__ logits, int64_t ldl, int rows, int experts, int topk, int shared,
-                            int* __restrict__ pick, float* __restrict__ wts) {
+                            int first, int count, int* __restrict__ pick, float* __restrict__ wts) {
   const int lane = threadIdx.x & 31, r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= rows) return;
   const float* l = logits + r * ldl;
@@ -322,13 +324,23 @@ __global__ void topk_kernel(const float* __restrict__ logits, int64_t ldl, int r
     }
   }
   if (lane < topk) {
+    float w = bf16r(mine_ex / total);
+    if (count > 0) {
+      mine_id -= first;
+      if (mine_id < 0 || mine_id >= count) mine_id = -1, w = 0.f;
+    }
     pick[r * slots + lane] = mine_id;
-    wts[r * slots + lane] = bf16r(mine_ex / total);
+    wts[r * slots + lane] = w;
   }
   if (shared && lane == 0) {
-    const float sg = bf16r(l[experts]);
-    pick[r * slots + topk] = experts;
-    wts[r * slots + topk] = bf16r(1.f / (1.f + expf(-sg)));
+    if (count > 0) {
+      pick[r * slots + topk] = -1;
+      wts[r * slots + topk] = 0.f;
+    } else {
+      const float sg = bf16r(l[experts]);
+      pick[r * slots + topk] = experts;
+      wts[r * slots + topk] = bf16r(1.f / (1.f + expf(-sg)));
+    }
   }
 }
 
@@ -447,9 +459,24 @@ constexpr int STATIC_PLAN_HIST = 65536;               // blocks * experts it may
 // GPU that loads the library holds these 320 KB until the process exits.
 static __device__ __align__(256) int g_plan_scratch[STATIC_PLAN_PAIRS + STATIC_PLAN_HIST];
 
-int* g_plan_scratch_ptr[64] = {};                     // device address of the array, per device, resolved on first use
+int* g_plan_scratch_ptr[64] = {};                     // device address of the array, per device (set once, under tf_init's lock)
 
 }  // namespace
+
+// Called by tf_init with `device` current: looks the array's address up once, so that tf_moe_plan_static itself is a
+// pure look-up afterwards (no symbol query, no module load: safe under stream capture).  The array's name is only a
+// host-side handle; the kernels need its address on that device.
+cudaError_t moe_static_init(int device) {
+  if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+  if (g_plan_scratch_ptr[device] != nullptr) return cudaSuccess;
+  int* ptr = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_plan_scratch);
+  if (e != cudaSuccess) return e;
+  if (ptr == nullptr) return cudaErrorInvalidSymbol;
+  g_plan_scratch_ptr[device] = ptr;
+  return cudaSuccess;
+}
+
 }  // namespace tf
 
 extern "C" {
@@ -469,13 +496,8 @@ int tf_moe_plan_static(const int* picks, int pairs, int experts, int tile, int* 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail_moe(e, "tf_moe_plan_static: cudaGetDevice");
   if (dev < 0 || dev >= 64) return fail_moe(TF_ERR_ARG, "tf_moe_plan_static: device index out of range");
-  if (g_plan_scratch_ptr[dev] == nullptr) {
-    // The array's name is only a host-side handle; the kernel needs its address on the current device.
-    int* ptr = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_plan_scratch);
-    if (e != cudaSuccess || ptr == nullptr) return cuda_fail_moe(e, "tf_moe_plan_static: cudaGetSymbolAddress");
-    g_plan_scratch_ptr[dev] = ptr;
-  }
+  if (g_plan_scratch_ptr[dev] == nullptr)
+    return fail_moe(TF_ERR_STATE, "tf_moe_plan_static: tf_init has not been called for the current device");
   int* rank = g_plan_scratch_ptr[dev];
   return tf_moe_plan(picks, pairs, experts, tile, members, items, counts, rank, rank + STATIC_PLAN_PAIRS, max_items, stream);
 }
@@ -516,9 +538,21 @@ int tf_moe_topk(const float* logits, int64_t ldl, int rows, int experts, int top
   if (rows < 1 || experts < 1 || experts > 1024 || topk < 1 || topk > 32 || topk > experts || !logits || !pick || !wts ||
       ldl < experts + (shared ? 1 : 0))
     return fail_moe(TF_ERR_ARG, "tf_moe_topk: bad arguments (at most 1024 experts, top 32)");
-  topk_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, ldl, rows, experts, topk, shared, pick, wts);
+  topk_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, ldl, rows, experts, topk, shared, 0, 0, pick,
+                                                                             wts);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_topk");
+}
+
+int tf_moe_topk_local(const float* logits, int64_t ldl, int rows, int experts, int topk, int shared, int first, int count,
+                      int* pick, float* wts, void* stream) {
+  if (rows < 1 || experts < 1 || experts > 1024 || topk < 1 || topk > 32 || topk > experts || !logits || !pick || !wts ||
+      ldl < experts || first < 0 || count < 1 || first + count > experts)
+    return fail_moe(TF_ERR_ARG, "tf_moe_topk_local: bad arguments (at most 1024 experts, top 32, a range inside them)");
+  topk_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, ldl, rows, experts, topk, shared, first,
+                                                                             count, pick, wts);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_topk_local");
 }
 
 int tf_moe_combine(const void* y, int y_bf16, const float* wts, int rows, int slots, int d, void* out, void* stream) {

@@ -1,0 +1,285 @@
+// Rank-ordered all-reduce of partial sums over peer memory (NVLink / NVSwitch), one launch a rank: the ranks' buffers are
+// mapped into every process, a rank reads the partials of all ranks with plain peer loads, adds them in rank order in
+// fp32 ((p0 + p1) + p2 ...), rounds once and writes the result.  Generalises the two-rank
+// rank0.float() + rank1.float() of families/qwen3_5/cuda/distributed.py:249-284 (an all-gather and an add there).
+//
+// Each rank's buffer starts with a page of 32-bit flags, 128 bytes apart:
+//   ready[r]  how many reductions rank r has announced its partial for
+//   done[r]   how many reductions rank r has finished reading and writing
+//   calls     reductions this rank has completed (the kernel reads it at entry and bumps it at exit, so launches
+//             replayed from a CUDA graph keep counting)
+//   arrive    blocks of the running launch that have finished their share
+// A launch: announce `ready` on every rank, wait for every rank's `ready`, reduce, count the blocks in, the last block
+// announces `done` on every rank, wait for every rank's `done` (all shares have landed here, and no rank still reads this
+// rank's partial), bump `calls`.  Every wait has a poll limit; a wait that runs out sets ERR_WAIT_PEER in the device error
+// word, the kernel skips its remaining waits and returns, and the host sees the error at its next check.
+//
+// All blocks of a launch must be resident at once (they wait for one another through `arrive`): the grid is bounded by
+// the occupancy the runtime reports for the kernel.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "../../include/tensorfold_b200.h"
+#include "tf_ptx.cuh"
+
+namespace tf {
+
+int fail_moe(int code, const char* msg);
+int cuda_fail_moe(cudaError_t e, const char* what);
+int* device_error_word();
+
+namespace {
+
+constexpr int PEER_MAX = 8;
+constexpr int PEER_THREADS = 512;
+constexpr int FLAG_WORDS = 32;                 // flags sit 128 bytes apart
+constexpr int FLAG_READY = 0, FLAG_DONE = PEER_MAX, FLAG_CALLS = 2 * PEER_MAX, FLAG_ARRIVE = 2 * PEER_MAX + 1;
+constexpr size_t FLAG_BYTES = 4096;
+static_assert((FLAG_ARRIVE + 1) * FLAG_WORDS * 4 <= FLAG_BYTES, "the flags fit their page");
+
+struct PeerArgs {
+  char* buf[PEER_MAX];                         // every rank's buffer as this process sees it (buf[rank] is local)
+  char* mine;                                  // buf[rank]
+  int rank, world;
+  size_t part_off, out_off;                    // byte offsets of the partial and of the result inside every buffer
+  int64_t total;                               // elements of the partial
+  int parts_bf16, out_f32, two_shot;
+  uint32_t polls;                              // limit of every wait
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t* flag(char* buf, int which) { return reinterpret_cast<uint32_t*>(buf) + which * FLAG_WORDS; }
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void add_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_peer16(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_peer16(void* p, const uint4& v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Waits until *p has reached `target` (counters only grow; the comparison survives their wrap).
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t target, uint32_t polls) {
+  for (uint32_t i = 0; i < polls; ++i) {
+    if (static_cast<int32_t>(ld_acquire_sys(p) - target) >= 0) return true;
+    __nanosleep(i < 64 ? 20 : 400);
+  }
+  return false;
+}
+
+// Eight consecutive elements of every rank's partial, summed in rank order.
+template <int WORLD, bool BF16>
+__device__ __forceinline__ void sum8(const PeerArgs& a, int64_t i, float (&acc)[8]) {
+  if constexpr (BF16) {
+    uint4 q[WORLD];
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) q[r] = ld_peer16(a.buf[r] + a.part_off + i * 2);
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) {
+      const uint32_t u[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = __uint_as_float(u[j] << 16), hi = __uint_as_float(u[j] & 0xFFFF0000u);
+        acc[2 * j] = r == 0 ? lo : acc[2 * j] + lo;
+        acc[2 * j + 1] = r == 0 ? hi : acc[2 * j + 1] + hi;
+      }
+    }
+  } else {
+    uint4 q[WORLD][2];
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) {
+      q[r][0] = ld_peer16(a.buf[r] + a.part_off + i * 4);
+      q[r][1] = ld_peer16(a.buf[r] + a.part_off + i * 4 + 16);
+    }
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) {
+      const uint32_t u[8] = {q[r][0].x, q[r][0].y, q[r][0].z, q[r][0].w, q[r][1].x, q[r][1].y, q[r][1].z, q[r][1].w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = r == 0 ? __uint_as_float(u[j]) : acc[j] + __uint_as_float(u[j]);
+    }
+  }
+}
+
+// Stores eight results at element i of the result inside `buf`.
+__device__ __forceinline__ void store8(const PeerArgs& a, char* buf, int64_t i, const float (&acc)[8]) {
+  if (a.out_f32) {
+    char* o = buf + a.out_off + i * 4;
+    st_peer16(o, make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3])));
+    st_peer16(o + 16, make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]), __float_as_uint(acc[6]), __float_as_uint(acc[7])));
+  } else {
+    uint32_t u[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 t = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      u[j] = *reinterpret_cast<const uint32_t*>(&t);
+    }
+    st_peer16(buf + a.out_off + i * 2, make_uint4(u[0], u[1], u[2], u[3]));
+  }
+}
+
+template <int WORLD, bool BF16>
+__global__ void __launch_bounds__(PEER_THREADS) peer_reduce_kernel(const PeerArgs a) {
+  __shared__ uint32_t s_target;
+  __shared__ int s_lost, s_last;
+  __shared__ char* s_buf[WORLD];               // the buffers by a run-time index
+  const int tid = threadIdx.x;
+  char* mine = a.mine;
+#pragma unroll
+  for (int r = 0; r < WORLD; ++r)
+    if (tid == r) s_buf[r] = a.buf[r];
+  if (tid == 0) {
+    s_target = *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_CALLS)) + 1;
+    s_lost = 0;
+  }
+  __syncthreads();
+  const uint32_t target = s_target;
+
+  // this rank's partial was written by an earlier kernel of this stream: announce it, then wait for everyone's
+  if (blockIdx.x == 0 && tid < WORLD) add_release_sys(flag(s_buf[tid], FLAG_READY + a.rank), 1);
+  if (tid < WORLD && !wait_flag(flag(mine, FLAG_READY + tid), target, a.polls)) s_lost = 1;
+  __syncthreads();
+  const bool lost = s_lost != 0;
+
+  if (!lost) {
+    const int64_t step = static_cast<int64_t>(gridDim.x) * PEER_THREADS * 8;
+    const int64_t lane0 = (static_cast<int64_t>(blockIdx.x) * PEER_THREADS + tid) * 8;
+    if (a.two_shot) {                          // this rank sums its share and hands it to every rank
+      const int64_t share = a.total / WORLD, base = share * a.rank;
+      for (int64_t i = lane0; i < share; i += step) {
+        float acc[8];
+        sum8<WORLD, BF16>(a, base + i, acc);
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) store8(a, a.buf[r], base + i, acc);
+      }
+    } else {                                   // every rank sums everything for itself
+      for (int64_t i = lane0; i < a.total; i += step) {
+        float acc[8];
+        sum8<WORLD, BF16>(a, i, acc);
+        store8(a, mine, i, acc);
+      }
+    }
+  }
+
+  // count the blocks in; the last one tells every rank that this rank has finished reading and writing
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(flag(mine, FLAG_ARRIVE), 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (tid < WORLD) add_release_sys(flag(s_buf[tid], FLAG_DONE + a.rank), 1);
+    if (tid == 0) *flag(mine, FLAG_ARRIVE) = 0;
+  }
+  if (!lost && tid < WORLD && !wait_flag(flag(mine, FLAG_DONE + tid), target, a.polls)) s_lost = 1;
+  __syncthreads();
+  if (s_lost && tid == 0) atomicCAS(a.err, 0, ERR_WAIT_PEER);
+  if (s_last && tid == 0) {
+    *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_CALLS)) = target;
+    __threadfence();
+  }
+}
+
+template <int WORLD>
+cudaError_t launch_world(const PeerArgs& a, int grid_cap, cudaStream_t s) {
+  auto run = [&](auto kernel) -> cudaError_t {
+    int per_sm = 0, dev = 0, sms = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, PEER_THREADS, 0);
+    if (e != cudaSuccess) return e;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    const int64_t work = a.two_shot ? a.total / a.world : a.total;
+    int64_t grid = (work / 8 + PEER_THREADS - 1) / PEER_THREADS;
+    const int64_t resident = static_cast<int64_t>(per_sm > 0 ? per_sm : 1) * sms;
+    if (grid > resident) grid = resident;
+    if (grid_cap > 0 && grid > grid_cap) grid = grid_cap;
+    if (grid < 1) grid = 1;
+    kernel<<<static_cast<unsigned>(grid), PEER_THREADS, 0, s>>>(a);
+    return cudaGetLastError();
+  };
+  return a.parts_bf16 ? run(peer_reduce_kernel<WORLD, true>) : run(peer_reduce_kernel<WORLD, false>);
+}
+
+}  // namespace
+}  // namespace tf
+
+using namespace tf;
+
+extern "C" {
+
+size_t tf_peer_flag_bytes(void) { return FLAG_BYTES; }
+
+int tf_peer_alloc(size_t bytes, void** ptr) {
+  if (!ptr || bytes < FLAG_BYTES) return fail_moe(TF_ERR_ARG, "tf_peer_alloc: a buffer holds its page of flags at least");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return cuda_fail_moe(e, "tf_peer_alloc");
+  if ((e = cudaMemset(p, 0, bytes)) != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail_moe(e, "tf_peer_alloc: clearing");
+  }
+  *ptr = p;
+  return TF_OK;
+}
+
+int tf_peer_free(void* ptr) {
+  const cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_peer_free");
+}
+
+int tf_peer_export(void* ptr, void* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "an exported handle is 64 bytes");
+  if (!ptr || !handle64) return fail_moe(TF_ERR_ARG, "tf_peer_export: null argument");
+  const cudaError_t e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), ptr);
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_peer_export");
+}
+
+int tf_peer_open(const void* handle64, void** ptr) {
+  if (!handle64 || !ptr) return fail_moe(TF_ERR_ARG, "tf_peer_open: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  const cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_peer_open");
+}
+
+int tf_peer_close(void* ptr) {
+  const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_peer_close");
+}
+
+int tf_peer_reduce(void* const* bufs, int rank, int world, size_t part_off, size_t out_off, int64_t total, int parts_bf16,
+                   int out_f32, int two_shot, unsigned polls, int grid_cap, void* stream) {
+  if (!bufs || (world != 2 && world != 4 && world != 8) || rank < 0 || rank >= world || total < 8)
+    return fail_moe(TF_ERR_ARG, "tf_peer_reduce: 2, 4 or 8 ranks and at least eight elements");
+  if (total % (two_shot ? 8 * world : 8)) return fail_moe(TF_ERR_ARG, "tf_peer_reduce: the elements split into pieces of eight (a rank)");
+  if (part_off < FLAG_BYTES || out_off < FLAG_BYTES || part_off % 16 || out_off % 16)
+    return fail_moe(TF_ERR_ALIGN, "tf_peer_reduce: offsets past the flags, 16-byte aligned");
+  const size_t part_bytes = static_cast<size_t>(total) * (parts_bf16 ? 2 : 4), out_bytes = static_cast<size_t>(total) * (out_f32 ? 4 : 2);
+  if ((part_off < out_off ? part_off + part_bytes > out_off : out_off + out_bytes > part_off))
+    return fail_moe(TF_ERR_ARG, "tf_peer_reduce: the partial and the result overlap");
+  int* err = device_error_word();
+  if (!err) return fail_moe(TF_ERR_STATE, "tf_peer_reduce: tf_init has not run for the current device");
+  PeerArgs a = {};
+  for (int r = 0; r < world; ++r) {
+    if (!bufs[r] || reinterpret_cast<uintptr_t>(bufs[r]) % 256) return fail_moe(TF_ERR_ALIGN, "tf_peer_reduce: a buffer is null or not 256-byte aligned");
+    a.buf[r] = static_cast<char*>(bufs[r]);
+  }
+  a.mine = a.buf[rank];
+  a.rank = rank, a.world = world, a.part_off = part_off, a.out_off = out_off, a.total = total;
+  a.parts_bf16 = parts_bf16, a.out_f32 = out_f32, a.two_shot = two_shot, a.polls = polls ? polls : (1u << 20), a.err = err;
+  const cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const cudaError_t e = world == 2 ? launch_world<2>(a, grid_cap, s) : world == 4 ? launch_world<4>(a, grid_cap, s) : launch_world<8>(a, grid_cap, s);
+  return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_peer_reduce");
+}
+
+}  // extern "C"

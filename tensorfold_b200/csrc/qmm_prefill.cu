@@ -71,6 +71,7 @@ struct PrefillParams {
   const int* counts;
   const int* members;
   int64_t expert_stride;
+  int experts;                // experts the table holds (grouped form)
   int epi;                    // 0 store, 1 relu^2, 2 SwiGLU over gate/up rows interleaved in tiles of 16 (out: N / 2 columns)
   float limit;
 };
@@ -175,9 +176,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     ti.wroot = p.w;
     if (grouped) {
       const int* item = p.items + 3 * y;
-      ti.wroot += static_cast<int64_t>(item[0]) * p.expert_stride;
+      // an item that names an expert outside the table runs against expert 0 with no rows (nothing is stored) and
+      // is reported: every role still walks the same tile sequence, and nothing is read past the table
+      const bool known = item[0] >= 0 && item[0] < p.experts;
+      if (!known && threadIdx.x == 0) atomicCAS(p.err, 0, ERR_BAD_ITEM);
+      ti.wroot += static_cast<int64_t>(known ? item[0] : 0) * p.expert_stride;
       ti.first = item[1];
-      ti.rows_here = min(PF_ROWS, item[2]);
+      ti.rows_here = known ? min(PF_ROWS, item[2]) : 0;
       ti.m0 = item[1];                                       // row of the member-ordered input
     } else {
       ti.first = 0;
@@ -586,10 +591,11 @@ extern "C" int tf_qmm_prefill_act(const void* x, int64_t ldx, int m, const void*
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_qmm_prefill");
 }
 
-extern "C" int tf_moe_experts_prefill(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int n,
-                                      int k, int gs, const int* items, const int* counts, const int* members, int pairs,
-                                      int max_items, void* sorted, void* out, int64_t ldo, int out_f32, int epi, float limit,
-                                      void* stream) {
+extern "C" int tf_moe_experts_prefill(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride,
+                                      int experts, int n, int k, int gs, const int* items, const int* counts,
+                                      const int* members, int pairs, int max_items, void* sorted, void* out, int64_t ldo,
+                                      int out_f32, int epi, float limit, void* stream) {
+  if (experts < 1) return fail_moe(TF_ERR_ARG, "tf_moe_experts_prefill: the table holds at least one expert");
   if (gs != 32 && gs != 64) return fail_moe(TF_ERR_UNSUPPORTED, "tf_moe_experts_prefill: 4-bit weights with groups of 32 or 64");
   if (n < 1 || k < gs || k % gs || k % 8 || pairs < 1 || max_items < 1 || max_items > 65535)
     return fail_moe(TF_ERR_ARG, "tf_moe_experts_prefill: bad sizes");
@@ -614,6 +620,7 @@ extern "C" int tf_moe_experts_prefill(const void* x, int64_t ldx, int slots, con
   p.err = err;
   p.items = items, p.counts = counts, p.members = members;
   p.expert_stride = expert_stride;
+  p.experts = experts;
   p.epi = epi, p.limit = limit;
   const int64_t tiles = static_cast<int64_t>((n + PF_COLS - 1) / PF_COLS) * max_items;   // upper bound: the plan says how many
   const int sms = sm_count();

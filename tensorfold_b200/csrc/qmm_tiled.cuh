@@ -31,22 +31,6 @@ namespace tf {
 
 namespace cg = cooperative_groups;
 
-#ifdef TF_TRACE
-// debug build only: block (0, 0, 0) logs (event, stage, clock) into shared memory, dumped to p.part when it ends
-#ifndef TF_TRACE_EVENTS
-#define TF_TRACE_EVENTS 200
-#endif
-#define TF_MARK(ev, st)                                                                    \
-  do {                                                                                     \
-    if (tf_trace_on && lane == 0 && tf_tr < TF_TRACE_EVENTS) {                             \
-      tf_trace[warp][tf_tr] = (static_cast<long long>((ev) * 1000 + (st)) << 40) | (clock64() & 0xFFFFFFFFFFLL); \
-      ++tf_tr;                                                                             \
-    }                                                                                      \
-  } while (0)
-#else
-#define TF_MARK(ev, st) do {} while (0)
-#endif
-
 struct QmmParams {
   const __nv_bfloat16* x;     // [M, K] bf16, row stride ldx elements, rows 16-byte aligned
   int64_t ldx;
@@ -71,6 +55,7 @@ struct QmmParams {
   const int* members;         // pair ids grouped by expert
   int slots;
   int64_t expert_stride;      // words from one expert's units to the next
+  int experts;                // experts the table holds: an item that names another one is skipped and reported
   // epilogue: 0 store as is; 1 bf16(relu(bf16 v)^2); 2 SwiGLU over column pairs: the weight rows interleave 16 gate
   // columns with 16 up columns, so a tile pair holds both halves and out has N / 2 columns.
   int epi;
@@ -182,18 +167,6 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(recv_bar + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef TF_TRACE
-  __shared__ long long tf_trace[6][TF_TRACE_EVENTS];
-  int tf_tr = 0;
-  const bool tf_trace_on = blockIdx.x == TF_TRACE_BX && blockIdx.y == 0 && blockIdx.z == 0 && warp < 6;
-  unsigned long long tf_t_start;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tf_t_start));
-  unsigned int tf_smid;
-  asm volatile("mov.u32 %0, %%smid;" : "=r"(tf_smid));
-  unsigned long long tf_t1 = 0, tf_t2 = 0, tf_t3 = 0;
-#define TF_STAMP(v) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v))
-  for (int i = tid; i < 6 * TF_TRACE_EVENTS; i += blockDim.x) (&tf_trace[0][0])[i] = 0;
-#endif
   const int nsb = (p.N + SB_COLS - 1) / SB_COLS;
   const int sb0 = blockIdx.x * KW;                          // lane kw streams super-block sb0 + kw (if it exists)
   const int lanes_here = min(KW, nsb - sb0);
@@ -209,6 +182,10 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
     pdl_wait();                                             // the plan may be the previous kernel's output
     if (static_cast<int>(blockIdx.y) >= p.counts[0]) return;
     const int* item = p.items + 3 * blockIdx.y;
+    if (item[0] < 0 || item[0] >= p.experts) {              // never read past the table: skip the item, tell the host
+      if (tid == 0) atomicCAS(p.err, 0, ERR_BAD_ITEM);
+      return;
+    }
     wroot += static_cast<int64_t>(item[0]) * p.expert_stride;
     first = item[1];
     rows_here = min(ROWS, item[2]);
@@ -233,9 +210,6 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
     mbar_fence_init();
   }
   __syncthreads();
-#ifdef TF_TRACE
-  TF_STAMP(tf_t1);
-#endif
   pdl_launch_dependents();
 
   auto stage_ptr = [&](int slot) { return smem + slot * Geo::STAGE; };
@@ -301,10 +275,8 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
         give_up(ERR_WAIT_EMPTY);
         break;
       }
-      TF_MARK(10, st);
       issue_w(st, slot);
       issue_x(st, slot);
-      TF_MARK(11, st);
     }
     if (!ok) {
       // give copies still in flight time to land before this block's shared memory is released
@@ -320,7 +292,6 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
         break;
       }
       const int ng = groups_of(st);
-      TF_MARK(20, st);
       float* xs_s = reinterpret_cast<float*>(stage_ptr(slot) + Geo::XS_OFF);
       if (p.xs != nullptr) {
         const int g0 = g_first + st * G;
@@ -344,7 +315,6 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(sums + slot);               // also tells the consumers that the stage has landed
-      TF_MARK(21, st);
     }
   } else {
     // ------------------------------------------------------------------ consumers: dequantise, MMA, affine epilogue
@@ -357,9 +327,7 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
     for (int st = 0; st < nstages && ok; ++st) {
       const int slot = st % NST;
       const uint32_t parity = (st / NST) & 1;
-      TF_MARK(0, st);
       ok = mbar_wait_probed(ready, sums + slot, parity, abort_flag);
-      TF_MARK(1, st);
       if (!ok) {
         give_up(ERR_WAIT_SUMS);
         break;
@@ -432,7 +400,6 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
           }
         }
 
-        TF_MARK(5 + 2 * u, st);
         const uint32_t sbv[4] = {sbw.x, sbw.y, sbw.z, sbw.w};       // (tile 0, col g), (0, g + 8), (1, g), (1, g + 8)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -447,18 +414,13 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
             acc[h][mt][3] = fmaf(xv.y, c1, fmaf(P[h][mt][3], s1, acc[h][mt][3]));
           }
         }
-        TF_MARK(6 + 2 * u, st);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty + slot);
-      TF_MARK(4, st);
     }
   }
 
   // -------------------------------------------------------------------- output: stage, sum the slices in order, store
-#ifdef TF_TRACE
-  TF_STAMP(tf_t2);
-#endif
   __syncthreads();                                          // every stage consumed: its memory becomes the staging tiles
   pdl_wait();                                               // nothing is written before the previous kernel is done
   float* red = reinterpret_cast<float*>(smem);              // [KW][ROWS][RED_STRIDE]
@@ -480,9 +442,6 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
   const bool clustered = p.cluster && p.sk > 1;
   cg::cluster_group cluster = cg::this_cluster();
   if (clustered) cluster.sync(); else __syncthreads();
-#ifdef TF_TRACE
-  TF_STAMP(tf_t3);
-#endif
 
   const bool failed = *abort_flag != 0;
   if (!failed && p.epi == 2) {
@@ -595,20 +554,6 @@ qmm_tiled_kernel(const __grid_constant__ CUtensorMap tmx, const QmmParams p) {
     volatile int never = 0;
     mbar_wait_cluster(recv_bar, 0, &never);
   }
-#ifdef TF_TRACE
-  __syncthreads();
-  if (tid == 0 && p.xs == nullptr && p.part != nullptr && p.cluster) {
-    unsigned long long tf_t_end;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tf_t_end));
-    const long long cta = (static_cast<long long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-    long long* rec = reinterpret_cast<long long*>(p.part) + 2048 + cta * 6;
-    rec[0] = static_cast<long long>(tf_t_start), rec[1] = static_cast<long long>(tf_t_end), rec[2] = tf_smid;
-    rec[3] = static_cast<long long>(tf_t1), rec[4] = static_cast<long long>(tf_t2), rec[5] = static_cast<long long>(tf_t3);
-  }
-  if (blockIdx.x == TF_TRACE_BX && blockIdx.y == 0 && blockIdx.z == 0 && p.xs == nullptr && p.part != nullptr && p.cluster)
-    for (int i = tid; i < 6 * TF_TRACE_EVENTS; i += blockDim.x)
-      reinterpret_cast<long long*>(p.part)[i] = (&tf_trace[0][0])[i];
-#endif
 }
 
 }  // namespace tf

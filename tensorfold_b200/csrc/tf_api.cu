@@ -56,6 +56,7 @@ std::mutex g_init_mutex;
 }  // namespace
 
 cudaError_t prefill_configure();      // qmm_prefill.cu
+cudaError_t moe_static_init(int device);   // moe.cu: the built-in plan scratch's address on that device
 int encode_rows(CUtensorMap* map, const void* x, int64_t ldx, int rows, int k, int box_rows);
 
 int* device_error_word() {
@@ -239,6 +240,20 @@ __global__ void sum_ranks_kernel(const void* __restrict__ parts, int world, int6
   }
 }
 
+// A wait nothing will ever satisfy, with a short limit: what a lost copy or a lost peer looks like to the host.  One
+// warp polls a barrier no one arrives on `polls` times, gives up, and reports through the device error word.
+__global__ void lost_wait_kernel(int polls, int* err) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  bool done = false;
+  for (int i = 0; i < polls && !done; ++i) done = mbar_try_wait_sleep(&bar, 0, 1000u);
+  if (!__all_sync(0xFFFFFFFFu, done) && threadIdx.x == 0) atomicCAS(err, 0, ERR_WAIT_FULL);
+}
+
 namespace {
 
 // The dense form fetches the rows of x with tensor-map copies ([64 inputs x row tile] boxes, 128-byte swizzle); the map
@@ -360,6 +375,7 @@ int tf_init(int device) {
             g_devices[device].resident[b][g][m][k] =
                 static_cast<signed char>(stream_resident_bits(BIT_WIDTHS[b], 32 << g, m + 1, 1 << k));
   }
+  if (e == cudaSuccess) e = moe_static_init(device);
   int* err = nullptr;
   if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_error_word);
   if (e == cudaSuccess) e = cudaMemset(err, 0, sizeof(int));
@@ -379,6 +395,15 @@ int tf_device_error(int device, void* stream, int* code) {
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e == cudaSuccess && *code != 0) e = cudaMemsetAsync(g_devices[device].err, 0, sizeof(int), s);
   return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_device_error");
+}
+
+int tf_selftest_lost_wait(int polls, void* stream) {
+  if (polls < 1 || polls > 4096) return fail(TF_ERR_ARG, "tf_selftest_lost_wait: 1 to 4096 polls");
+  DeviceState* st = nullptr;
+  if (int rc = current_state(&st)) return rc;
+  lost_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(polls, st->err);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_selftest_lost_wait");
 }
 
 int tf_tune(const char* key, int value) {
@@ -654,9 +679,10 @@ int tf_qmm_act(const void* x, int64_t ldx, int m, const void* tiled, int64_t sb_
   return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_qmm_act launch");
 }
 
-int tf_moe_experts(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int n, int k, int gs,
-                   const int* items, const int* counts, const int* members, int max_items, int tile, void* out, int64_t ldo,
-                   int out_f32, int epi, float limit, void* stream) {
+int tf_moe_experts(const void* x, int64_t ldx, int slots, const void* tiled, int64_t expert_stride, int experts, int n, int k,
+                   int gs, const int* items, const int* counts, const int* members, int max_items, int tile, void* out,
+                   int64_t ldo, int out_f32, int epi, float limit, void* stream) {
+  if (experts < 1) return fail(TF_ERR_ARG, "tf_moe_experts: the table holds at least one expert");
   if (!format_ok(4, gs)) return fail(TF_ERR_ARG, "tf_moe_experts: groups of 32, 64 or 128, not %d", gs);
   if (n < 1 || k < gs || k % gs || max_items < 1) return fail(TF_ERR_ARG, "tf_moe_experts: bad shape n=%d k=%d items=%d", n, k, max_items);
   if (tile != 8 && tile != 16 && tile != 32 && tile != 64) return fail(TF_ERR_ARG, "tf_moe_experts: items of 8, 16, 32 or 64 pairs");
@@ -681,6 +707,7 @@ int tf_moe_experts(const void* x, int64_t ldx, int slots, const void* tiled, int
   p.err = st->err;
   p.items = items, p.counts = counts, p.members = members, p.slots = slots;
   p.expert_stride = expert_stride;
+  p.experts = experts;
   p.epi = epi, p.limit = limit;
   const cudaError_t e = launch_bits(p, 4, gs, tile / 8, 1, static_cast<cudaStream_t>(stream), false);
   return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_moe_experts launch");

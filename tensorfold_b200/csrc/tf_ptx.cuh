@@ -17,6 +17,7 @@ enum ErrorCode : int {
   ERR_WAIT_EMPTY = 2,     // the producer never got a stage back
   ERR_WAIT_SUMS = 3,      // a consumer never saw the group sums
   ERR_WAIT_PEER = 4,      // a peer flag never arrived (cross-GPU reduce)
+  ERR_BAD_ITEM = 5,       // a plan item named an expert outside the table (the item was skipped)
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }

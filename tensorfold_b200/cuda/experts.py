@@ -161,12 +161,12 @@ def _grouped(x, slots, table, n, k, ex, plan, out, rows, epi, limit):
         if plan.sorted is None or plan.sorted.numel() < pairs * k:
             plan.sorted = torch.empty((pairs * max(k, ex.dims, ex.width),), dtype=torch.bfloat16, device=x.device)
         _lib.check(_lib.lib().tf_moe_experts_prefill(
-            x.data_ptr(), x.stride(0), slots, table.data_ptr(), table.stride(0), n, k, ex.gs, plan.items.data_ptr(),
+            x.data_ptr(), x.stride(0), slots, table.data_ptr(), table.stride(0), table.shape[0], n, k, ex.gs, plan.items.data_ptr(),
             plan.counts.data_ptr(), plan.members.data_ptr(), rows * plan.slots, items, plan.sorted.data_ptr(), out.data_ptr(),
             out.stride(0), int(out.dtype == torch.float32), epi, float(limit), stream), "experts (prefill)")
         return
     _lib.check(_lib.lib().tf_moe_experts(
-        x.data_ptr(), x.stride(0), slots, table.data_ptr(), table.stride(0), n, k, ex.gs, plan.items.data_ptr(),
+        x.data_ptr(), x.stride(0), slots, table.data_ptr(), table.stride(0), table.shape[0], n, k, ex.gs, plan.items.data_ptr(),
         plan.counts.data_ptr(), plan.members.data_ptr(), items, plan.tile, out.data_ptr(), out.stride(0),
         int(out.dtype == torch.float32), epi, float(limit), stream), "experts")
 

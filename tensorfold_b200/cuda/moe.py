@@ -58,6 +58,17 @@ def select_rows(logits: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int)
                                       buf.wts.data_ptr(), stream), "select_rows")
 
 
+def select_local_rows(logits: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int, first: int, count: int) -> None:
+    """``select_rows`` for a rank that holds experts [first, first + count): local ids and weights for those, id -1 and
+    weight 0 for every other slot (the shared one too).  logits: (R, >= E) fp32."""
+
+    rows = logits.shape[0]
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or logits.shape[1] < experts:
+        raise ValueError("select_local_rows: logits must be (R, E) fp32")
+    _lib.check(_lib.lib().tf_moe_topk_local(logits.data_ptr(), logits.stride(0), rows, experts, top_k, 1, first, count,
+                                            buf.pick.data_ptr(), buf.wts.data_ptr(), _lib.stream_of(logits)), "select_local_rows")
+
+
 def select(logits: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int) -> None:
     """Each row's experts and weights (rows in parallel), then the (row, slot) pairs grouped by expert."""
 
@@ -95,13 +106,16 @@ def moe(x: torch.Tensor, router_rows: torch.Tensor, ex: grouped.Experts, buf: Mo
     return buf
 
 
-def combine(y: torch.Tensor, wts: torch.Tensor) -> torch.Tensor:
+def combine(y: torch.Tensor, wts: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """y [R, S, D] (fp32, or bf16 in prefill) and wts [R, S] fp32 -> [R, D] bf16; a row's bits never depend on R."""
 
     rows, slots, dims = y.shape
     if not y.is_contiguous() or wts.dtype != torch.float32 or wts.shape != (rows, slots) or not wts.is_contiguous():
         raise ValueError("combine: y [R, S, D] and wts [R, S] fp32 must be contiguous")
-    out = torch.empty((rows, dims), dtype=torch.bfloat16, device=y.device)
+    if out is None:
+        out = torch.empty((rows, dims), dtype=torch.bfloat16, device=y.device)
+    elif out.shape != (rows, dims) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("combine: out must be a contiguous [R, D] bf16 tensor")
     stream = _lib.stream_of(y)
     _lib.check(_lib.lib().tf_moe_combine(y.data_ptr(), int(y.dtype == torch.bfloat16), wts.data_ptr(), rows, slots, dims,
                                          out.data_ptr(), stream), "combine")

@@ -9,11 +9,13 @@ across its two ranks instead, families/nemotron_h/cuda/tp.py:38-51)."""
 
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
 
+from .. import _lib
 from . import experts as grouped
 from . import moe
 from .kernels import qmm
@@ -46,6 +48,102 @@ def ordered_all_reduce(local: torch.Tensor, group=None, dtype: torch.dtype = tor
     return out.view(local.shape)
 
 
+class _Raw:
+    """A device address as an object torch can wrap (no copy, no ownership)."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerReducer:
+    """The rank-ordered all-reduce in one launch over peer memory (``tf_peer_reduce``): every rank owns one buffer that the
+    other processes of the box map, producers write their partial straight into it (``partial``), and ``reduce`` returns
+    the sum, the bits ``ordered_all_reduce`` gives.  Buffers: [flags | partial | result].  ``two_shot_from`` bytes and up,
+    a rank sums one share and stores it to every rank; below, every rank reads all partials itself.
+
+    The result tensor is a view of the buffer: it is overwritten by the next ``reduce``, and so is the partial."""
+
+    def __init__(self, elements: int, group=None, *, device=None, two_shot_from: int = 1 << 19, bufs: list[int] | None = None,
+                 rank: int | None = None) -> None:
+        lib = _lib.lib()
+        self.group, self.elements, self.two_shot_from = group, elements, two_shot_from
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.flags, self.part_off, self.out_off, self.nbytes = self.layout(elements)
+        self._opened: list[int] = []
+        self._owned = 0
+        if bufs is not None:                                   # buffers made by the caller (one process driving them all)
+            self.rank, self.world, self.bufs = rank, len(bufs), list(bufs)
+        else:
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+            with torch.cuda.device(self.device):
+                self._owned = self.alloc(self.nbytes)
+                handle = ctypes.create_string_buffer(64)
+                _lib.check(lib.tf_peer_export(self._owned, handle), "peer export")
+                handles = [None] * self.world
+                dist.all_gather_object(handles, handle.raw, group=group)
+                self.bufs = []
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        self.bufs.append(self._owned)
+                        continue
+                    ptr = ctypes.c_void_p()
+                    _lib.check(lib.tf_peer_open(h, ctypes.byref(ptr)), f"peer open (rank {r})")
+                    self._opened.append(ptr.value)
+                    self.bufs.append(ptr.value)
+                dist.barrier(group)                            # every buffer is mapped before anyone signals
+        self._table = (ctypes.c_void_p * self.world)(*self.bufs)
+        self._mine = torch.as_tensor(_Raw(self.bufs[self.rank], self.nbytes), device=self.device)
+
+    @staticmethod
+    def layout(elements: int) -> tuple[int, int, int, int]:
+        """Bytes of the flags, offsets of the partial and of the result, bytes of a buffer for ``elements`` fp32 values."""
+
+        flags = int(_lib.lib().tf_peer_flag_bytes())
+        room = (-(-elements * 4 // 256)) * 256
+        return flags, flags, flags + room, flags + 2 * room
+
+    @staticmethod
+    def alloc(nbytes: int) -> int:
+        ptr = ctypes.c_void_p()
+        _lib.check(_lib.lib().tf_peer_alloc(nbytes, ctypes.byref(ptr)), "peer alloc")
+        return ptr.value
+
+    def partial(self, shape, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """Where this rank's partial goes: a view of its buffer for the producer to write into."""
+
+        n = int(torch.Size(shape).numel())
+        if n > self.elements or dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("PeerReducer.partial: fp32 or bf16, no more elements than the reducer was made for")
+        return self._mine[self.part_off:self.part_off + n * dtype.itemsize].view(dtype).view(shape)
+
+    def reduce(self, part: torch.Tensor, dtype: torch.dtype = torch.bfloat16, *, polls: int = 0, grid_cap: int = 0) -> torch.Tensor:
+        """Sum of every rank's ``part`` (a tensor from ``partial``; anything else is copied in first)."""
+
+        n = part.numel()
+        home = self.partial(part.shape, part.dtype)
+        if part.data_ptr() != home.data_ptr() or not part.is_contiguous():
+            home.copy_(part)
+        two_shot = n * part.element_size() >= self.two_shot_from and n % (8 * self.world) == 0
+        _lib.check(_lib.lib().tf_peer_reduce(self._table, self.rank, self.world, self.part_off, self.out_off, n,
+                                             int(part.dtype == torch.bfloat16), int(dtype == torch.float32), int(two_shot),
+                                             polls, grid_cap, _lib.stream_of(home)), "peer reduce")
+        return self._mine[self.out_off:self.out_off + n * dtype.itemsize].view(dtype).view(part.shape)
+
+    def close(self) -> None:
+        lib = _lib.lib()
+        torch.cuda.synchronize(self.device)
+        if self._owned and dist.is_initialized():
+            dist.barrier(self.group)                           # no rank unmaps while another may still read
+        for ptr in self._opened:
+            lib.tf_peer_close(ptr)
+        self._opened = []
+        if self._owned:
+            if dist.is_initialized():
+                dist.barrier(self.group)
+            lib.tf_peer_free(self._owned)
+            self._owned = 0
+
+
 def shard_experts(raw_up: list[tuple], raw_down: tuple, rank: int, world: int) -> tuple[list[tuple], tuple, int]:
     """Rank's share of the expert tables: experts [rank * E / world, (rank + 1) * E / world)."""
 
@@ -66,7 +164,7 @@ class ExpertParallelMoE:
     top_k: int
     first: int                      # global id of local expert 0
     total: int                      # experts in the whole layer
-    has_shared_row: bool = False    # router carries a shared-expert gate row (slot k), run elsewhere
+    has_shared_row: bool = False    # router carries a shared-expert gate row after the experts' (not read here)
 
     def buffers(self, rows: int, device, *, prefill: bool = False) -> moe.MoEBuffers:
         class _Cfg:
@@ -74,29 +172,25 @@ class ExpertParallelMoE:
             moe_intermediate_size, hidden_size = self.experts.width, self.experts.dims
         return moe.MoEBuffers(rows, _Cfg, device, prefill=prefill, table_experts=self.experts.count)
 
-    def partial(self, x: torch.Tensor, buf: moe.MoEBuffers) -> torch.Tensor:
+    def partial(self, x: torch.Tensor, buf: moe.MoEBuffers, out: torch.Tensor | None = None) -> torch.Tensor:
         """This rank's contribution [R, D] bf16: its experts' slots combined, the others weighted zero."""
 
         rows = x.shape[0]
         logits = buf.logits[:rows]
         form = buf.plan.prefill                                # prompt passes take the tensor-core router, as moe.moe does
-        if self.has_shared_row:
-            moe.router(x, self.router, logits, prefill=form)
-        else:
-            moe.router(x, self.router, logits[:, :self.total], prefill=form)
-            logits[:, self.total].zero_()
-        moe.select_rows(logits, buf, self.top_k, self.total)
-        pick, wts = buf.pick[:rows], buf.wts[:rows]
-        pick -= self.first                                                   # local ids; others fall outside the table
-        local = (pick >= 0) & (pick < self.experts.count)
-        wts.mul_(local)
-        grouped.route(pick, buf.plan)
+        moe.router(x, self.router[:self.total], logits[:, :self.total], prefill=form)
+        moe.select_local_rows(logits, buf, self.top_k, self.total, self.first, self.experts.count)
+        wts = buf.wts[:rows]
+        grouped.route(buf.pick[:rows], buf.plan)
         grouped.gate_up(x, self.experts, buf.plan, buf.act.view(-1, self.experts.width), rows)
         grouped.down(buf.act.view(-1, self.experts.width), self.experts, buf.plan, buf.y.view(-1, self.experts.dims), rows)
-        return moe.combine(buf.y[:rows], wts)
+        return moe.combine(buf.y[:rows], wts, out)
 
-    def run(self, x: torch.Tensor, buf: moe.MoEBuffers, group=None) -> torch.Tensor:
-        return ordered_all_reduce(self.partial(x, buf), group)
+    def run(self, x: torch.Tensor, buf: moe.MoEBuffers, group=None, reducer: PeerReducer | None = None) -> torch.Tensor:
+        if reducer is None:
+            return ordered_all_reduce(self.partial(x, buf), group)
+        part = reducer.partial((x.shape[0], self.experts.dims))
+        return reducer.reduce(self.partial(x, buf, out=part))
 
 
 @dataclass
@@ -110,10 +204,15 @@ class RowParallelLinear:
         part = distributed.split_input(q, rank, world)
         return RowParallelLinear(qmm.pack(part.weight, part.scales, part.biases, part.gs, bits=part.bits))
 
-    def partial(self, x_local: torch.Tensor, *, f32: bool = False) -> torch.Tensor:
+    def partial(self, x_local: torch.Tensor, *, f32: bool = True) -> torch.Tensor:
+        """This rank's share of the sums: fp32, unrounded (``f32=False`` rounds the share to bf16 first: half the
+        bytes on the wire, two roundings instead of one, not what the reference does)."""
+
         return qmm.matmul(x_local, self.q, f32=f32)
 
-    def forward(self, x_local: torch.Tensor, group=None, *, f32: bool = False) -> torch.Tensor:
+    def forward(self, x_local: torch.Tensor, group=None, *, f32: bool = True) -> torch.Tensor:
+        """fp32 partials summed in rank order and rounded once (families/qwen3_5/cuda/distributed.py:249-284)."""
+
         return ordered_all_reduce(self.partial(x_local, f32=f32), group)
 
 

@@ -12,7 +12,9 @@ import torch.distributed as dist
 
 from .... import _lib
 from ....cuda.kernels import affine
-from .weights import QLinear
+from dataclasses import dataclass, replace
+
+from .weights import GDN, Attention, Config, Layer, QLinear, Weights
 
 
 def _rank(rank: int, world_size: int) -> None:
@@ -124,3 +126,82 @@ def gather_rank_partials(local: torch.Tensor, group=None, dtype: torch.dtype = t
     gathered = torch.empty((world, *local.shape), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(gathered.view(-1), local.view(-1), group=group)
     return _ordered_sum(gathered, dtype)
+
+
+@dataclass
+class LayerShard:
+    """One rank's share of a layer and the head counts it holds (families/qwen3_5/cuda/distributed.py:90-99)."""
+
+    layer: Layer
+    rank: int
+    world_size: int
+    q_heads: int
+    kv_heads: int
+    k_heads: int
+    v_heads: int
+
+
+def split_layer(layer: Layer, cfg: Config, rank: int, world_size: int = 2) -> LayerShard:
+    """One rank's share of a layer, cut along heads and the MLP width without touching a checkpoint word
+    (families/qwen3_5/cuda/distributed.py:101-133): q/k/v, gate/up and the GDN inputs by whole output rows (whole
+    heads), o, down and the GDN output by whole groups of inputs; the per-head GDN tensors follow their heads."""
+
+    _rank(rank, world_size)
+    counts = [cfg.intermediate] + ([cfg.heads, cfg.kv_heads] if layer.attn is not None else []) + \
+             ([cfg.k_heads, cfg.v_heads] if layer.gdn is not None else [])
+    if any(v % world_size for v in counts):
+        raise ValueError("head count and MLP width must be divisible by rank count")
+    attn = None
+    if layer.attn is not None:
+        a = layer.attn
+        attn = Attention(q=split_output(a.q, rank, world_size, block=2 * cfg.head_dim),
+                         k=split_output(a.k, rank, world_size, block=cfg.head_dim),
+                         v=split_output(a.v, rank, world_size, block=cfg.head_dim),
+                         o=split_input(a.o, rank, world_size), q_norm=a.q_norm, k_norm=a.k_norm)
+    gdn = None
+    if layer.gdn is not None:
+        g = layer.gdn
+        kd, vd = cfg.k_heads * cfg.dk, cfg.v_heads * cfg.dv
+        rows = output_rows(g.qkv.n, rank, world_size, segments=(kd, kd, vd), device=g.conv.device)
+        vh = cfg.v_heads // world_size
+        lo, hi = rank * vh, (rank + 1) * vh
+        gdn = GDN(qkv=split_output(g.qkv, rank, world_size, segments=(kd, kd, vd)),
+                  z=split_output(g.z, rank, world_size, block=cfg.dv),
+                  b=split_output(g.b, rank, world_size), a=split_output(g.a, rank, world_size),
+                  out=split_input(g.out, rank, world_size),
+                  conv=g.conv.index_select(0, rows).contiguous(),
+                  A_log=g.A_log[lo:hi].contiguous(), dt_bias=g.dt_bias[lo:hi].contiguous(), norm=g.norm)
+    cut = lambda q, fn: fn(q, rank, world_size) if q is not None else None
+    local = Layer(linear=layer.linear, input_norm=layer.input_norm, post_norm=layer.post_norm, gdn=gdn, attn=attn,
+                  gate=cut(layer.gate, split_output), up=cut(layer.up, split_output), down=cut(layer.down, split_input),
+                  moe=layer.moe)
+    return LayerShard(local, rank, world_size, cfg.heads // world_size, cfg.kv_heads // world_size,
+                      cfg.k_heads // world_size, cfg.v_heads // world_size)
+
+
+def split_weights(w: Weights, rank: int, world_size: int = 2, *, tiled: bool = False, fuse: bool = False,
+                  split_head: bool = False) -> Weights:
+    """One rank's share of a model's projections, cut in the stored layout and only then (optionally) tiled
+    (families/qwen3_5/cuda/distributed.py:136-165); ``split_head`` also cuts the head's vocabulary rows (every rank then
+    holds whole dot products of its rows, so logits keep their bits and candidates can be merged)."""
+
+    _rank(rank, world_size)
+    c = w.config
+    local_cfg = replace(c, heads=c.heads // world_size, kv_heads=c.kv_heads // world_size, k_heads=c.k_heads // world_size,
+                        v_heads=c.v_heads // world_size, intermediate=c.intermediate // world_size)
+    layers = []
+    for layer in w.layers:
+        local = split_layer(layer, c, rank, world_size).layer
+        if tiled:
+            from .qmm_fast import stack_small, tile_layer
+
+            if fuse:
+                stack_small(local)
+            tile_layer(local)
+        layers.append(local)
+    head = split_output(w.head, rank, world_size) if split_head and w.head is not None else w.head
+    if tiled and head is not None:
+        from .qmm_fast import tile
+
+        head = tile(head)
+    return Weights(local_cfg, w.embed, layers, w.norm, head, w.inv_freq)

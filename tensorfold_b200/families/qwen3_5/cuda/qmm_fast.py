@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ....cuda.kernels import affine, qmm as shared
-from .weights import QLinear
+from .weights import QLinear, Weights
 
 
 def tile(q: QLinear) -> QLinear:
@@ -78,3 +78,50 @@ def stack(parts: list[QLinear]) -> QLinear:
         raise ValueError("stacked projections must share an affine format and input width")
     return QLinear(torch.cat([q.weight for q in parts]).contiguous(), torch.cat([q.scales for q in parts]).contiguous(),
                    torch.cat([q.biases for q in parts]).contiguous(), gs=parts[0].gs, bits=parts[0].bits)
+
+
+def _stackable(parts: list[QLinear]) -> bool:
+    return (all(q is not None and q.layout == "mlx" for q in parts)
+            and len({(q.bits, q.gs, q.k, q.scales.dtype, q.biases.dtype) for q in parts}) == 1)
+
+
+def stack_small(layer) -> None:
+    """[z | b | a] and [k | v] as one projection each (families/qwen3_5/cuda/qmm_fast.py:89-95): the gates and k/v are too
+    narrow to fill the GPU alone.  Stacking changes the K split, hence the bits: a load-time decision.  (With
+    ``shared.matmul_set`` the same projections share a launch WITHOUT changing bits; stacking stays for engines that
+    want one output tensor.)"""
+
+    if layer.gdn is not None and layer.gdn.zba is None and _stackable([layer.gdn.z, layer.gdn.b, layer.gdn.a]):
+        layer.gdn.zba = stack([layer.gdn.z, layer.gdn.b, layer.gdn.a])
+    if layer.attn is not None and layer.attn.kv is None and _stackable([layer.attn.k, layer.attn.v]):
+        layer.attn.kv = stack([layer.attn.k, layer.attn.v])
+
+
+PROJECTIONS = ((None, ("gate", "up", "down")), ("gdn", ("qkv", "z", "b", "a", "out", "zba")), ("attn", ("q", "k", "v", "o", "kv")))
+
+
+def tile_layer(layer) -> None:
+    """Tile every projection a layer holds, in place (stacked ones included)."""
+
+    for owner_name, names in PROJECTIONS:
+        owner = layer if owner_name is None else getattr(layer, owner_name)
+        if owner is None:
+            continue
+        for name in names:
+            q = getattr(owner, name, None)
+            if q is not None:
+                setattr(owner, name, tile(q))
+
+
+def prepare(w: Weights, *, fuse: bool = False) -> None:
+    """Pack every projection and the head in place (families/qwen3_5/cuda/qmm_fast.py:98-115); ``fuse`` stacks the
+    narrow projections first, which changes K splits and bits, so every run of a model must share it."""
+
+    for layer in w.layers:
+        if fuse:
+            stack_small(layer)
+        tile_layer(layer)
+    if w.head is not None:
+        w.head = tile(w.head)
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()

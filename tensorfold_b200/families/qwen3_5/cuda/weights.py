@@ -3,8 +3,9 @@
 
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from functools import cached_property
+from typing import Any
 
 import torch
 
@@ -39,3 +40,69 @@ class QLinear:
             return True
         return (self.bits, self.gs) == (4, 64) and self.layout != "dense" and all(
             t.dtype == torch.bfloat16 for t in (self.scales, self.biases))
+
+
+# The layer containers the sharding and packing helpers walk (families/qwen3_5/cuda/weights.py:107-215 of the
+# reference).  Only the fields those helpers touch are kept: the projections, and the per-head tensors that are cut
+# with them.  Attention, the GDN recurrence and the norms themselves are outside this library.
+
+@dataclass
+class Config:
+    hidden: int
+    intermediate: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    k_heads: int = 0          # GDN key heads
+    v_heads: int = 0          # GDN value heads
+    dk: int = 0
+    dv: int = 0
+    vocab: int = 0
+
+
+@dataclass
+class GDN:
+    qkv: QLinear
+    z: QLinear
+    b: QLinear
+    a: QLinear
+    out: QLinear
+    conv: torch.Tensor        # (conv_dim, kernel)
+    A_log: torch.Tensor       # (Hv,)
+    dt_bias: torch.Tensor     # (Hv,)
+    norm: torch.Tensor | None = None
+    zba: QLinear | None = None  # [z | b | a] stacked into one projection (``qmm_fast.stack``)
+
+
+@dataclass
+class Attention:
+    q: QLinear                # (heads * head_dim * 2, hidden): [q_h | gate_h] per head
+    k: QLinear
+    v: QLinear
+    o: QLinear
+    q_norm: torch.Tensor | None = None
+    k_norm: torch.Tensor | None = None
+    kv: QLinear | None = None   # [k | v] stacked
+
+
+@dataclass
+class Layer:
+    linear: bool = False
+    input_norm: torch.Tensor | None = None
+    post_norm: torch.Tensor | None = None
+    gdn: GDN | None = None
+    attn: Attention | None = None
+    gate: QLinear | None = None
+    up: QLinear | None = None
+    down: QLinear | None = None
+    moe: Any = None
+
+
+@dataclass
+class Weights:
+    config: Config
+    embed: Any
+    layers: list = field(default_factory=list)
+    norm: torch.Tensor | None = None
+    head: Any = None
+    inv_freq: torch.Tensor | None = None

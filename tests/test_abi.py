@@ -60,3 +60,29 @@ def test_refused_arguments_raise_before_any_launch():
         qmm.matmul(x, q)                                 # CPU tensors: no CPU implementation
     with pytest.raises(ValueError):
         qmm.pack(torch.zeros((4, 16), dtype=torch.int32), torch.zeros((4, 2)), torch.zeros((4, 2)), 64)
+
+
+def test_c_abi_refuses_null_and_short_buffers_without_launching():
+    """tf_qmm is called with made-up (non-null, aligned) addresses and must refuse before touching any of them: out missing
+    when the sum is written to it, part missing when the slices leave the kernel, out rows shorter than n."""
+
+    lib = _lib.lib()
+    x, w, out, part = 0x10000, 0x20000, 0x30000, 0x40000
+
+    def call(**kw):
+        a = dict(x=x, ldx=128, m=4, xs=None, tiled=w, sb=0, n=64, k=128, bits=4, gs=64, sk=1, out=out, ldo=64, f32=0, part=None,
+                 reduce=1, pdl=0)
+        a.update(kw)
+        return lib.tf_qmm(a["x"], a["ldx"], a["m"], a["xs"], a["tiled"], a["sb"], a["n"], a["k"], a["bits"], a["gs"], a["sk"],
+                          a["out"], a["ldo"], a["f32"], a["part"], a["reduce"], a["pdl"], None)
+
+    assert call(out=None) < 0                                    # one slice: the result goes to out
+    assert call(sk=2, out=None) < 0                              # slices summed on chip: out again
+    assert call(sk=2, reduce=0, part=None) < 0                   # slices leave the kernel: part
+    assert call(k=64 * 32, ldx=64 * 32, sk=16, part=None) < 0    # more slices than a cluster holds: part
+    assert call(ldo=32) < 0 and call(sb=-1) < 0
+    assert call(x=None) < 0 and call(tiled=None) < 0 and call(x=x + 2) < 0
+    assert call(sk=3) < 0                                        # two groups do not make three slices
+    assert b"tf_qmm" in lib.tf_last_error()
+    # with everything in place the next refusal is the missing per-device set-up (no GPU here): still no launch
+    assert call() != 0

@@ -79,3 +79,28 @@ def test_expert_parallel_partials_sum_to_the_layer(world, prefill):
         one = tp.ExpertParallelMoE(wr.to(DEV), experts.make([dev(gate), dev(up)], dev(down), gs), top_k, 0, e)
         whole = one.partial(x, one.buffers(rows, DEV)).float()
         assert (got.float() - whole).abs().max() <= 2 ** -6 * whole.abs().max()
+
+
+def test_forward_hands_unrounded_partials_to_the_reduction(monkeypatch):
+    """``RowParallelLinear.forward`` with its defaults: the partial that meets the other ranks' is fp32 and the result is
+    the rank-ordered sum rounded once, the bits ``sum_rank_partials`` gives for the fp32 partials."""
+
+    n, k, gs, world = 512, 4096, 64, 2
+    q = QLinear(*to_dev(*synthetic.affine_weight(n, k, 4, gs, seed=11)), gs=gs)
+    x = synthetic.activations(9, k, 3).to(DEV)
+    lins = [tp.RowParallelLinear.shard(q, r, world) for r in range(world)]
+    xs = [distributed.local_input(x, r, world, group_size=gs) for r in range(world)]
+    theirs = lins[1].partial(xs[1])
+    assert theirs.dtype == torch.float32
+    seen = []
+
+    def two_ranks(local, group=None, dtype=torch.bfloat16):      # rank 0's view of the reduction: its partial, then rank 1's
+        seen.append(local)
+        return distributed.sum_rank_partials([local, theirs], dtype)
+
+    monkeypatch.setattr(tp, "ordered_all_reduce", two_ranks)
+    got = lins[0].forward(xs[0])
+    assert seen[0].dtype == torch.float32
+    assert torch.equal(got, distributed.sum_rank_partials([lins[0].partial(xs[0], f32=True), theirs]))
+    rounded = distributed.sum_rank_partials([lins[0].partial(xs[0], f32=False), lins[1].partial(xs[1], f32=False)])
+    assert got.dtype == rounded.dtype == torch.bfloat16        # the bf16-partial form stays an explicit option
