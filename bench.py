@@ -158,8 +158,8 @@ def layer_bytes_total() -> int:
 
 
 def reference_torch_baseline(rows: int) -> dict:
-    """The reference's own CPU-runnable code for this op, where its checkout can be imported (TENSORFOLD_REFERENCE, or
-    /root/reference when present): ``dequantize`` (families/qwen3_5/cuda/qmm.py:132-149) then ``x.float() @ w.T``, timed
+    """The reference's own CPU-runnable code for this op, where its checkout can be imported (the directory TENSORFOLD_REFERENCE
+    names): ``dequantize`` (families/qwen3_5/cuda/qmm.py:132-149) then ``x.float() @ w.T``, timed
     both ways on one projection (q_proj), all host threads.  Also records whether MLX (the reference's named CPU
     baseline, ``mx.quantized_matmul`` on mx.cpu) can be imported on this box."""
 
@@ -171,7 +171,7 @@ def reference_torch_baseline(rows: int) -> dict:
         out["mlx"] = "importable"
     except Exception as exc:                                 # noqa: BLE001
         out["mlx"] = f"MLX unavailable on this box ({type(exc).__name__})"
-    root = os.environ.get("TENSORFOLD_REFERENCE") or ("/root/reference" if os.path.isdir("/root/reference/src/tensorfold") else "")
+    root = os.environ.get("TENSORFOLD_REFERENCE", "")
     if not root:
         out["reference_torch"] = "reference checkout not present on this box"
         return out
@@ -530,6 +530,32 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
         torch.cuda.synchronize()
         return biggest(a.elapsed_time(b) * 1e3 / iters)
 
+    def graph_timed(fn, blocks=10, replays=5) -> float:
+        side = side_stream()
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(blocks):
+                fn()
+        graph.replay()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(replays):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us = biggest(a.elapsed_time(b) * 1e3 / (blocks * replays))
+        del graph
+        return us
+
     out = {}
     for rows in rows_list:
         prefill = rows > 128
@@ -544,10 +570,12 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
             project(attn, o_proj, out=part)
             return layer.run(reducer.reduce(part), buf, reducer=reducer)
 
-        entry = {"us": timed(lambda: block(red)), "timing": "eager launches, CUDA events, max over ranks",
+        entry = {"us": graph_timed(lambda: block(red)), "us_eager": timed(lambda: block(red)),
+                 "timing": "us: ten blocks replayed from one CUDA graph; us_eager: eager launches; CUDA events, max over ranks",
                  "reduce": "peer memory, one launch" if red is not None else "none (one rank)"}
         if red is not None:
-            entry["us_collectives"] = timed(lambda: block(None))
+            entry["us_collectives"] = graph_timed(lambda: block(None))
+            entry["us_collectives_eager"] = timed(lambda: block(None))
 
         # the same block step by step (an event after every step; the sum exceeds the block by the events' gaps)
         state = {}

@@ -217,12 +217,19 @@ int tf_sum_ranks(const void* parts, int world, int64_t total, int parts_bf16, vo
  * then sums the `total` elements at byte offset part_off of EVERY rank's buffer (fp32, or bf16 with parts_bf16) in
  * rank order, fp32 adds, one rounding, into byte offset out_off of this rank's buffer: the bits of tf_sum_ranks over
  * the gathered partials.  Every rank calls it once per reduction with the same arguments, after the kernel that wrote
- * its partial, on the same stream.  two_shot: a rank sums only its 1/world share and stores it into every rank's
- * result (less NVLink traffic for large partials; total a multiple of 8 * world); otherwise every rank reads all
- * partials (total a multiple of 8).  polls: limit of each wait on a peer (0: about a second); a wait that runs out
- * sets device error 4 (tf_device_error) and the kernel returns; the buffers must then be freed and made anew.
- * grid_cap > 0 bounds the blocks (testing).  No counterpart in the reference, which reduces its two ranks with an
- * all-gather and a torch add (families/qwen3_5/cuda/distributed.py:249-284). */
+ * its partial, on the same stream.  mode:
+ *   2  flagged words, for small partials: a rank stores its partial as {data, epoch} words into a slot of every other
+ *      rank's buffer and collects the others' from its own; no barrier between the ranks.  The 2 * world slots of
+ *      ll_slot >= 2 * partial bytes each start at ll_off, past partial and result.  total a multiple of 8.
+ *   1  shares, for large ones: after a barrier a rank reads its 1/world share of every partial, stores the sum into
+ *      every rank's result, and a second barrier ends the call.  total a multiple of 8 * world.
+ *   0  as 1 but every rank reads all partials whole (total a multiple of 8).
+ *   3, 4  the storing and the collecting half of mode 2 as launches of their own (a test driving all ranks from one
+ *      process runs every rank's 3, then every rank's 4).
+ * polls: limit of each wait on a peer (0: about a second); a wait that runs out sets device error 4 (tf_device_error)
+ * and the kernel returns; the buffers must then be freed and made anew.  grid_cap > 0 bounds the blocks (testing).
+ * No counterpart in the reference, which reduces its two ranks with an all-gather and a torch add
+ * (families/qwen3_5/cuda/distributed.py:249-284). */
 size_t tf_peer_flag_bytes(void);
 int tf_peer_alloc(size_t bytes, void** ptr);
 int tf_peer_free(void* ptr);
@@ -230,7 +237,7 @@ int tf_peer_export(void* ptr, void* handle64);
 int tf_peer_open(const void* handle64, void** ptr);
 int tf_peer_close(void* ptr);
 int tf_peer_reduce(void* const* bufs, int rank, int world, size_t part_off, size_t out_off, int64_t total, int parts_bf16,
-                   int out_f32, int two_shot, unsigned polls, int grid_cap, void* stream);
+                   int out_f32, int mode, size_t ll_off, size_t ll_slot, unsigned polls, int grid_cap, void* stream);
 
 /* Glue that feeds the matmuls (rows contiguous, bf16, 16-byte aligned; d a multiple of gs; one block a row, so a row's
  * bits do not depend on the row count).

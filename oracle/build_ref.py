@@ -10,6 +10,7 @@
 from __future__ import annotations
 
 import ast
+import os
 import shutil
 import subprocess
 import sys
@@ -56,9 +57,19 @@ def build_code_at(reference: str | Path) -> Path | None:
     return lib
 
 
-def build(reference: str | Path = "/root/reference") -> dict:
+def find_reference() -> str:
+    """The reference checkout: the directory TENSORFOLD_REFERENCE names, else a ``reference`` directory beside this
+    repository; empty when neither exists."""
+
+    named = os.environ.get("TENSORFOLD_REFERENCE", "")
+    beside = HERE.resolve().parent.parent / "reference"
+    return named or (str(beside) if (beside / "src" / "tensorfold").is_dir() else "")
+
+
+def build(reference: str | Path | None = None) -> dict:
+    reference = reference or find_reference()
     return {"port": build_port(), "code_at": build_code_at(reference)}
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None))

@@ -52,7 +52,8 @@ SIGNATURES = {
     "tf_peer_export": (_i32, (_vp, _vp)),
     "tf_peer_open": (_i32, (_vp, _vp)),
     "tf_peer_close": (_i32, (_vp,)),
-    "tf_peer_reduce": (_i32, (_vp, _i32, _i32, ctypes.c_size_t, ctypes.c_size_t, _i64, _i32, _i32, _i32, ctypes.c_uint, _i32, _vp)),
+    "tf_peer_reduce": (_i32, (_vp, _i32, _i32, ctypes.c_size_t, ctypes.c_size_t, _i64, _i32, _i32, _i32, ctypes.c_size_t,
+                              ctypes.c_size_t, ctypes.c_uint, _i32, _vp)),
     "tf_moe_topk_local": (_i32, (_vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp)),
     "tf_moe_combine": (_i32, (_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp)),
     "tf_affine_rows": (_i32, (_vp, _i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp)),

@@ -1,21 +1,26 @@
 // Rank-ordered all-reduce of partial sums over peer memory (NVLink / NVSwitch), one launch a rank: the ranks' buffers are
-// mapped into every process, a rank reads the partials of all ranks with plain peer loads, adds them in rank order in
-// fp32 ((p0 + p1) + p2 ...), rounds once and writes the result.  Generalises the two-rank
-// rank0.float() + rank1.float() of families/qwen3_5/cuda/distributed.py:249-284 (an all-gather and an add there).
+// mapped into every process; the partials of all ranks are added in rank order in fp32 ((p0 + p1) + p2 ...), rounded
+// once, and every rank ends with the same bits.  Generalises the two-rank rank0.float() + rank1.float() of
+// families/qwen3_5/cuda/distributed.py:249-284 (an all-gather and an add there).  Three forms:
 //
-// Each rank's buffer starts with a page of 32-bit flags, 128 bytes apart:
-//   ready[r]  how many reductions rank r has announced its partial for
-//   done[r]   how many reductions rank r has finished reading and writing
-//   calls     reductions this rank has completed (the kernel reads it at entry and bumps it at exit, so launches
-//             replayed from a CUDA graph keep counting)
-//   arrive    blocks of the running launch that have finished their share
-// A launch: announce `ready` on every rank, wait for every rank's `ready`, reduce, count the blocks in, the last block
-// announces `done` on every rank, wait for every rank's `done` (all shares have landed here, and no rank still reads this
-// rank's partial), bump `calls`.  Every wait has a poll limit; a wait that runs out sets ERR_WAIT_PEER in the device error
-// word, the kernel skips its remaining waits and returns, and the host sees the error at its next check.
+//   flagged words (small partials)  a rank stores its partial into a slot of every other rank's buffer as 8-byte
+//       {data, epoch} words (16-byte stores of two such words; each half carries its own flag), then polls the slots
+//       of its own buffer until every word shows this call's epoch, and adds.  No barrier, no fence: one trip over the
+//       links.  Slots alternate with the parity of the epoch: a slot is rewritten two calls later, which the writer
+//       can only reach after this rank has sent its next partial, that is, after it has finished reading this one.
+//   shares (large partials)  ranks tell one another that their partials are in place, a rank reads its 1/world share of
+//       every partial with plain peer loads, adds, stores the sum into every rank's result, and the ranks tell one
+//       another that they are done (all shares have landed; nobody still reads this rank's partial).
+//   all (testing, and totals that do not split)  as shares, but every rank reads every partial whole.
 //
-// All blocks of a launch must be resident at once (they wait for one another through `arrive`): the grid is bounded by
-// the occupancy the runtime reports for the kernel.
+// Each rank's buffer starts with a page of 32-bit flags, 128 bytes apart: ready[r] and done[r] (how many reductions of
+// the share forms rank r has announced / finished), the calls completed in the share forms and in the flagged form (a
+// launch reads its epoch there at entry and the last block bumps it at exit, so launches replayed from a CUDA graph keep
+// counting), and a count of the blocks of the running launch that have finished.  Every wait has a poll limit; a wait
+// that runs out sets ERR_WAIT_PEER in the device error word, the kernel skips its remaining waits and returns.
+//
+// In the share forms all blocks of a launch must be resident at once (the last one to finish signals for all): the grid
+// is bounded by the occupancy the runtime reports.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -33,19 +38,23 @@ int* device_error_word();
 namespace {
 
 constexpr int PEER_MAX = 8;
-constexpr int PEER_THREADS = 512;
+constexpr int PEER_THREADS = 512;              // share forms
+constexpr int LL_THREADS = 256;                // flagged words
 constexpr int FLAG_WORDS = 32;                 // flags sit 128 bytes apart
-constexpr int FLAG_READY = 0, FLAG_DONE = PEER_MAX, FLAG_CALLS = 2 * PEER_MAX, FLAG_ARRIVE = 2 * PEER_MAX + 1;
+constexpr int FLAG_READY = 0, FLAG_DONE = PEER_MAX, FLAG_CALLS = 2 * PEER_MAX, FLAG_ARRIVE = 2 * PEER_MAX + 1,
+              FLAG_LL_CALLS = 2 * PEER_MAX + 2, FLAG_LL_ARRIVE = 2 * PEER_MAX + 3;
 constexpr size_t FLAG_BYTES = 4096;
-static_assert((FLAG_ARRIVE + 1) * FLAG_WORDS * 4 <= FLAG_BYTES, "the flags fit their page");
+static_assert((FLAG_LL_ARRIVE + 1) * FLAG_WORDS * 4 <= FLAG_BYTES, "the flags fit their page");
+enum Mode : int { MODE_ALL = 0, MODE_SHARES = 1, MODE_FLAGGED = 2, MODE_FLAGGED_PUSH = 3, MODE_FLAGGED_PULL = 4 };
 
 struct PeerArgs {
   char* buf[PEER_MAX];                         // every rank's buffer as this process sees it (buf[rank] is local)
   char* mine;                                  // buf[rank]
   int rank, world;
   size_t part_off, out_off;                    // byte offsets of the partial and of the result inside every buffer
+  size_t ll_off, ll_slot;                      // flagged words: 2 * world slots of ll_slot bytes from ll_off
   int64_t total;                               // elements of the partial
-  int parts_bf16, out_f32, two_shot;
+  int parts_bf16, out_f32, mode;
   uint32_t polls;                              // limit of every wait
   int* err;
 };
@@ -68,8 +77,17 @@ __device__ __forceinline__ uint4 ld_peer16(const void* p) {
 __device__ __forceinline__ void st_peer16(void* p, const uint4& v) {
   asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+__device__ __forceinline__ uint4 ld_volatile16(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile16(void* p, const uint4& v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 
-// Waits until *p has reached `target` (counters only grow; the comparison survives their wrap).
+// Waits until *p has reached `target` (counters only grow; the comparison survives their wrap).  (Polling with relaxed
+// loads and one fence after the last measured slower than acquiring loads: 42 us against 22 us a call on two GPUs.)
 __device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t target, uint32_t polls) {
   for (uint32_t i = 0; i < polls; ++i) {
     if (static_cast<int32_t>(ld_acquire_sys(p) - target) >= 0) return true;
@@ -154,7 +172,7 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_reduce_kernel(const PeerArg
   if (!lost) {
     const int64_t step = static_cast<int64_t>(gridDim.x) * PEER_THREADS * 8;
     const int64_t lane0 = (static_cast<int64_t>(blockIdx.x) * PEER_THREADS + tid) * 8;
-    if (a.two_shot) {                          // this rank sums its share and hands it to every rank
+    if (a.mode == MODE_SHARES) {               // this rank sums its share and hands it to every rank
       const int64_t share = a.total / WORLD, base = share * a.rank;
       for (int64_t i = lane0; i < share; i += step) {
         float acc[8];
@@ -190,17 +208,125 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_reduce_kernel(const PeerArg
   }
 }
 
+// Flagged words.  A thread owns quads of four 4-byte words of the partial (four fp32 values, or eight bf16): it stores
+// them into its slot on every other rank, then collects the same quad from every other rank's slot here.
+template <int WORLD, bool BF16>
+__global__ void __launch_bounds__(LL_THREADS) peer_reduce_flagged_kernel(const PeerArgs a) {
+  __shared__ uint32_t s_epoch;
+  const int tid = threadIdx.x;
+  char* mine = a.mine;
+  if (tid == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_LL_CALLS)) + 1;
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const bool push = a.mode != MODE_FLAGGED_PULL, pull = a.mode != MODE_FLAGGED_PUSH;
+  const int64_t quads = (BF16 ? a.total / 2 : a.total) / 4;
+  const size_t slots = a.ll_off + static_cast<size_t>(epoch & 1) * WORLD * a.ll_slot;
+  bool lost = false;
+  for (int64_t q = static_cast<int64_t>(blockIdx.x) * LL_THREADS + tid; q < quads; q += static_cast<int64_t>(gridDim.x) * LL_THREADS) {
+    const uint4 v = *reinterpret_cast<const uint4*>(mine + a.part_off + q * 16);
+    if (push) {
+      const uint4 lo = make_uint4(v.x, epoch, v.y, epoch), hi = make_uint4(v.z, epoch, v.w, epoch);
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r)
+        if (r != a.rank) {
+          char* dst = a.buf[r] + slots + a.rank * a.ll_slot + q * 32;
+          st_volatile16(dst, lo);
+          st_volatile16(dst + 16, hi);
+        }
+    }
+    if (!pull || lost) continue;
+    uint4 got[WORLD][2];
+    bool ok = false;
+    for (uint32_t i = 0; i < a.polls && !ok; ++i) {
+      ok = true;
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r)
+        if (r != a.rank) {
+          const char* src = mine + slots + r * a.ll_slot + q * 32;
+          got[r][0] = ld_volatile16(src);
+          got[r][1] = ld_volatile16(src + 16);
+          ok &= got[r][0].y == epoch && got[r][0].w == epoch && got[r][1].y == epoch && got[r][1].w == epoch;
+        }
+      if (!ok && i >= 64) __nanosleep(i < 512 ? 50 : 500);
+    }
+    if (!ok) {
+      lost = true;
+      continue;
+    }
+    float acc[BF16 ? 8 : 4];
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) {
+      const bool own = r == a.rank;
+      const uint32_t w[4] = {own ? v.x : got[r][0].x, own ? v.y : got[r][0].z, own ? v.z : got[r][1].x, own ? v.w : got[r][1].z};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if constexpr (BF16) {
+          const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xFFFF0000u);
+          acc[2 * j] = r == 0 ? lo : acc[2 * j] + lo;
+          acc[2 * j + 1] = r == 0 ? hi : acc[2 * j + 1] + hi;
+        } else {
+          acc[j] = r == 0 ? __uint_as_float(w[j]) : acc[j] + __uint_as_float(w[j]);
+        }
+      }
+    }
+    constexpr int VALUES = BF16 ? 8 : 4;
+    if (a.out_f32) {
+      float4* o = reinterpret_cast<float4*>(mine + a.out_off + q * VALUES * 4);
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      if constexpr (BF16) o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      uint32_t u[VALUES / 2];
+#pragma unroll
+      for (int j = 0; j < VALUES / 2; ++j) {
+        const __nv_bfloat162 t = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        u[j] = *reinterpret_cast<const uint32_t*>(&t);
+      }
+      if constexpr (BF16) *reinterpret_cast<uint4*>(mine + a.out_off + q * 16) = make_uint4(u[0], u[1], u[2], u[3]);
+      else *reinterpret_cast<uint2*>(mine + a.out_off + q * 8) = make_uint2(u[0], u[1]);
+    }
+  }
+  if (lost) atomicCAS(a.err, 0, ERR_WAIT_PEER);
+  if (!pull) return;                           // the pushing half of a test leaves the epoch to the pulling half
+  __syncthreads();
+  if (tid == 0 && atomicAdd(flag(mine, FLAG_LL_ARRIVE), 1u) == gridDim.x - 1) {
+    *flag(mine, FLAG_LL_ARRIVE) = 0;
+    *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_LL_CALLS)) = epoch;
+    __threadfence();
+  }
+}
+
+struct DeviceFacts {
+  int sms = 0, per_sm[3][2] = {};              // resident blocks of the share kernel by world (2, 4, 8) and partial type
+};
+
 template <int WORLD>
 cudaError_t launch_world(const PeerArgs& a, int grid_cap, cudaStream_t s) {
+  static DeviceFacts facts[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  DeviceFacts& f = facts[dev];
+  if (!f.sms && (e = cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  if (a.mode >= MODE_FLAGGED) {
+    const int64_t quads = (a.parts_bf16 ? a.total / 2 : a.total) / 4;
+    int64_t grid = (quads + LL_THREADS - 1) / LL_THREADS;
+    if (grid > 4 * f.sms) grid = 4 * f.sms;
+    if (grid_cap > 0 && grid > grid_cap) grid = grid_cap;
+    if (a.parts_bf16) peer_reduce_flagged_kernel<WORLD, true><<<static_cast<unsigned>(grid), LL_THREADS, 0, s>>>(a);
+    else peer_reduce_flagged_kernel<WORLD, false><<<static_cast<unsigned>(grid), LL_THREADS, 0, s>>>(a);
+    return cudaGetLastError();
+  }
   auto run = [&](auto kernel) -> cudaError_t {
-    int per_sm = 0, dev = 0, sms = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, PEER_THREADS, 0);
-    if (e != cudaSuccess) return e;
-    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
-    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
-    const int64_t work = a.two_shot ? a.total / a.world : a.total;
+    int& per_sm = f.per_sm[WORLD == 2 ? 0 : WORLD == 4 ? 1 : 2][a.parts_bf16 ? 1 : 0];
+    if (!per_sm) {
+      cudaError_t q = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, PEER_THREADS, 0);
+      if (q != cudaSuccess) return q;
+      if (per_sm < 1) per_sm = 1;
+    }
+    const int64_t work = a.mode == MODE_SHARES ? a.total / a.world : a.total;
     int64_t grid = (work / 8 + PEER_THREADS - 1) / PEER_THREADS;
-    const int64_t resident = static_cast<int64_t>(per_sm > 0 ? per_sm : 1) * sms;
+    const int64_t resident = static_cast<int64_t>(per_sm) * f.sms;
     if (grid > resident) grid = resident;
     if (grid_cap > 0 && grid > grid_cap) grid = grid_cap;
     if (grid < 1) grid = 1;
@@ -258,15 +384,21 @@ int tf_peer_close(void* ptr) {
 }
 
 int tf_peer_reduce(void* const* bufs, int rank, int world, size_t part_off, size_t out_off, int64_t total, int parts_bf16,
-                   int out_f32, int two_shot, unsigned polls, int grid_cap, void* stream) {
-  if (!bufs || (world != 2 && world != 4 && world != 8) || rank < 0 || rank >= world || total < 8)
-    return fail_moe(TF_ERR_ARG, "tf_peer_reduce: 2, 4 or 8 ranks and at least eight elements");
-  if (total % (two_shot ? 8 * world : 8)) return fail_moe(TF_ERR_ARG, "tf_peer_reduce: the elements split into pieces of eight (a rank)");
+                   int out_f32, int mode, size_t ll_off, size_t ll_slot, unsigned polls, int grid_cap, void* stream) {
+  if (!bufs || (world != 2 && world != 4 && world != 8) || rank < 0 || rank >= world || total < 8 || mode < MODE_ALL ||
+      mode > MODE_FLAGGED_PULL)
+    return fail_moe(TF_ERR_ARG, "tf_peer_reduce: 2, 4 or 8 ranks, at least eight elements, a form 0..4");
+  if (total % (mode == MODE_SHARES ? 8 * world : 8)) return fail_moe(TF_ERR_ARG, "tf_peer_reduce: the elements split into pieces of eight (a rank)");
   if (part_off < FLAG_BYTES || out_off < FLAG_BYTES || part_off % 16 || out_off % 16)
     return fail_moe(TF_ERR_ALIGN, "tf_peer_reduce: offsets past the flags, 16-byte aligned");
   const size_t part_bytes = static_cast<size_t>(total) * (parts_bf16 ? 2 : 4), out_bytes = static_cast<size_t>(total) * (out_f32 ? 4 : 2);
   if ((part_off < out_off ? part_off + part_bytes > out_off : out_off + out_bytes > part_off))
     return fail_moe(TF_ERR_ARG, "tf_peer_reduce: the partial and the result overlap");
+  if (mode >= MODE_FLAGGED) {
+    const size_t top = part_off > out_off ? part_off + part_bytes : out_off + out_bytes;
+    if (ll_off % 16 || ll_slot % 16 || ll_off < top || ll_slot < 2 * part_bytes)
+      return fail_moe(TF_ERR_ARG, "tf_peer_reduce: the slots lie past partial and result and hold twice the partial each");
+  }
   int* err = device_error_word();
   if (!err) return fail_moe(TF_ERR_STATE, "tf_peer_reduce: tf_init has not run for the current device");
   PeerArgs a = {};
@@ -275,8 +407,8 @@ int tf_peer_reduce(void* const* bufs, int rank, int world, size_t part_off, size
     a.buf[r] = static_cast<char*>(bufs[r]);
   }
   a.mine = a.buf[rank];
-  a.rank = rank, a.world = world, a.part_off = part_off, a.out_off = out_off, a.total = total;
-  a.parts_bf16 = parts_bf16, a.out_f32 = out_f32, a.two_shot = two_shot, a.polls = polls ? polls : (1u << 20), a.err = err;
+  a.rank = rank, a.world = world, a.part_off = part_off, a.out_off = out_off, a.ll_off = ll_off, a.ll_slot = ll_slot, a.total = total;
+  a.parts_bf16 = parts_bf16, a.out_f32 = out_f32, a.mode = mode, a.polls = polls ? polls : (1u << 20), a.err = err;
   const cudaStream_t s = static_cast<cudaStream_t>(stream);
   const cudaError_t e = world == 2 ? launch_world<2>(a, grid_cap, s) : world == 4 ? launch_world<4>(a, grid_cap, s) : launch_world<8>(a, grid_cap, s);
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_peer_reduce");

@@ -58,23 +58,28 @@ class _Raw:
 class PeerReducer:
     """The rank-ordered all-reduce in one launch over peer memory (``tf_peer_reduce``): every rank owns one buffer that the
     other processes of the box map, producers write their partial straight into it (``partial``), and ``reduce`` returns
-    the sum, the bits ``ordered_all_reduce`` gives.  Buffers: [flags | partial | result].  ``two_shot_from`` bytes and up,
-    a rank sums one share and stores it to every rank; below, every rank reads all partials itself.
+    the sum, the bits ``ordered_all_reduce`` gives.  Buffers: [flags | partial | result | slots].  Partials of up to
+    ``flagged_up_to`` bytes travel as flagged words (one trip over the links, no barrier); larger ones in shares between
+    two barriers (a rank sums 1/world and stores it to every rank).
 
     The result tensor is a view of the buffer: it is overwritten by the next ``reduce``, and so is the partial."""
 
-    def __init__(self, elements: int, group=None, *, device=None, two_shot_from: int = 1 << 19, bufs: list[int] | None = None,
+    ALL, SHARES, FLAGGED, FLAGGED_PUSH, FLAGGED_PULL = range(5)
+
+    def __init__(self, elements: int, group=None, *, device=None, flagged_up_to: int = 1 << 19, bufs: list[int] | None = None,
                  rank: int | None = None) -> None:
         lib = _lib.lib()
-        self.group, self.elements, self.two_shot_from = group, elements, two_shot_from
+        self.group, self.elements, self.flagged_up_to = group, elements, flagged_up_to
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        self.flags, self.part_off, self.out_off, self.nbytes = self.layout(elements)
+        self.world = len(bufs) if bufs is not None else dist.get_world_size(group)
+        self.flags, self.part_off, self.out_off, self.ll_off, self.ll_slot, self.nbytes = self.layout(elements, self.world, flagged_up_to)
+        self.force: int | None = None                          # a form for every call (tests)
         self._opened: list[int] = []
         self._owned = 0
         if bufs is not None:                                   # buffers made by the caller (one process driving them all)
-            self.rank, self.world, self.bufs = rank, len(bufs), list(bufs)
+            self.rank, self.bufs = rank, list(bufs)
         else:
-            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+            self.rank = dist.get_rank(group)
             with torch.cuda.device(self.device):
                 self._owned = self.alloc(self.nbytes)
                 handle = ctypes.create_string_buffer(64)
@@ -93,14 +98,18 @@ class PeerReducer:
                 dist.barrier(group)                            # every buffer is mapped before anyone signals
         self._table = (ctypes.c_void_p * self.world)(*self.bufs)
         self._mine = torch.as_tensor(_Raw(self.bufs[self.rank], self.nbytes), device=self.device)
+        self._views: dict[tuple, torch.Tensor] = {}
 
     @staticmethod
-    def layout(elements: int) -> tuple[int, int, int, int]:
-        """Bytes of the flags, offsets of the partial and of the result, bytes of a buffer for ``elements`` fp32 values."""
+    def layout(elements: int, world: int, flagged_up_to: int = 1 << 19) -> tuple[int, int, int, int, int, int]:
+        """Bytes of the flags, offsets of the partial and of the result, offset and size of the slots of flagged words,
+        bytes of a whole buffer, for partials of up to ``elements`` fp32 values."""
 
         flags = int(_lib.lib().tf_peer_flag_bytes())
         room = (-(-elements * 4 // 256)) * 256
-        return flags, flags, flags + room, flags + 2 * room
+        slot = 2 * min(room, (-(-flagged_up_to // 256)) * 256)
+        ll_off = flags + 2 * room
+        return flags, flags, flags + room, ll_off, slot, ll_off + 2 * world * slot
 
     @staticmethod
     def alloc(nbytes: int) -> int:
@@ -108,13 +117,27 @@ class PeerReducer:
         _lib.check(_lib.lib().tf_peer_alloc(nbytes, ctypes.byref(ptr)), "peer alloc")
         return ptr.value
 
+    def _view(self, off: int, shape, dtype: torch.dtype) -> torch.Tensor:
+        key = (off, tuple(shape), dtype)
+        view = self._views.get(key)
+        if view is None:
+            n = int(torch.Size(shape).numel())
+            if n > self.elements or dtype not in (torch.float32, torch.bfloat16):
+                raise ValueError("PeerReducer: fp32 or bf16, no more elements than the reducer was made for")
+            view = self._views[key] = self._mine[off:off + n * dtype.itemsize].view(dtype).view(shape)
+        return view
+
     def partial(self, shape, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
         """Where this rank's partial goes: a view of its buffer for the producer to write into."""
 
-        n = int(torch.Size(shape).numel())
-        if n > self.elements or dtype not in (torch.float32, torch.bfloat16):
-            raise ValueError("PeerReducer.partial: fp32 or bf16, no more elements than the reducer was made for")
-        return self._mine[self.part_off:self.part_off + n * dtype.itemsize].view(dtype).view(shape)
+        return self._view(self.part_off, shape, dtype)
+
+    def form(self, n: int, itemsize: int) -> int:
+        if self.force is not None:
+            return self.force
+        if n * itemsize <= self.flagged_up_to:
+            return self.FLAGGED
+        return self.SHARES if n % (8 * self.world) == 0 else self.ALL
 
     def reduce(self, part: torch.Tensor, dtype: torch.dtype = torch.bfloat16, *, polls: int = 0, grid_cap: int = 0) -> torch.Tensor:
         """Sum of every rank's ``part`` (a tensor from ``partial``; anything else is copied in first)."""
@@ -123,11 +146,11 @@ class PeerReducer:
         home = self.partial(part.shape, part.dtype)
         if part.data_ptr() != home.data_ptr() or not part.is_contiguous():
             home.copy_(part)
-        two_shot = n * part.element_size() >= self.two_shot_from and n % (8 * self.world) == 0
         _lib.check(_lib.lib().tf_peer_reduce(self._table, self.rank, self.world, self.part_off, self.out_off, n,
-                                             int(part.dtype == torch.bfloat16), int(dtype == torch.float32), int(two_shot),
-                                             polls, grid_cap, _lib.stream_of(home)), "peer reduce")
-        return self._mine[self.out_off:self.out_off + n * dtype.itemsize].view(dtype).view(part.shape)
+                                             int(part.dtype == torch.bfloat16), int(dtype == torch.float32),
+                                             self.form(n, part.element_size()), self.ll_off, self.ll_slot, polls, grid_cap,
+                                             _lib.stream_of(home)), "peer reduce")
+        return self._view(self.out_off, part.shape, dtype)
 
     def close(self) -> None:
         lib = _lib.lib()

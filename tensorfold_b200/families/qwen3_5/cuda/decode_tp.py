@@ -43,3 +43,26 @@ def head_logits(x: torch.Tensor, head, rank: int, world_size: int):
     from . import qmm_fast
 
     return qmm_fast.matmul(x, head), rank * head.n
+
+
+def gather_candidates(values: torch.Tensor, ids: torch.Tensor, comm) -> tuple[torch.Tensor, torch.Tensor]:
+    """Every rank's candidates side by side, rank 0's first: ([R, world * C] values, ids).  ``comm`` is a
+    ``tensorfold_b200.cuda.comm.Comm``; the reference gathers its two ranks the same way
+    (families/qwen3_5/cuda/decode_tp.py:96-104)."""
+
+    rows, count = values.shape
+    ids = ids.to(torch.int64)
+    all_values = torch.empty((comm.world, rows, count), dtype=values.dtype, device=values.device)
+    all_ids = torch.empty((comm.world, rows, count), dtype=ids.dtype, device=ids.device)
+    comm.all_gather(values.contiguous(), all_values)
+    comm.all_gather(ids.contiguous(), all_ids)
+    side_by_side = lambda t: t.permute(1, 0, 2).reshape(rows, comm.world * count)
+    return side_by_side(all_values), side_by_side(all_ids)
+
+
+def greedy_merged(values: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """The whole vocabulary's first maximum from the ranks' local maxima (one candidate a rank, rank order = id order):
+    the earliest rank that holds the largest value wins, as ``argmax`` over the unsplit logits would choose."""
+
+    best = values.argmax(dim=1, keepdim=True)               # torch returns the first of equal maxima
+    return ids.gather(1, best)[:, 0]

@@ -14,6 +14,7 @@ needs the reference.
 
 from __future__ import annotations
 
+import os
 import sys
 from pathlib import Path
 
@@ -113,4 +114,6 @@ def main(ref: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and not os.environ.get("TENSORFOLD_REFERENCE"):
+        sys.exit("usage: make_golden.py <reference checkout>   (or set TENSORFOLD_REFERENCE)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["TENSORFOLD_REFERENCE"])

@@ -31,6 +31,35 @@ def timed(fn, iters):
     return float(t.item())
 
 
+def graph_timed(fn, iters=20):
+    """Microseconds a call when ``iters`` of them replay from one CUDA graph (no launch cost of the host between them)."""
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(iters):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(5):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) * 1e3 / (5 * iters)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    del graph
+    return float(t.item())
+
+
 def main() -> None:
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -44,15 +73,20 @@ def main() -> None:
             g = torch.Generator().manual_seed(1000 * rank + shape[0])
             part = (torch.randn(shape, generator=g) * 2).to(dtype).cuda()
             want = tp.ordered_all_reduce(part)
-            for _ in range(3):                                  # repeated calls reuse the buffers and keep the flags counting
+            forms = [red.ALL, red.SHARES] + ([red.FLAGGED] if part.numel() * part.element_size() <= red.flagged_up_to else [])
+            for form in forms + forms:                          # repeated calls reuse the buffers and keep the flags counting
+                red.force = form
                 home = red.partial(shape, dtype)
                 home.copy_(part)
                 got = red.reduce(home)
                 equal &= bool(torch.equal(got, want))
+            red.force = None
             key = f"{shape[0]}x{shape[1]}_{'bf16' if dtype == torch.bfloat16 else 'f32'}"
             home = red.partial(shape, dtype)
             times[key] = {"peer_us": round(timed(lambda: red.reduce(home), 50), 2),
-                          "collective_us": round(timed(lambda: tp.ordered_all_reduce(part), 50), 2)}
+                          "collective_us": round(timed(lambda: tp.ordered_all_reduce(part), 50), 2),
+                          "peer_graph_us": round(graph_timed(lambda: red.reduce(home)), 2),
+                          "collective_graph_us": round(graph_timed(lambda: tp.ordered_all_reduce(part)), 2)}
     errors = _lib.device_error(part)
     flag = torch.tensor([int(equal), errors], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

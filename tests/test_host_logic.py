@@ -74,6 +74,40 @@ def _worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
+def _head_worker(rank, world, port, out):
+    from tensorfold_b200.cuda.comm import Comm
+    from tensorfold_b200.families.qwen3_5.cuda import decode_tp
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        comm = Comm()
+        g = torch.Generator().manual_seed(9)
+        logits = torch.randn((5, 64 * world), generator=g)      # every rank draws the same full logits, keeps its columns
+        logits[1, 3] = logits[1, 64 * world - 2] = 7.0          # a tie between the first and the last rank
+        mine = logits[:, 64 * rank:64 * (rank + 1)]
+        values, ids = decode_tp.gather_candidates(*decode_tp.split_candidates(mine, None, 64 * rank), comm)
+        pick = decode_tp.greedy_merged(values, ids)
+        s = decode_tp.Sampling(top_k=5)
+        cv, ci = decode_tp.gather_candidates(*decode_tp.split_candidates(mine, s, 64 * rank), comm)
+        comm.barrier()
+        torch.save((logits, pick, cv, ci), f"{out}/h{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gloo_ranks_gather_head_candidates(tmp_path, world):
+    port = 29650 + world + os.getpid() % 200
+    mp.spawn(_head_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        logits, pick, cv, ci = torch.load(tmp_path / f"h{r}.pt")
+        assert torch.equal(pick, logits.argmax(dim=-1)) and int(pick[1]) == 3
+        assert cv.shape == (5, world * (5 + 8)) and torch.equal(logits.gather(1, ci), cv)
+        want = torch.topk(logits, 5, dim=-1).indices
+        assert all(set(want[i].tolist()) <= set(ci[i].tolist()) for i in range(5))
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_gloo_ranks_agree_bit_for_bit_and_sum_in_rank_order(tmp_path, world):
     port = 29600 + world + os.getpid() % 200

@@ -18,13 +18,14 @@ from tensorfold_b200.families.qwen3_5.cuda import distributed
 from gpu_util import DEV
 
 pytestmark = pytest.mark.gpu
+R = tp.PeerReducer
 
 
 def local_ranks(world, elements):
     """``world`` reducers over buffers of this one device; every flag another rank would raise is already far ahead."""
 
     _lib.check(_lib.lib().tf_init(torch.cuda.current_device()), "init")
-    bufs = [tp.PeerReducer.alloc(tp.PeerReducer.layout(elements)[3]) for _ in range(world)]
+    bufs = [tp.PeerReducer.alloc(tp.PeerReducer.layout(elements, world)[-1]) for _ in range(world)]
     ranks = [tp.PeerReducer(elements, bufs=bufs, rank=r, device=DEV) for r in range(world)]
     for red in ranks:
         flags = red._mine[:red.flags].view(torch.int32).view(-1, 32)
@@ -43,17 +44,22 @@ def test_both_forms_give_the_rank_ordered_sum(world, part_dtype):
         parts = [(torch.randn(shape, generator=g) * 3).to(part_dtype).to(DEV) for _ in range(world)]
         for out_dtype in (torch.bfloat16, torch.float32):
             want = distributed.sum_rank_partials(parts, out_dtype)
-            for two_shot_from in (1 << 40, 0):                   # every rank sums all; a rank sums its share for all
+            for form in (R.ALL, R.SHARES, R.FLAGGED):            # every rank sums all; a rank sums its share for all; flagged words
                 outs = []
                 for r, red in enumerate(ranks):
-                    red.two_shot_from = two_shot_from
                     red.partial(shape, part_dtype).copy_(parts[r])
+                    red._view(red.out_off, shape, out_dtype).zero_()
                 torch.cuda.synchronize()
-                for red, p in zip(ranks, parts):
-                    outs.append(red.reduce(red.partial(shape, part_dtype), out_dtype, grid_cap=3 if two_shot_from else 0))
+                halves = (R.FLAGGED_PUSH, R.FLAGGED_PULL) if form == R.FLAGGED else (form,)
+                for half in halves:                              # all ranks store their words before any rank collects
+                    for red in ranks:
+                        red.force = half
+                        out = red.reduce(red.partial(shape, part_dtype), out_dtype, grid_cap=3 if form == R.ALL else 0)
+                        if half != R.FLAGGED_PUSH:
+                            outs.append(out)
                 torch.cuda.synchronize()
                 for r, o in enumerate(outs):
-                    assert torch.equal(o, want), (world, part_dtype, out_dtype, two_shot_from, r)
+                    assert torch.equal(o, want), (world, part_dtype, out_dtype, form, r)
         assert _lib.device_error(parts[0]) == 0
     finally:
         torch.cuda.synchronize()
@@ -66,13 +72,15 @@ def test_a_missing_peer_ends_the_wait_with_an_error():
 
     _lib.check(_lib.lib().tf_init(torch.cuda.current_device()), "init")
     n = 4096
-    bufs = [tp.PeerReducer.alloc(tp.PeerReducer.layout(n)[3]) for _ in range(2)]
+    bufs = [tp.PeerReducer.alloc(tp.PeerReducer.layout(n, 2)[-1]) for _ in range(2)]
     try:
         red = tp.PeerReducer(n, bufs=bufs, rank=0, device=DEV)
         red.partial((n,), torch.float32).fill_(1.0)
-        red.reduce(red.partial((n,), torch.float32), polls=2000)
-        torch.cuda.synchronize()
-        assert _lib.device_error(red._mine) == 4
+        for form in (R.SHARES, R.FLAGGED):                       # a barrier that no one joins; words that never come
+            red.force = form
+            red.reduce(red.partial((n,), torch.float32), polls=2000)
+            torch.cuda.synchronize()
+            assert _lib.device_error(red._mine) == 4, form
         x = torch.ones((8,), device=DEV)
         assert float((x + x).sum()) == 16.0                      # the context still works
         assert _lib.device_error(red._mine) == 0                 # read and cleared
@@ -85,11 +93,13 @@ def refused(**kw):
     import ctypes
     bufs = [tp.PeerReducer.alloc(1 << 20) for _ in range(2)]
     try:
-        args = dict(rank=0, world=2, part_off=4096, out_off=4096 + (1 << 18), total=4096, parts_bf16=0, out_f32=0, two_shot=0)
+        args = dict(rank=0, world=2, part_off=4096, out_off=4096 + (1 << 18), total=4096, parts_bf16=0, out_f32=0, mode=0,
+                    ll_off=1 << 19, ll_slot=1 << 15)
         args.update(kw)
         table = (ctypes.c_void_p * 2)(*bufs)
         return _lib.lib().tf_peer_reduce(table, args["rank"], args["world"], args["part_off"], args["out_off"], args["total"],
-                                         args["parts_bf16"], args["out_f32"], args["two_shot"], 10, 0, None)
+                                         args["parts_bf16"], args["out_f32"], args["mode"], args["ll_off"], args["ll_slot"], 10, 0,
+                                         None)
     finally:
         for b in bufs:
             _lib.lib().tf_peer_free(b)
@@ -100,7 +110,8 @@ def test_bad_arguments_launch_nothing():
     assert refused(world=3) < 0 and refused(rank=2) < 0 and refused(total=4) < 0 and refused(total=4100) < 0
     assert refused(part_off=0) < 0 and refused(part_off=4104) < 0
     assert refused(out_off=4096 + 1024) < 0                       # the result would overlap the partial
-    assert refused(total=4104, two_shot=1) < 0                    # does not split into pieces of eight a rank
+    assert refused(total=4104, mode=1) < 0                        # does not split into pieces of eight a rank
+    assert refused(mode=5) < 0 and refused(mode=2, ll_slot=1 << 14) < 0 and refused(mode=2, ll_off=4096) < 0
     torch.cuda.synchronize()
 
 
