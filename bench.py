@@ -485,7 +485,7 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
     """Tensor-parallel MoE decoder block: hidden 6144, 160 experts top 8 of width 1536 split by expert across the ranks,
     attention o_proj 8192 -> 6144 row-parallel; both bf16 partials [M, 6144] are reduced in rank order over NVLink, by
     the one-launch peer-memory reduction (``us``) and by the NCCL collectives plus a sum kernel (``us_collectives``).
-    ``phases_us``: the block's steps timed one by one on rank order (max over ranks each), with the peer reduction."""
+    ``phases_us``: each of the block's steps replayed alone from a CUDA graph (max over ranks), with the peer reduction."""
 
     import torch
     import torch.distributed as dist
@@ -577,9 +577,11 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
             entry["us_collectives"] = graph_timed(lambda: block(None))
             entry["us_collectives_eager"] = timed(lambda: block(None))
 
-        # the same block step by step (an event after every step; the sum exceeds the block by the events' gaps)
-        state = {}
-        part_of = (lambda: red.partial((rows, d))) if red is not None else (lambda: torch.empty((rows, d), dtype=torch.bfloat16, device=dev))
+        # the same block step by step: each step replayed alone from a CUDA graph of ten (no host launch cost between
+        # them; a step that waits for the other ranks, the reductions, still does)
+        state = {"h": torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)}
+        part_of = (lambda: red.partial((rows, d))) if red is not None else (lambda: state.setdefault(
+            "own", torch.empty((rows, d), dtype=torch.bfloat16, device=dev)))
         reduce_of = (lambda p: red.reduce(p)) if red is not None else (lambda p: p)
         width = layer.experts.width
 
@@ -595,21 +597,9 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
                  ("down", lambda: experts.down(buf.act.view(-1, width), layer.experts, buf.plan, buf.y.view(-1, d), rows)),
                  ("combine", lambda: state.__setitem__("p", moe.combine(buf.y[:rows], buf.wts[:rows], part_of()))),
                  ("reduce_experts", lambda: reduce_of(state["p"]))]
-        iters = 10
-        marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(steps) + 1)] for _ in range(iters)]
-        for _, fn in steps:
-            fn()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        for it in range(iters):
-            marks[it][0].record()
-            for i, (_, fn) in enumerate(steps):
-                fn()
-                marks[it][i + 1].record()
-        torch.cuda.synchronize()
-        entry["phases_us"] = {name: round(biggest(sum(m[i].elapsed_time(m[i + 1]) for m in marks) * 1e3 / iters), 1)
-                              for i, (name, _) in enumerate(steps)}
+        entry["phases_us"] = {}
+        for name, fn in steps:                                   # in order: each step leaves the next one's inputs
+            entry["phases_us"][name] = round(graph_timed(fn), 1)
         out[f"M{rows}"] = entry
     if red is not None:
         red.close()
@@ -802,12 +792,12 @@ def run_b200(args) -> None:
         layer = layers[i % ring]
         for names in SETS:
             if names[0] in row_parallel:
-                qmm.matmul(dev_x[names[0]], layer[names[0]], f32=True, out=partial[names[0]], pdl=False, sk=splits[names[0]])
+                qmm.matmul(dev_x[names[0]], layer[names[0]], f32=True, out=partial[names[0]], pdl=pdl, sk=splits[names[0]])
                 reduced[names[0]] = (reducers[names[0]].reduce(partial[names[0]]) if peer else
                                      tp.ordered_all_reduce(partial[names[0]]))
             else:
                 qmm.matmul_set(dev_x[names[0]], [layer[n] for n in names], sks=[splits[n] for n in names],
-                               outs=[dev_y[n] for n in names], pdl=pdl and world == 1)
+                               outs=[dev_y[n] for n in names], pdl=pdl)
 
     def barrier():
         if world > 1:
@@ -820,7 +810,8 @@ def run_b200(args) -> None:
             step(i, False)
     barrier()
 
-    pdl = not args.no_pdl and world == 1
+    # programmatic dependent launch between this library's kernels; NCCL's kernels in between rule it out
+    pdl = not args.no_pdl and (world == 1 or peer)
 
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
     names = [name for name, _ in shapes]

@@ -46,6 +46,19 @@ struct StreamParams {
   int nproj, items;
   int* err;
   StreamProj proj[STREAM_MAX_PROJ];
+  // grouped (mixture-of-experts) form, GROUPED kernels only: one projection (proj[0], one K slice) whose weights are a
+  // table of experts; plan item y = (expert, first, count <= ROWS) runs rows members[first .. first + count), read from
+  // row pair / slots of x (slots > 0) or row pair (slots == 0), and writes row `pair` of out.  Work item i is plan item
+  // i / groups_of_sb for the super-blocks (i % groups_of_sb) * KW ...; the item count comes from counts[0] on the device.
+  int64_t ldx;                // row stride of x in elements
+  const int* plan_items;      // [max items][3]
+  const int* counts;          // [0] = plan items in use
+  const int* members;         // pair ids grouped by expert
+  int slots;
+  int64_t expert_stride;      // words from one expert's units to the next
+  int experts;                // experts the table holds: an item that names another one is skipped and reported
+  int epi;                    // 0 store as is; 1 bf16(relu(bf16 v)^2); 2 SwiGLU over the gate / up halves of a tile pair
+  float limit;                // SwiGLU clip (0: none)
 };
 
 template <int BITS, int GS, int MT, int KW>
@@ -96,6 +109,7 @@ struct StreamItem {
   int g_first;                // first group of the slice
   int per;                    // groups of the slice
   int nst;                    // stages of the slice
+  int expert, first, rows;    // grouped form: the plan item (rows == 0: nothing to do)
 };
 
 #define TF_PROJ_FIELD(p, pi, field)                                                                   \
@@ -122,7 +136,26 @@ __device__ __forceinline__ StreamItem stream_item(const StreamParams& p, int i) 
   return it;
 }
 
-template <int BITS, int GS, int MT, int KW>
+// Grouped form: work item i = (plan item i / sbg, super-blocks (i % sbg) * KW ...), sbg = ceil(nsb / KW).
+template <int KW, int G, int ROWS>
+__device__ __forceinline__ StreamItem grouped_item(const StreamParams& p, int i, int sbg) {
+  StreamItem it;
+  const int y = i / sbg;
+  const int* item = p.plan_items + 3 * y;
+  it.p = 0, it.sk = 1, it.slice = 0, it.g_first = 0;
+  it.sb0 = (i - y * sbg) * KW;
+  it.lanes = min(KW, p.proj[0].nsb - it.sb0);
+  it.per = p.KG;
+  it.nst = (p.KG + G - 1) / G;
+  it.expert = __ldg(item), it.first = __ldg(item + 1), it.rows = min(ROWS, __ldg(item + 2));
+  if (it.expert < 0 || it.expert >= p.experts) {             // never read past the table: skip the item, tell the host
+    atomicCAS(p.err, 0, ERR_BAD_ITEM);
+    it.rows = 0, it.nst = 0;
+  }
+  return it;
+}
+
+template <int BITS, int GS, int MT, int KW, bool GROUPED = false>
 __global__ void __launch_bounds__(StreamGeo<BITS, GS, MT, KW>::THREADS, StreamGeo<BITS, GS, MT, KW>::MINB)
 qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ StreamParams p) {
   using Geo = StreamGeo<BITS, GS, MT, KW>;
@@ -143,7 +176,9 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
   const int tid = threadIdx.x, warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0), lane = tid & 31;
   if (tid == 0) {
     for (int i = 0; i < NST; ++i) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full32 + 8 * i), "r"(2) : "memory");    // weights' bytes + bytes of x
+      // dense: the weights' bytes and the bytes of x each come with an arrival; grouped: the weights' arrival and one
+      // from every lane of the copy warp when its 16-byte copies of x have landed
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full32 + 8 * i), "r"(GROUPED ? 33 : 2) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty32 + 8 * i), "r"(CONSUMERS) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sums32 + 8 * i), "r"(1) : "memory");
     }
@@ -160,12 +195,23 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
     }
   };
   const int first_item = blockIdx.x, step = gridDim.x;
+  int n_items = p.items, sbg = 1;
+  if constexpr (GROUPED) {
+    pdl_wait();                                             // the plan may be the previous kernel's output
+    sbg = (p.proj[0].nsb + KW - 1) / KW;
+    n_items = __ldg(p.counts) * sbg;
+  }
+  auto item_at = [&](int i) -> StreamItem {
+    if constexpr (GROUPED) return grouped_item<KW, G, ROWS>(p, i, sbg);
+    else return stream_item<KW, G>(p, i);
+  };
 
   if (warp == CONSUMERS) {
     // ------------------------------------------------------------------ copy warp: one bulk copy per lane and stage
     auto issue_w = [&](const StreamItem& it, int st, int slot) {
       if (lane == 0) {
         const uint32_t* w = TF_PROJ_FIELD(p, it.p, w);
+        if constexpr (GROUPED) w += static_cast<int64_t>(it.expert) * p.expert_stride;
         const int64_t sb_stride = TF_PROJ_FIELD(p, it.p, sb_stride);
         const int ng = min(G, it.per - st * G);
         const uint32_t* src = w + static_cast<int64_t>(it.sb0) * sb_stride +
@@ -175,8 +221,28 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
         for (int kw = 0; kw < it.lanes; ++kw) bulk_load32(dst + kw * Geo::W_BYTES, src + kw * sb_stride, ng * UNITW * 4, bar);
       }
     };
-    auto issue_x = [&](const StreamItem& it, int st, int slot) {
-      if (lane == 0) {
+    auto issue_x = [&](const StreamItem& it, int st, int slot, int64_t my_row) {
+      if constexpr (GROUPED) {
+        // gathered rows: 16-byte copies placed in the swizzle pattern of the tensor-map boxes; lane r < rows holds the
+        // row of x that row r reads (my_row)
+        const int ng = min(G, it.per - st * G);
+        const int cpr = ng * GS / 8;                        // 16-byte chunks a row
+        const uint32_t bar = full32 + 8 * slot, dst = smem32 + slot * Geo::STAGE + Geo::X_OFF;
+        const __nv_bfloat16* src = p.x + static_cast<int64_t>(it.g_first + st * G) * GS;
+        const int chunks = it.rows * cpr;
+        for (int c0 = 0; c0 < chunks; c0 += 32) {
+          const int c = c0 + lane;
+          const bool valid = c < chunks;
+          const int r = valid ? c / cpr : 0, q = c - r * cpr;
+          const int64_t row = __shfl_sync(0xFFFFFFFFu, my_row, r);
+          if (valid)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (q >> 3) * Geo::XHALF + r * XHALF_ROW +
+                                                                          (((q & 7) ^ (r & 7)) << 4)),
+                         "l"(src + row * p.ldx + q * 8)
+                         : "memory");
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+      } else if (lane == 0) {
         const int ng = min(G, it.per - st * G);
         const int boxes = (ng * GS + 63) / 64;              // a [64 inputs x ROWS] box lands in a swizzled half tile
         const uint32_t bar = full32 + 8 * slot, dst = smem32 + slot * Geo::STAGE + Geo::X_OFF;
@@ -188,8 +254,8 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
     // the weights of the first NST stages never depend on the previous kernel: they go out before the dependency wait
     {
       int gst = 0;
-      for (int i = first_item; i < p.items && gst < NST; i += step) {
-        const StreamItem it = stream_item<KW, G>(p, i);
+      for (int i = first_item; i < n_items && gst < NST; i += step) {
+        const StreamItem it = item_at(i);
         for (int st = 0; st < it.nst && gst < NST; ++st, ++gst) issue_w(it, st, gst);
       }
     }
@@ -197,8 +263,15 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
     bool ok = true;
     int gst = 0, slot = 0;
     uint32_t phase = 1;                                     // parity of the `empty` phase that frees the slot (first round: none)
-    for (int i = first_item; i < p.items && ok; i += step) {
-      const StreamItem it = stream_item<KW, G>(p, i);
+    for (int i = first_item; i < n_items && ok; i += step) {
+      const StreamItem it = item_at(i);
+      int64_t my_row = 0;
+      if constexpr (GROUPED) {
+        if (lane < it.rows) {
+          const int pair = __ldg(p.members + it.first + lane);
+          my_row = p.slots > 0 ? pair / p.slots : pair;
+        }
+      }
       for (int st = 0; st < it.nst; ++st, ++gst) {
         if (gst >= NST) {                                   // the stage goes where stage gst - NST was
           ok = mbar32_wait(empty32 + 8 * slot, phase, abort32, 256);     // (naps between polls: the ring has slack)
@@ -208,7 +281,7 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
           }
           issue_w(it, st, slot);
         }
-        issue_x(it, st, slot);
+        issue_x(it, st, slot, my_row);
         if (++slot == NST) slot = 0, phase ^= 1;
       }
     }
@@ -223,8 +296,8 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
     uint32_t phase = 0;
     const uint32_t xrow = (lane & 7) * XHALF_ROW;
     const uint32_t sw0 = (((lane >> 3) ^ (lane & 7)) << 4), sw1 = (((4 | (lane >> 3)) ^ (lane & 7)) << 4);
-    for (int i = first_item; i < p.items && ok; i += step) {
-      const StreamItem it = stream_item<KW, G>(p, i);
+    for (int i = first_item; i < n_items && ok; i += step) {
+      const StreamItem it = item_at(i);
       for (int st = 0; st < it.nst; ++st) {
         ok = mbar32_wait(full32 + 8 * slot, phase, abort32, 64);
         if (!ok) {
@@ -391,10 +464,10 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
     GroupRegs ra, rb;
     int slot = 0;
     uint32_t phase = 0;                                     // parity of the `sums` phase the current slot waits for
-    for (int i = first_item; i < p.items && ok; i += step) {
-      const StreamItem it = stream_item<KW, G>(p, i);
+    for (int i = first_item; i < n_items && ok; i += step) {
+      const StreamItem it = item_at(i);
       const bool active = kw < it.lanes;
-      const bool more_items = i + step < p.items;
+      const bool more_items = i + step < n_items;
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -447,7 +520,46 @@ qmm_stream_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant
       if (!ok) break;
 
       // ---------------------------------------------------------------- the item's output
-      if (active) {
+      if constexpr (GROUPED) {
+        if (active && it.rows > 0) {
+          // rows mt * 8 + 2 t (+ 1) of the item are pairs members[first + row]; each writes its own row of out
+          const int sb = it.sb0 + kw;
+          int64_t orow[MT][2];
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int ml = mt * 8 + 2 * t + e;
+              orow[mt][e] = ml < it.rows ? static_cast<int64_t>(__ldg(p.members + it.first + ml)) * p.proj[0].ldo : -1;
+            }
+          if (p.epi == 2) {
+            // SwiGLU: half 0 of a tile pair holds 16 gate columns, half 1 the up columns of the same 16 outputs
+            const int nout = p.proj[0].N / 2;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.proj[0].out);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int n = sb * (SB_COLS / 2) + tp * 16 + g + 8 * (e >> 1);
+                if (orow[mt][e & 1] >= 0 && n < nout)
+                  out[orow[mt][e & 1] + n] = __float2bfloat16_rn(swiglu_f(acc[0][mt][e], acc[1][mt][e], p.limit));
+              }
+          } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int n = sb * SB_COLS + tp * 32 + h * 16 + g + 8 * (e >> 1);
+                  if (orow[mt][e & 1] < 0 || n >= p.proj[0].N) continue;
+                  const float v = p.epi == 1 ? relu2_f(acc[h][mt][e]) : acc[h][mt][e];
+                  if (p.proj[0].out_f32) reinterpret_cast<float*>(p.proj[0].out)[orow[mt][e & 1] + n] = v;
+                  else reinterpret_cast<__nv_bfloat16*>(p.proj[0].out)[orow[mt][e & 1] + n] = __float2bfloat16_rn(v);
+                }
+          }
+        }
+      } else if (active) {
         pdl_wait();                                         // nothing is written before the previous kernel is done
         OutProj pr;
         pr.out = TF_PROJ_FIELD(p, it.p, out), pr.ldo = TF_PROJ_FIELD(p, it.p, ldo);

@@ -84,6 +84,45 @@ cudaError_t configure_gs() {
   return e;
 }
 
+#if TF_BITS == 4
+// The grouped (mixture-of-experts) form: expert tables are 4-bit; one lane a block, 8 or 16 rows an item.
+template <int GS, int MT>
+cudaError_t launch_grouped(const StreamParams& p, int grid, cudaStream_t stream, bool pdl) {
+  using Geo = StreamGeo<4, GS, MT, 1>;
+  static const CUtensorMap none = {};
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(Geo::THREADS);
+  cfg.dynamicSmemBytes = Geo::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  int na = 0;
+  if (pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, qmm_stream_kernel<4, GS, MT, 1, true>, none, p);
+}
+
+template <int GS, int MT>
+int resident_grouped() {
+  using Geo = StreamGeo<4, GS, MT, 1>;
+  int blocks = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, qmm_stream_kernel<4, GS, MT, 1, true>, Geo::THREADS, Geo::SMEM) != cudaSuccess)
+    return 0;
+  return blocks;
+}
+
+template <int GS, int MT>
+cudaError_t configure_grouped() {
+  return cudaFuncSetAttribute(qmm_stream_kernel<4, GS, MT, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              StreamGeo<4, GS, MT, 1>::SMEM);
+}
+#endif
+
 }  // namespace
 
 #define TF_CAT2(a, b) a##b
@@ -112,7 +151,41 @@ cudaError_t TF_CAT(qmm_stream_configure_b, TF_BITS)() {
   cudaError_t e = configure_gs<32>();
   if (e == cudaSuccess) e = configure_gs<64>();
   if (e == cudaSuccess) e = configure_gs<128>();
+#if TF_BITS == 4
+  if (e == cudaSuccess) e = configure_grouped<32, 1>();
+  if (e == cudaSuccess) e = configure_grouped<32, 2>();
+  if (e == cudaSuccess) e = configure_grouped<64, 1>();
+  if (e == cudaSuccess) e = configure_grouped<64, 2>();
+  if (e == cudaSuccess) e = configure_grouped<128, 1>();
+  if (e == cudaSuccess) e = configure_grouped<128, 2>();
+#endif
   return e;
 }
+
+#if TF_BITS == 4
+cudaError_t qmm_stream_grouped_launch(const StreamParams& p, int gs, int mt, int grid, cudaStream_t stream, bool pdl) {
+  switch (gs * 10 + mt) {
+    case 321: return launch_grouped<32, 1>(p, grid, stream, pdl);
+    case 322: return launch_grouped<32, 2>(p, grid, stream, pdl);
+    case 641: return launch_grouped<64, 1>(p, grid, stream, pdl);
+    case 642: return launch_grouped<64, 2>(p, grid, stream, pdl);
+    case 1281: return launch_grouped<128, 1>(p, grid, stream, pdl);
+    case 1282: return launch_grouped<128, 2>(p, grid, stream, pdl);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+int qmm_stream_grouped_resident(int gs, int mt) {
+  switch (gs * 10 + mt) {
+    case 321: return resident_grouped<32, 1>();
+    case 322: return resident_grouped<32, 2>();
+    case 641: return resident_grouped<64, 1>();
+    case 642: return resident_grouped<64, 2>();
+    case 1281: return resident_grouped<128, 1>();
+    case 1282: return resident_grouped<128, 2>();
+    default: return 0;
+  }
+}
+#endif
 
 }  // namespace tf

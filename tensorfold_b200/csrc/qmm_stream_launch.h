@@ -21,4 +21,8 @@ TF_DECLARE_STREAM_BITS(6)
 TF_DECLARE_STREAM_BITS(8)
 #undef TF_DECLARE_STREAM_BITS
 
+// The grouped (mixture-of-experts) form, 4-bit tables: mt = 1 (items of up to 8 rows) or 2 (16 rows).
+cudaError_t qmm_stream_grouped_launch(const StreamParams& p, int gs, int mt, int grid, cudaStream_t stream, bool pdl);
+int qmm_stream_grouped_resident(int gs, int mt);
+
 }  // namespace tf

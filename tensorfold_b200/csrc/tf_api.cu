@@ -41,11 +41,13 @@ struct DeviceState {
   int* err = nullptr;
   int sms = 0;
   signed char resident[6][3][2][3] = {};   // blocks of a streaming kernel an SM holds: [bits][group][row tile][lanes]
+  signed char resident_grouped[3][2] = {}; // the same for the grouped form: [group][row tile]
 };
 DeviceState g_devices[MAX_DEVICES];
 int g_lanes_pref = 0;                 // tuning knob (tf_tune): preferred slice lanes per block, 0 = default
 int g_stream_lanes = 0;               // tuning knob: super-blocks a streaming block holds side by side, 0 = default
 int g_stream_blocks = 0;              // tuning knob: streaming blocks an SM may hold, 0 = as many as fit
+int g_grouped_tiled = 0;              // tuning knob: 1 sends the experts' decode form through the tiled kernel (one block an item)
 
 constexpr int BIT_WIDTHS[6] = {2, 3, 4, 5, 6, 8};
 int bits_index(int bits) { return bits == 8 ? 5 : bits - 2; }
@@ -375,6 +377,11 @@ int tf_init(int device) {
             g_devices[device].resident[b][g][m][k] =
                 static_cast<signed char>(stream_resident_bits(BIT_WIDTHS[b], 32 << g, m + 1, 1 << k));
   }
+  if (e == cudaSuccess) {
+    for (int g = 0; g < 3; ++g)
+      for (int m = 0; m < 2; ++m)
+        g_devices[device].resident_grouped[g][m] = static_cast<signed char>(qmm_stream_grouped_resident(32 << g, m + 1));
+  }
   if (e == cudaSuccess) e = moe_static_init(device);
   int* err = nullptr;
   if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_error_word);
@@ -417,6 +424,10 @@ int tf_tune(const char* key, int value) {
   }
   if (key != nullptr && std::string(key) == "stream_blocks" && value >= 0 && value <= 8) {
     g_stream_blocks = value;
+    return TF_OK;
+  }
+  if (key != nullptr && std::string(key) == "grouped_tiled" && (value == 0 || value == 1)) {
+    g_grouped_tiled = value;
     return TF_OK;
   }
   return fail(TF_ERR_ARG, "tf_tune: unknown key or value");
@@ -695,21 +706,43 @@ int tf_moe_experts(const void* x, int64_t ldx, int slots, const void* tiled, int
   if (max_items > 65535) return fail(TF_ERR_ARG, "tf_moe_experts: too many items");
   DeviceState* st = nullptr;
   if (int rc = current_state(&st)) return rc;
-  QmmParams p = {};
-  p.x = static_cast<const __nv_bfloat16*>(x);
-  p.ldx = ldx, p.M = max_items;
-  p.w = static_cast<const uint32_t*>(tiled);
-  p.sb_stride = static_cast<int64_t>(k / gs) * unit_words(4, gs);
-  p.N = n, p.K = k, p.KG = k / gs, p.sk = 1;
-  p.out = out, p.ldo = ldo, p.out_f32 = out_f32;
-  p.out_vec = reinterpret_cast<uintptr_t>(out) % 16 == 0 && (ldo * (out_f32 ? 4 : 2)) % 16 == 0;
-  p.cluster = 1;
-  p.err = st->err;
-  p.items = items, p.counts = counts, p.members = members, p.slots = slots;
-  p.expert_stride = expert_stride;
-  p.experts = experts;
-  p.epi = epi, p.limit = limit;
-  const cudaError_t e = launch_bits(p, 4, gs, tile / 8, 1, static_cast<cudaStream_t>(stream), false);
+  const cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const int nsb = (n + SB_COLS - 1) / SB_COLS;
+  const int resident = tile <= 16 ? st->resident_grouped[gs_index(gs)][tile / 8 - 1] : 0;
+  cudaError_t e;
+  if (resident > 0 && !g_grouped_tiled) {
+    // items of up to 16 pairs: the persistent kernel in its grouped form, (plan item, super-block) units dealt to the
+    // resident blocks (the item count is read on the device, so the grid covers the most the plan can hold)
+    StreamParams sp = {};
+    sp.x = static_cast<const __nv_bfloat16*>(x);
+    sp.ldx = ldx, sp.M = tile, sp.K = k, sp.KG = k / gs, sp.nproj = 1, sp.items = 0, sp.err = st->err;
+    sp.proj[0].w = static_cast<const uint32_t*>(tiled);
+    sp.proj[0].sb_stride = static_cast<int64_t>(k / gs) * unit_words(4, gs);
+    sp.proj[0].out = out, sp.proj[0].ldo = ldo, sp.proj[0].N = n, sp.proj[0].sk = 1, sp.proj[0].nsb = nsb;
+    sp.proj[0].out_f32 = out_f32;
+    sp.plan_items = items, sp.counts = counts, sp.members = members, sp.slots = slots;
+    sp.expert_stride = expert_stride, sp.experts = experts, sp.epi = epi, sp.limit = limit;
+    const int64_t units = static_cast<int64_t>(max_items) * nsb;
+    int64_t grid = static_cast<int64_t>(g_stream_blocks > 0 ? std::min(g_stream_blocks, resident) : resident) * st->sms;
+    if (grid > units) grid = units;
+    e = qmm_stream_grouped_launch(sp, gs, tile / 8, static_cast<int>(grid), cs, true);
+  } else {
+    QmmParams p = {};
+    p.x = static_cast<const __nv_bfloat16*>(x);
+    p.ldx = ldx, p.M = max_items;
+    p.w = static_cast<const uint32_t*>(tiled);
+    p.sb_stride = static_cast<int64_t>(k / gs) * unit_words(4, gs);
+    p.N = n, p.K = k, p.KG = k / gs, p.sk = 1;
+    p.out = out, p.ldo = ldo, p.out_f32 = out_f32;
+    p.out_vec = reinterpret_cast<uintptr_t>(out) % 16 == 0 && (ldo * (out_f32 ? 4 : 2)) % 16 == 0;
+    p.cluster = 1;
+    p.err = st->err;
+    p.items = items, p.counts = counts, p.members = members, p.slots = slots;
+    p.expert_stride = expert_stride;
+    p.experts = experts;
+    p.epi = epi, p.limit = limit;
+    e = launch_bits(p, 4, gs, tile / 8, 1, cs, false);
+  }
   return e == cudaSuccess ? TF_OK : cuda_fail(e, "tf_moe_experts launch");
 }
 

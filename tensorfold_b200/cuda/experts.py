@@ -16,7 +16,7 @@ from .kernels import qmm
 
 NTW = 4                  # n8 tiles a warp
 COLS = 8 * NTW           # output columns a warp
-TILE = 16                # pairs an item holds (decode form)
+TILE = 16                # pairs an item holds (decode form; 8 while experts see few pairs each, see ``decode_tile``)
 PREFILL_TILE = 128       # pairs an item holds (prefill form: one tcgen05 tile of 128 rows; the reference's is 64)
 SMALL = 1024             # pairs the one-block plan takes; wider plans rank in blocks of 1024 pairs
 
@@ -105,6 +105,14 @@ def make(up: list[tuple], down: tuple, gs: int, *, limit: float = 0.0) -> Expert
     return Experts(u, d, gs, width, dims, float(limit), len(up) == 2)
 
 
+def decode_tile(pairs: int, experts: int) -> int:
+    """Pairs a decode item holds: 8 while an expert sees four pairs on average at most (an item then costs one row
+    tile of MMAs, and an expert with more than 8 pairs gets a second item), else 16.  A load-time choice from the
+    buffers' sizes; a pair's bits do not depend on it."""
+
+    return 8 if pairs <= 4 * experts else TILE
+
+
 def max_items(pairs: int, experts: int, tile: int = TILE) -> int:
     """Items a plan of ``pairs`` can hold: an item per used expert, plus one per ``tile`` pairs past its first."""
 
@@ -118,7 +126,7 @@ class Plan:
                  prefill: bool = False) -> None:
         pairs = rows * slots
         self.rows, self.slots, self.experts, self.prefill = rows, slots, experts, prefill
-        self.tile = PREFILL_TILE if prefill else TILE
+        self.tile = PREFILL_TILE if prefill else decode_tile(pairs, experts)
         self.members = torch.zeros((pairs,), dtype=torch.int32, device=device)
         self.items = torch.zeros((max_items(pairs, experts, self.tile), 3), dtype=torch.int32, device=device)
         self.counts = torch.zeros((2,), dtype=torch.int32, device=device)

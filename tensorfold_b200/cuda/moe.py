@@ -92,17 +92,30 @@ def moe(x: torch.Tensor, router_rows: torch.Tensor, ex: grouped.Experts, buf: Mo
     """Route x [R, D] and run its experts into buf.y [R, k + 1, D] (bf16 in prefill); slot k is the shared expert."""
 
     rows = x.shape[0]
-    router(x, router_rows, buf.logits[:rows], prefill=buf.plan.prefill)
-    select(buf.logits[:rows], buf, top_k, experts)
-    grouped.gate_up(x, ex, buf.plan, buf.act.view(-1, ex.width), rows)
-    grouped.down(buf.act.view(-1, ex.width), ex, buf.plan, buf.y.view(-1, ex.dims), rows)
-    if shared is not None:
+
+    def routed() -> None:
+        router(x, router_rows, buf.logits[:rows], prefill=buf.plan.prefill)
+        select(buf.logits[:rows], buf, top_k, experts)
+        grouped.gate_up(x, ex, buf.plan, buf.act.view(-1, ex.width), rows)
+        grouped.down(buf.act.view(-1, ex.width), ex, buf.plan, buf.y.view(-1, ex.dims), rows)
+
+    def dense() -> None:
         if buf.plan.prefill:                                    # prefill arithmetic for the dense shared expert too
             act = qmm.matmul_act(x, shared.up, act="swiglu", limit=shared.limit, prefill=True)
             qmm.prefill_matmul(act, shared.down, f32=buf.y.dtype == torch.float32, out=buf.y[:rows, top_k])
         else:
             act = qmm.matmul_act(x, shared.up, act="swiglu", limit=shared.limit)
             qmm.matmul(act, shared.down, f32=buf.y.dtype == torch.float32, out=buf.y[:rows, top_k])
+
+    if shared is None:
+        routed()
+    elif buf.plan.prefill:
+        routed()
+        dense()
+    else:
+        # decode: the shared expert reads only x and writes its own slot, so it runs beside the routed path (whose
+        # router, top-k and plan are short kernels that leave the memory system idle)
+        qmm.fork_join([routed, dense])
     return buf
 
 

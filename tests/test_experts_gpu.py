@@ -220,3 +220,37 @@ def test_many_items_keep_the_bits():
     assert int(plan.counts[0]) >= 200
     for r in (0, 31, 63):
         assert torch.equal(run(ex, x[r:r + 1], picks[r:r + 1])[1], y[9 * r:9 * r + 9]), r
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_persistent_and_tiled_kernels_give_the_same_pairs(case):
+    """The decode form runs the persistent kernel's grouped mode; the tiled kernel (one block an item and column block)
+    stays behind a tuning switch.  Same arithmetic: every pair has the same bits through both, for items of 8 and of 16."""
+
+    from tensorfold_b200 import _lib
+
+    ex, _, _ = build(case, 31)
+    rows = 29
+    x = synthetic.activations(rows, ex.dims, 6, std=0.5).to(DEV)
+    picks = picks_for(rows, case, 8)
+    slots = picks.shape[1]
+    results = {}
+    try:
+        for tiled in (0, 1):
+            _lib.check(_lib.lib().tf_tune(b"grouped_tiled", tiled), "tune")
+            for tile in (8, 16):
+                plan = experts.Plan(rows, slots, ex.count, DEV)
+                plan.tile = tile
+                plan.items = torch.zeros((experts.max_items(rows * slots, ex.count, tile), 3), dtype=torch.int32, device=DEV)
+                experts.route(picks.contiguous(), plan)
+                act = torch.zeros((rows * slots, ex.width), dtype=torch.bfloat16, device=DEV)
+                y = torch.zeros((rows * slots, ex.dims), dtype=torch.float32, device=DEV)
+                experts.gate_up(x, ex, plan, act, rows)
+                experts.down(act, ex, plan, y, rows)
+                results[(tiled, tile)] = (act, y)
+    finally:
+        _lib.lib().tf_tune(b"grouped_tiled", 0)
+    first = results[(0, 8)]
+    for key, (act, y) in results.items():
+        assert torch.equal(act, first[0]) and torch.equal(y, first[1]), key
+    assert _lib.device_error(x) == 0
