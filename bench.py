@@ -490,7 +490,7 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
     import torch
     import torch.distributed as dist
 
-    from tensorfold_b200 import synthetic
+    from tensorfold_b200 import _lib, synthetic
     from tensorfold_b200.cuda import experts, moe, tp
     from tensorfold_b200.cuda.kernels import qmm
 
@@ -508,7 +508,17 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
     layer = tp.ExpertParallelMoE(wr, ex, top_k, rank * local_e, e)
     wo = synthetic.affine_weight(d, ko // world, BITS, GS, seed=30 + rank)
     o_proj = qmm.pack(*todev(wo), GS)
-    red = tp.PeerReducer(max(rows_list) * d, device=dev) if world > 1 else None
+    red, red_note = None, None
+    if world > 1:
+        try:                                                 # peer mappings can be refused by a box's set-up: every rank must
+            red = tp.PeerReducer(max(rows_list) * d, device=dev)         # agree, or all fall back to the collectives
+            made = 1
+        except Exception as exc:                             # noqa: BLE001
+            made, red_note = 0, f"peer buffers unavailable ({type(exc).__name__}: {exc})"[:200]
+        agree = torch.tensor([made], device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if not int(agree.item()):
+            red, red_note = None, red_note or "peer buffers unavailable on another rank"
 
     def biggest(us: float) -> float:
         t = torch.tensor([us], dtype=torch.float64, device=dev)
@@ -572,10 +582,18 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
 
         entry = {"us": graph_timed(lambda: block(red)), "us_eager": timed(lambda: block(red)),
                  "timing": "us: ten blocks replayed from one CUDA graph; us_eager: eager launches; CUDA events, max over ranks",
-                 "reduce": "peer memory, one launch" if red is not None else "none (one rank)"}
+                 "reduce": "peer memory, one launch" if red is not None else (red_note or "none (one rank)") if world == 1 or red_note
+                 else "collectives"}
         if red is not None:
             entry["us_collectives"] = graph_timed(lambda: block(None))
             entry["us_collectives_eager"] = timed(lambda: block(None))
+            code = torch.tensor([_lib.device_error(attn)], device=dev)
+            dist.all_reduce(code, op=dist.ReduceOp.MAX)
+            if int(code.item()):                             # a wait on a peer ran out: the peer figure is not a result
+                entry["peer_error"] = int(code.item())
+                entry["us"], entry["us_eager"] = entry["us_collectives"], entry["us_collectives_eager"]
+                entry["reduce"] = "collectives (a wait on a peer ran out)"
+                red = None
 
         # the same block step by step: each step replayed alone from a CUDA graph of ten (no host launch cost between
         # them; a step that waits for the other ranks, the reductions, still does)
@@ -778,8 +796,17 @@ def run_b200(args) -> None:
         counts = qmm.set_splits([(nout[n], kin[n]) for n in names], GS)
         splits.update({n: (qmm.split_k(nout[n], kin[n], GS, args.sk_target) if args.sk_target else c) for n, c in zip(names, counts)})
     row_parallel = ("o_proj", "down_proj") if world > 1 else ()
-    peer = args.reduce == "peer"                             # the one-launch reduction over peer memory, or NCCL + a sum kernel
-    reducers = {name: tp.PeerReducer(rows * nout[name], device=dev) for name in row_parallel} if peer else {}
+    peer = args.reduce == "peer" and world > 1               # the one-launch reduction over peer memory, or NCCL + a sum kernel
+    reducers = {}
+    if peer:
+        try:
+            reducers = {name: tp.PeerReducer(rows * nout[name], device=dev) for name in row_parallel}
+            made = 1
+        except Exception:                                    # noqa: BLE001 - a box that refuses peer mappings: collectives
+            made = 0
+        agree = torch.tensor([made], device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        peer = bool(int(agree.item()))
     partial = {name: (reducers[name].partial((rows, nout[name]), torch.float32) if peer else
                       torch.empty((rows, nout[name]), dtype=torch.float32, device=dev)) for name in row_parallel}
     reduced = {}
@@ -809,6 +836,17 @@ def run_b200(args) -> None:
         for i in range(max(args.warmup, 3)):                 # eager warm-up (also the first, configuring, calls)
             step(i, False)
     barrier()
+    if peer:
+        # a peer that never answers costs a second a wait: find that out in the warm-up, not in the timed graph
+        code = torch.tensor([_lib.device_error(dev_y["q_proj"])], device=dev)
+        dist.all_reduce(code, op=dist.ReduceOp.MAX)
+        if int(code.item()):
+            peer = False
+            partial = {name: torch.empty((rows, nout[name]), dtype=torch.float32, device=dev) for name in row_parallel}
+            with torch.cuda.stream(stream):
+                for i in range(3):
+                    step(i, False)
+            barrier()
 
     # programmatic dependent launch between this library's kernels; NCCL's kernels in between rule it out
     pdl = not args.no_pdl and (world == 1 or peer)
@@ -1031,6 +1069,27 @@ def run_case(args) -> None:
         torch.cuda.synchronize()
         print(json.dumps({"case": args.case, "rows": args.rows, "launches": 6, "max_abs": float(y.float().abs().max())}))
         return
+    if args.case == "moe_experts":                           # the routed experts of the MoE layer (128 experts, top 6)
+        from tensorfold_b200.cuda import experts
+
+        d, e, ni, top_k = 2688, 128, 1856, 6
+        one = lambda n, k, s: synthetic.affine_weight(n, k, BITS, GS, seed=s)
+        rep = lambda w: tuple(torch.stack([torch.roll(t, 7 * i + 1, 0) for i in range(e)]).to(dev) for t in w)
+        ex = experts.make([rep(one(ni, d, 1)), rep(one(ni, d, 2))], rep(one(d, ni, 3)), GS)
+        g = torch.Generator().manual_seed(4)
+        picks = torch.stack([torch.randperm(e, generator=g)[:top_k] for _ in range(args.rows)]).to(torch.int32).to(dev)
+        plan = experts.Plan(args.rows, top_k, e, dev, prefill=args.prefill)
+        experts.route(picks, plan)
+        x = synthetic.activations(args.rows, d, 0).to(dev)
+        act = torch.empty((args.rows * top_k, ni), dtype=torch.bfloat16, device=dev)
+        y = torch.empty((args.rows * top_k, d), dtype=torch.bfloat16 if args.prefill else torch.float32, device=dev)
+        for _ in range(3):
+            experts.gate_up(x, ex, plan, act, args.rows)
+            experts.down(act, ex, plan, y, args.rows)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "rows": args.rows, "prefill": args.prefill, "launches": 6,
+                          "items": int(plan.counts[0]), "max_abs": float(y.float().abs().max())}))
+        return
     n, k = synthetic.DENSE_27B[args.case]
     qs = []
     for i in range(3):
@@ -1051,7 +1110,8 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--no-pdl", action="store_true")
-    ap.add_argument("--case", default="", help="profiler case: run six launches of one projection (e.g. gate_proj) and exit")
+    ap.add_argument("--case", default="", help="profiler case: run six launches of one projection (e.g. gate_proj), of a set (qkv_set, gate_up_set) or "
+                    "of the routed experts (moe_experts) and exit")
     ap.add_argument("--prefill", action="store_true", help="with --case: the prefill arithmetic (tcgen05 kernel)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--reduce", default="peer", choices=("peer", "collectives"),

@@ -204,9 +204,10 @@ __global__ void __launch_bounds__(128) router_tiles_kernel(const __nv_bfloat16* 
 }
 
 // The same arithmetic from shared memory: a block of four warps takes 64 rows x 32 experts, 64 inputs a step, staged by
-// 16-byte cp.async copies into 128-byte rows with the chunk index xor-ed by the row (conflict-free ldmatrix), two
-// buffers.  Each (row, expert) accumulator sees the same m16n8k16 operands in the same order as in
-// router_tiles_kernel, so both give the same bits; this one reads x once per 32 experts instead of once per 16 and
+// 16-byte cp.async copies into 128-byte rows with the chunk index xor-ed by the row (conflict-free ldmatrix), four
+// buffers (one chunk in flight made every step wait a full trip to memory: 44 us for 2048 rows x 160 experts x 6144).
+// Each (row, expert) accumulator sees the same m16n8k16 operands in the same order as in router_tiles_kernel, so both
+// give the same bits; this one reads x once per 32 experts instead of once per 16 and
 // fetches fragments with ldmatrix instead of 4-byte global loads.
 __device__ __forceinline__ void router_ldm4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -214,44 +215,47 @@ __device__ __forceinline__ void router_ldm4(uint32_t (&r)[4], uint32_t addr) {
                : "r"(addr));
 }
 
+constexpr int ROUTER_BUFS = 4;                               // stages in flight: three chunks are on their way while one is used
+constexpr int ROUTER_STAGE = (64 + 32) * 128;                // 64 rows of x and 32 experts, 64 inputs (128 bytes) each
+
 __global__ void __launch_bounds__(128) router_tiles_staged_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int rows,
                                                                   int d, const __nv_bfloat16* __restrict__ w, int ne,
                                                                   float* __restrict__ out, int64_t ldo) {
-  __shared__ __align__(128) uint8_t sx[2][64 * 128];
-  __shared__ __align__(128) uint8_t sw[2][32 * 128];
+  extern __shared__ __align__(128) uint8_t router_smem[];    // [ROUTER_BUFS][x tile | expert tile]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int e0 = blockIdx.x * 32, r0 = blockIdx.y * 64;
   const int chunks = d / 64;
+  const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(router_smem));
   auto stage = [&](int c, int buf) {
+    const uint32_t sx = base + buf * ROUTER_STAGE, sw = sx + 64 * 128;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {                              // 64 rows x 8 pieces of 16 bytes
       const int p = tid + 128 * i, row = p >> 3, ch = p & 7;
       const __nv_bfloat16* src = x + static_cast<int64_t>(min(r0 + row, rows - 1)) * ldx + c * 64 + ch * 8;
-      const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(sx[buf] + row * 128 + ((ch ^ (row & 7)) << 4)));
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sx + row * 128 + ((ch ^ (row & 7)) << 4)), "l"(src) : "memory");
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {                              // 32 experts x 8 pieces
       const int p = tid + 128 * i, row = p >> 3, ch = p & 7;
       const __nv_bfloat16* src = w + static_cast<int64_t>(min(e0 + row, ne - 1)) * d + c * 64 + ch * 8;
-      const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(sw[buf] + row * 128 + ((ch ^ (row & 7)) << 4)));
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sw + row * 128 + ((ch ^ (row & 7)) << 4)), "l"(src) : "memory");
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
   };
   float acc[4][4] = {};
-  stage(0, 0);
+  // every iteration commits exactly one group (an empty one past the end), so "all but the last ROUTER_BUFS - 1 groups
+  // have landed" always means chunk c has
+#pragma unroll
+  for (int c = 0; c < ROUTER_BUFS - 1; ++c) {
+    if (c < chunks) stage(c, c);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   for (int c = 0; c < chunks; ++c) {
-    const int buf = c & 1;
-    if (c + 1 < chunks) {
-      stage(c + 1, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
-    const uint32_t xs = static_cast<uint32_t>(__cvta_generic_to_shared(sx[buf]));
-    const uint32_t ws = static_cast<uint32_t>(__cvta_generic_to_shared(sw[buf]));
+    const int buf = c % ROUTER_BUFS;
+    asm volatile("cp.async.wait_group %0;" ::"n"(ROUTER_BUFS - 2) : "memory");
+    __syncthreads();                                          // chunk c is visible; the buffer of chunk c - 1 is free
+    if (c + ROUTER_BUFS - 1 < chunks) stage(c + ROUTER_BUFS - 1, (c + ROUTER_BUFS - 1) % ROUTER_BUFS);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const uint32_t xs = base + buf * ROUTER_STAGE, ws = xs + 64 * 128;
 #pragma unroll
     for (int k16 = 0; k16 < 4; ++k16) {
       uint32_t a[4], b0[4], b1[4];
@@ -269,7 +273,6 @@ __global__ void __launch_bounds__(128) router_tiles_staged_kernel(const __nv_bfl
       router_mma(acc[2], a[0], a[1], a[2], a[3], b1[0], b1[1]);
       router_mma(acc[3], a[0], a[1], a[2], a[3], b1[2], b1[3]);
     }
-    __syncthreads();                                          // the buffer is staged again two steps on
   }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -524,7 +527,7 @@ int tf_moe_router_tiles(const void* x, int64_t ldx, int rows, int d, const void*
   const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
   if (d % 64 == 0 && ldx % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
     dim3 grid((ne + 31) / 32, (rows + 63) / 64);             // staged through shared memory: the same bits, faster
-    router_tiles_staged_kernel<<<grid, 128, 0, st>>>(xp, ldx, rows, d, wp, ne, out, ldo);
+    router_tiles_staged_kernel<<<grid, 128, ROUTER_BUFS * ROUTER_STAGE, st>>>(xp, ldx, rows, d, wp, ne, out, ldo);
   } else {
     dim3 grid((ne + 63) / 64, (rows + 15) / 16);
     router_tiles_kernel<<<grid, 128, 0, st>>>(xp, ldx, rows, d, wp, ne, out, ldo);

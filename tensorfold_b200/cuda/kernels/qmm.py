@@ -306,7 +306,11 @@ def fork_join(calls) -> None:
     read the same input, like q/k/v or gate/up).  The first runs on the current stream, the others on side streams that
     wait for everything already queued on it; the current stream then waits for all of them.  Works eagerly and under
     CUDA-graph capture (the waits become graph edges).  A decode-sized projection cannot fill the GPU on its own (its
-    launch, first-byte latency and slice reduction are fixed costs), so independent ones overlap nearly for free."""
+    launch, first-byte latency and slice reduction are fixed costs), so independent ones overlap nearly for free.
+
+    Tensors a thunk allocates belong to its side stream's pool: give the thunks preallocated outputs (``out=``) for
+    anything the main stream reads after the join, or call ``record_stream(main)`` on what they return; a tensor made
+    and consumed inside one thunk needs neither."""
 
     calls = list(calls)
     if len(calls) < 2:
