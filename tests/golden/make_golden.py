@@ -7,7 +7,12 @@ Run once where a checkout of the reference is available:
 It calls only pure-Python/torch-CPU functions of the reference (no GPU, no Triton launch): ``dequantize``, ``split_k``,
 ``bucket``, ``packed_shape``, ``input_slice``, ``max_items``, ``output_rows`` and ``sum_rank_partials``, and the expected
 expert plan ``want_plan`` of the reference's own test (tests/cuda/test_experts.py:107-115), taken out of that file by
-name because the module around it needs a GPU to import.  The outputs are
+name because the module around it needs a GPU to import.  The bodies of the Triton kernels ``_topk_rows`` and
+``_combine`` (cuda/moe.py:56-85,130-141) are run as plain Python over a small NumPy stand-in for ``tl`` (the way the
+reference's own tests/test_cuda_affine.py:36-78 runs its affine kernels without a GPU): the selection order, the tie
+rule, the normalisation, every rounding to bf16 and the shared slot are then the reference's own statements; only
+``exp`` is NumPy's instead of the GPU's.  The SwiGLU vectors follow the float64 formula of the reference's test
+(tests/cuda/test_experts.py:158-162) computed with torch.  The outputs are
 small and committed; the tests compare the CPU oracle (and, on a GPU, the kernels) against them, so nothing at test time
 needs the reference.
 """
@@ -107,6 +112,97 @@ def main(ref: str) -> None:
         out[f"plan_{tag}_picks"] = picks.numpy()
         out[f"plan_{tag}_items"] = np.asarray(items, dtype=np.int64).reshape(-1, 3)
         out[f"plan_{tag}_members"] = np.asarray(members, dtype=np.int64)
+
+    # ---- the Triton bodies of the router's top-k and of the combine, run over NumPy
+    def bf16(a):
+        u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+        r = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+        return r.view(np.float32)
+
+    class Arr(np.ndarray):
+        def to(self, dtype):
+            if dtype == "bf16":
+                return bf16(np.asarray(self, dtype=np.float32)).view(Arr)
+            return np.asarray(self).astype(dtype).view(Arr)
+
+    arr = lambda v: np.asarray(v).view(Arr)
+
+    class Ptr:
+        def __init__(self, values, offsets=0):
+            self.values, self.offsets = values.reshape(-1), offsets
+
+        def __add__(self, offsets):
+            return Ptr(self.values, self.offsets + offsets)
+
+    class TL:
+        int32, float32, bfloat16 = np.int32, np.float32, "bf16"
+        program = [0, 0]
+        constexpr = None
+        static_range = range
+
+        @staticmethod
+        def load(pointer, mask=True, other=0):
+            offsets, mask = np.broadcast_arrays(pointer.offsets, mask)
+            result = np.full(offsets.shape, other, dtype=pointer.values.dtype)
+            result[mask] = pointer.values[offsets[mask]]
+            return arr(result)
+
+        @staticmethod
+        def store(pointer, value, mask=True):
+            offsets, value, mask = np.broadcast_arrays(pointer.offsets, value, mask)
+            pointer.values[offsets[mask]] = value[mask]
+
+        program_id = classmethod(lambda cls, axis: cls.program[axis])
+        arange = staticmethod(lambda a, b: arr(np.arange(a, b)))
+        zeros = staticmethod(lambda shape, dtype: arr(np.zeros(shape, dtype=dtype)))
+        where = staticmethod(lambda c, a, b: arr(np.where(c, a, b)))
+        max = staticmethod(lambda a, axis: np.max(a, axis=axis))
+        min = staticmethod(lambda a, axis: np.min(a, axis=axis))
+        exp = staticmethod(lambda a: np.exp(np.float32(a), dtype=np.float32) if np.ndim(a) == 0 else arr(np.exp(a, dtype=np.float32)))
+
+    source = (Path(ref) / "src" / "tensorfold" / "cuda" / "moe.py").read_text()
+    bodies = [n for n in ast.parse(source).body if isinstance(n, ast.FunctionDef) and n.name in ("_topk_rows", "_combine")]
+    for fn in bodies:
+        fn.decorator_list = []
+        for a in fn.args.args:
+            a.annotation = None
+    scope = {"tl": TL}
+    exec(compile(ast.Module(body=bodies, type_ignores=[]), "moe_kernels_on_numpy", "exec"), scope)      # noqa: S102
+
+    rows, ne, top_k = 24, 128, 6
+    logits = (torch.randn((rows, ne + 1), generator=g) * 2).numpy().astype(np.float32)
+    logits[0, 7] = logits[0, 3] = logits[0].max() + 1           # the largest logit twice: the lower id comes first
+    logits[1, 100:104] = logits[1, :100].max() + 0.5            # four equal logits among the chosen
+    logits[2, :] = 0.25                                         # all equal: ids 0 .. top_k - 1
+    pick = np.zeros((rows, top_k + 1), dtype=np.int32)
+    wts = np.zeros((rows, top_k + 1), dtype=np.float32)
+    next_pow2 = lambda v: 1 << (v - 1).bit_length()
+    for r in range(rows):
+        TL.program = [r, 0]
+        scope["_topk_rows"](Ptr(logits), Ptr(pick), Ptr(wts), NE=ne, NL=ne + 1, TOPK=top_k, SLOTS=top_k + 1,
+                            BLOCK=next_pow2(ne + 1), SLOTP=next_pow2(top_k + 1))
+    out["topk_case"] = np.asarray([rows, ne, top_k], dtype=np.int64)
+    out["topk_logits"], out["topk_picks"], out["topk_wts"] = logits, pick, wts
+
+    crow, slots, dims = 5, top_k + 1, 700
+    y = (torch.randn((crow, slots, dims), generator=g)).numpy().astype(np.float32)
+    w = bf16((torch.rand((crow, slots), generator=g)).numpy())
+    cout = np.zeros((crow, dims), dtype=np.float32)
+    for r in range(crow):
+        for blk in range(-(-dims // 512)):
+            TL.program = [r, blk]
+            scope["_combine"](Ptr(y), Ptr(w), Ptr(cout), S=slots, D=dims, BLOCK=512)
+    out["combine_y"], out["combine_w"], out["combine_out"] = y, w, cout
+
+    # ---- SwiGLU as the reference's test states it in float64 (tests/cuda/test_experts.py:158-162)
+    gv = (torch.randn((6, 64), generator=g) * 3).float()
+    uv = (torch.randn((6, 64), generator=g) * 3).float()
+    for tag, limit in (("", 0.0), ("_limit", 2.5)):
+        gg, uu = (t.to(torch.bfloat16).double() for t in (gv, uv))
+        if limit:
+            gg, uu = gg.clamp(max=limit), uu.clamp(-limit, limit)
+        out["swiglu_out" + tag] = ((gg * torch.sigmoid(gg)).to(torch.bfloat16).double() * uu).numpy()
+    out["swiglu_g"], out["swiglu_u"] = gv.numpy(), uv.numpy()
 
     dest = Path(__file__).with_name("reference_golden.npz")
     np.savez_compressed(dest, **out)

@@ -51,8 +51,27 @@ def test_router_and_topk_match_the_oracle():
     picks, wts = omoe.select_rows(lg.cpu().numpy(), k, e, shared=True)
     assert buf.pick.cpu().numpy().tolist() == picks.tolist()
     assert buf.pick[0, 0] == 3 and buf.pick[0, 1] == 7
+    # One bf16 spacing is allowed here and only here: the kernel's expf and NumPy's exp may differ in the last fp32 bit,
+    # which moves the bf16 rounding of a quotient that sits within 2^-16 of a tie.  The rule itself (order, ties,
+    # normalisation, roundings) is held to equality below, on the vectors made from the reference's kernel body.
     np.testing.assert_allclose(buf.wts.cpu().numpy(), wts, rtol=2 ** -7, atol=0)
     assert torch.equal(buf.wts, buf.wts.to(torch.bfloat16).float())                      # weights are bf16 values
+
+
+def test_top_k_and_combine_equal_the_references_kernel_bodies(golden):
+    """``tf_moe_topk`` and ``tf_moe_combine`` on the golden vectors (the reference's ``_topk_rows`` and ``_combine`` bodies
+    run over NumPy): same experts in the same order, same bf16 weights, same combined rows, bit for bit."""
+
+    rows, ne, top_k = map(int, golden["topk_case"])
+
+    class Cfg:
+        num_experts_per_tok, num_experts, moe_intermediate_size, hidden_size = top_k, ne, 64, 64
+    buf = moe.MoEBuffers(rows, Cfg, DEV)
+    moe.select_rows(torch.from_numpy(golden["topk_logits"]).to(DEV), buf, top_k, ne)
+    assert buf.pick.cpu().numpy().tolist() == golden["topk_picks"].tolist()
+    assert np.array_equal(buf.wts.cpu().numpy(), golden["topk_wts"])
+    y, w = torch.from_numpy(golden["combine_y"]).to(DEV), torch.from_numpy(golden["combine_w"]).to(DEV)
+    assert np.array_equal(moe.combine(y, w).float().cpu().numpy(), golden["combine_out"])
 
 
 def test_combine_is_slot_ordered_fp32():

@@ -138,3 +138,24 @@ def test_plan_equals_the_references_expected_plan(golden):
         assert items.tolist() == golden[f"plan_{tag}_items"].tolist()
         assert members.tolist() == golden[f"plan_{tag}_members"].tolist()
         assert seen == distinct
+
+
+def test_top_k_rule_matches_the_references_kernel_body(golden):
+    """``select_rows`` against the reference's ``_topk_rows`` body run over NumPy (tests/golden/make_golden.py): the
+    chosen experts, their order under ties, the renormalised bf16 weights and the sigmoid-gated shared slot, bit for bit."""
+
+    from oracle import moe as omoe
+
+    rows, ne, top_k = map(int, golden["topk_case"])
+    picks, wts = omoe.select_rows(golden["topk_logits"], top_k, ne, shared=True)
+    assert picks.tolist() == golden["topk_picks"].tolist()
+    assert picks[0, :2].tolist() == [3, 7] and picks[2, :top_k].tolist() == list(range(top_k))
+    assert np.array_equal(wts, golden["topk_wts"])
+
+
+def test_combine_and_swiglu_match_the_references_statements(golden):
+    from oracle import moe as omoe
+
+    assert np.array_equal(omoe.combine(golden["combine_y"], golden["combine_w"]), golden["combine_out"])
+    assert np.array_equal(omoe.silu_mul(golden["swiglu_g"], golden["swiglu_u"]), golden["swiglu_out"])
+    assert np.array_equal(omoe.silu_mul(golden["swiglu_g"], golden["swiglu_u"], 2.5), golden["swiglu_out_limit"])
