@@ -226,21 +226,34 @@ __global__ void __launch_bounds__(128) router_tiles_staged_kernel(const __nv_bfl
   const int e0 = blockIdx.x * 32, r0 = blockIdx.y * 64;
   const int chunks = d / 64;
   const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(router_smem));
+  // where this thread's six 16-byte pieces of a chunk come from and go to: worked out once (with one warp a scheduler,
+  // the address arithmetic of every chunk was most of the instructions the loop issued)
+  const __nv_bfloat16* xsrc[4];
+  const __nv_bfloat16* wsrc[2];
+  uint32_t xdst[4], wdst[2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {                                // 64 rows x 8 pieces of 16 bytes
+    const int p = tid + 128 * i, row = p >> 3, ch = p & 7;
+    xsrc[i] = x + static_cast<int64_t>(min(r0 + row, rows - 1)) * ldx + ch * 8;
+    xdst[i] = row * 128 + ((ch ^ (row & 7)) << 4);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {                                // 32 experts x 8 pieces
+    const int p = tid + 128 * i, row = p >> 3, ch = p & 7;
+    wsrc[i] = w + static_cast<int64_t>(min(e0 + row, ne - 1)) * d + ch * 8;
+    wdst[i] = 64 * 128 + row * 128 + ((ch ^ (row & 7)) << 4);
+  }
   auto stage = [&](int c, int buf) {
-    const uint32_t sx = base + buf * ROUTER_STAGE, sw = sx + 64 * 128;
+    const uint32_t sb = base + buf * ROUTER_STAGE;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {                              // 64 rows x 8 pieces of 16 bytes
-      const int p = tid + 128 * i, row = p >> 3, ch = p & 7;
-      const __nv_bfloat16* src = x + static_cast<int64_t>(min(r0 + row, rows - 1)) * ldx + c * 64 + ch * 8;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sx + row * 128 + ((ch ^ (row & 7)) << 4)), "l"(src) : "memory");
-    }
+    for (int i = 0; i < 4; ++i)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sb + xdst[i]), "l"(xsrc[i] + c * 64) : "memory");
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {                              // 32 experts x 8 pieces
-      const int p = tid + 128 * i, row = p >> 3, ch = p & 7;
-      const __nv_bfloat16* src = w + static_cast<int64_t>(min(e0 + row, ne - 1)) * d + c * 64 + ch * 8;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sw + row * 128 + ((ch ^ (row & 7)) << 4)), "l"(src) : "memory");
-    }
+    for (int i = 0; i < 2; ++i)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sb + wdst[i]), "l"(wsrc[i] + c * 64) : "memory");
   };
+  const uint32_t a_row = (16 * warp + (lane & 15)) * 128, a_half = lane >> 4, a_x = (lane & 15) & 7;
+  const uint32_t b_row = ((lane & 7) + 8 * (lane >> 4)) * 128, b_half = (lane >> 3) & 1, b_x = lane & 7;
   float acc[4][4] = {};
   // every iteration commits exactly one group (an empty one past the end), so "all but the last ROUTER_BUFS - 1 groups
   // have landed" always means chunk c has
@@ -259,15 +272,10 @@ __global__ void __launch_bounds__(128) router_tiles_staged_kernel(const __nv_bfl
 #pragma unroll
     for (int k16 = 0; k16 < 4; ++k16) {
       uint32_t a[4], b0[4], b1[4];
-      {
-        const int row = 16 * warp + (lane & 15), ch = 2 * k16 + (lane >> 4);
-        router_ldm4(a, xs + row * 128 + ((ch ^ (row & 7)) << 4));       // rows 0-7 / 8-15 x inputs 0-7 / 8-15 of the step
-      }
-      {
-        const int row = (lane & 7) + 8 * (lane >> 4), ch = 2 * k16 + ((lane >> 3) & 1);
-        router_ldm4(b0, ws + row * 128 + ((ch ^ (row & 7)) << 4));       // experts 0-15: (b0, b1) of two n8 tiles
-        router_ldm4(b1, ws + (row + 16) * 128 + ((ch ^ (row & 7)) << 4));   // experts 16-31 ((row + 16) & 7 == row & 7)
-      }
+      // rows 0-7 / 8-15 x inputs 0-7 / 8-15 of the step; experts 0-15 then 16-31 ((row + 16) & 7 == row & 7)
+      router_ldm4(a, xs + a_row + (((2 * k16 + a_half) ^ a_x) << 4));
+      router_ldm4(b0, ws + b_row + (((2 * k16 + b_half) ^ b_x) << 4));
+      router_ldm4(b1, ws + b_row + 16 * 128 + (((2 * k16 + b_half) ^ b_x) << 4));
       router_mma(acc[0], a[0], a[1], a[2], a[3], b0[0], b0[1]);
       router_mma(acc[1], a[0], a[1], a[2], a[3], b0[2], b0[3]);
       router_mma(acc[2], a[0], a[1], a[2], a[3], b1[0], b1[1]);
