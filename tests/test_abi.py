@@ -86,3 +86,32 @@ def test_c_abi_refuses_null_and_short_buffers_without_launching():
     assert b"tf_qmm" in lib.tf_last_error()
     # with everything in place the next refusal is the missing per-device set-up (no GPU here): still no launch
     assert call() != 0
+
+
+def test_peer_reduction_layout_and_refusals():
+    """The buffers of the one-launch reduction: flags first, then partial, result and the slots of flagged words, all
+    16-byte aligned and disjoint; the form follows the partial's size; bad arguments are refused before any launch."""
+
+    import ctypes
+
+    from tensorfold_b200.cuda import tp
+
+    lib = _lib.lib()
+    flags = lib.tf_peer_flag_bytes()
+    assert flags >= 18 * 128 and flags % 256 == 0
+    for world in (2, 4, 8):
+        for elements in (6144, 16 * 6144, 2048 * 6144):
+            f, part, out, ll, slot, total = tp.PeerReducer.layout(elements, world)
+            assert f == flags == part and out >= part + elements * 4 and ll >= out + elements * 4
+            assert all(v % 16 == 0 for v in (part, out, ll, slot)) and total == ll + 2 * world * slot
+            assert slot >= 2 * min(elements * 4, 1 << 19)          # a slot holds twice the largest flagged partial
+    table = (ctypes.c_void_p * 2)(4096, 8192)                      # never dereferenced: every call below is refused
+    call = lambda **kw: lib.tf_peer_reduce(table, kw.get("rank", 0), kw.get("world", 2), kw.get("part", 4096),
+                                           kw.get("out", 1 << 20), kw.get("total", 4096), 0, 0, kw.get("mode", 0),
+                                           kw.get("ll", 1 << 21), kw.get("slot", 1 << 16), 0, 0, None)
+    assert call(world=3) < 0 and call(rank=2) < 0 and call(total=7) < 0 and call(total=4100) < 0
+    assert call(part=64) < 0 and call(part=4100) < 0 and call(out=4096 + 64) < 0
+    assert call(mode=7) < 0 and call(mode=1, total=4104) < 0
+    assert call(mode=2, ll=4096) < 0 and call(mode=2, slot=1 << 10) < 0
+    assert lib.tf_peer_reduce(None, 0, 2, 4096, 1 << 20, 4096, 0, 0, 0, 0, 0, 0, 0, None) < 0
+    assert lib.tf_peer_alloc(16, None) < 0 and lib.tf_peer_export(None, None) < 0 and lib.tf_peer_open(None, None) < 0
