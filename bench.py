@@ -959,8 +959,11 @@ def run_b200(args) -> None:
                 e2e_graphs[i % ring].replay()
                 stream.synchronize()                         # the step's result is on the host
             e2e_s = time.perf_counter() - t0
-    if _lib.device_error(dev_y["q_proj"]) != 0:
-        raise RuntimeError("a kernel wait gave up during the benchmark")
+    code = torch.tensor([_lib.device_error(dev_y["q_proj"])], device=dev)
+    if world > 1:
+        dist.all_reduce(code, op=dist.ReduceOp.MAX)          # every rank learns of it, so every rank leaves together
+    if int(code.item()) != 0:
+        raise RuntimeError(f"a kernel wait gave up during the benchmark (device error {int(code.item())})")
 
     times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if world > 1:
