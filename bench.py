@@ -617,6 +617,9 @@ def moe_block_tp_bench(dev, rank: int, world: int, rows_list=(16, 2048)) -> dict
                  ("reduce_experts", lambda: reduce_of(state["p"]))]
         entry["phases_us"] = {}
         for name, fn in steps:                                   # in order: each step leaves the next one's inputs
+            if red is None and name.startswith("reduce"):        # one rank: nothing to reduce (and nothing to capture)
+                fn()
+                continue
             entry["phases_us"][name] = round(graph_timed(fn), 1)
         out[f"M{rows}"] = entry
     if red is not None:
