@@ -226,8 +226,11 @@ int tf_sum_ranks(const void* parts, int world, int64_t total, int parts_bf16, vo
  *   1  shares, for large ones: after a barrier a rank reads its 1/world share of every partial, stores the sum into
  *      every rank's result, and a second barrier ends the call.  total a multiple of 8 * world.
  *   0  as 1 but every rank reads all partials whole (total a multiple of 8).
- *   3, 4  the storing and the collecting half of mode 2 as launches of their own (a test driving all ranks from one
- *      process runs every rank's 3, then every rank's 4).
+ *   5  flagged words in two hops, for 4 or 8 ranks: a rank sends every other rank only that rank's 1/world share,
+ *      adds the shares it receives, and sends the finished share to every rank: about a fifth of mode 2's bytes at 8
+ *      ranks.  Same slots (ll_slot a multiple of 16 * world); total a multiple of 8 * world.
+ *   3, 4 and 6, 7, 8  the halves of modes 2 and 5 as launches of their own (a test driving all ranks from one process
+ *      runs every rank's 3 then every rank's 4; every rank's 6, then 7, then 8).
  * polls: limit of each wait on a peer (0: about a second); a wait that runs out sets device error 4 (tf_device_error)
  * and the kernel returns; the buffers must then be freed and made anew.  grid_cap > 0 bounds the blocks (testing).
  * No counterpart in the reference, which reduces its two ranks with an all-gather and a torch add

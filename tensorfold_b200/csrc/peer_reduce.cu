@@ -42,10 +42,13 @@ constexpr int PEER_THREADS = 512;              // share forms
 constexpr int LL_THREADS = 256;                // flagged words
 constexpr int FLAG_WORDS = 32;                 // flags sit 128 bytes apart
 constexpr int FLAG_READY = 0, FLAG_DONE = PEER_MAX, FLAG_CALLS = 2 * PEER_MAX, FLAG_ARRIVE = 2 * PEER_MAX + 1,
-              FLAG_LL_CALLS = 2 * PEER_MAX + 2, FLAG_LL_ARRIVE = 2 * PEER_MAX + 3;
+              FLAG_LL_CALLS = 2 * PEER_MAX + 2, FLAG_LL_ARRIVE = 2 * PEER_MAX + 3, FLAG_GO = 2 * PEER_MAX + 4;
 constexpr size_t FLAG_BYTES = 4096;
-static_assert((FLAG_LL_ARRIVE + 1) * FLAG_WORDS * 4 <= FLAG_BYTES, "the flags fit their page");
-enum Mode : int { MODE_ALL = 0, MODE_SHARES = 1, MODE_FLAGGED = 2, MODE_FLAGGED_PUSH = 3, MODE_FLAGGED_PULL = 4 };
+static_assert((FLAG_GO + 1) * FLAG_WORDS * 4 <= FLAG_BYTES, "the flags fit their page");
+enum Mode : int {
+  MODE_ALL = 0, MODE_SHARES = 1, MODE_FLAGGED = 2, MODE_FLAGGED_PUSH = 3, MODE_FLAGGED_PULL = 4,
+  MODE_HOPS = 5, MODE_HOPS_SEND = 6, MODE_HOPS_MIDDLE = 7, MODE_HOPS_COLLECT = 8,     // flagged words in two hops
+};
 
 struct PeerArgs {
   char* buf[PEER_MAX];                         // every rank's buffer as this process sees it (buf[rank] is local)
@@ -65,6 +68,14 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void add_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -163,9 +174,28 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_reduce_kernel(const PeerArg
   __syncthreads();
   const uint32_t target = s_target;
 
-  // this rank's partial was written by an earlier kernel of this stream: announce it, then wait for everyone's
-  if (blockIdx.x == 0 && tid < WORLD) add_release_sys(flag(s_buf[tid], FLAG_READY + a.rank), 1);
-  if (tid < WORLD && !wait_flag(flag(mine, FLAG_READY + tid), target, a.polls)) s_lost = 1;
+  // this rank's partial was written by an earlier kernel of this stream: block 0 announces it to every rank and waits
+  // for everyone's announcement, then lets the other blocks of this launch go through a flag in local memory (a few
+  // threads poll across the links instead of a few thousand)
+  if (blockIdx.x == 0) {
+    if (tid < WORLD) {
+      add_release_sys(flag(s_buf[tid], FLAG_READY + a.rank), 1);
+      if (!wait_flag(flag(mine, FLAG_READY + tid), target, a.polls)) s_lost = 1;
+    }
+    __syncthreads();
+    if (tid == 0) st_release_gpu(flag(mine, FLAG_GO), s_lost ? target | 0x80000000u : target);   // (top bit: the wait was lost)
+  } else {
+    if (tid == 0) {
+      bool seen = false;
+      for (uint32_t i = 0; i < a.polls && !seen; ++i) {
+        const uint32_t v = ld_acquire_gpu(flag(mine, FLAG_GO));
+        seen = (v & 0x7FFFFFFFu) == target;
+        if (seen && (v >> 31)) s_lost = 1;
+        if (!seen) __nanosleep(i < 64 ? 20 : 200);
+      }
+      if (!seen) s_lost = 1;
+    }
+  }
   __syncthreads();
   const bool lost = s_lost != 0;
 
@@ -189,23 +219,26 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_reduce_kernel(const PeerArg
     }
   }
 
-  // count the blocks in; the last one tells every rank that this rank has finished reading and writing
+  // count the blocks in; the last one tells every rank that this rank has finished reading and writing, and stays until
+  // every rank has said so (all shares have landed here, nobody still reads this rank's partial): the launch ends with it
   __threadfence_system();
   __syncthreads();
   if (tid == 0) s_last = atomicAdd(flag(mine, FLAG_ARRIVE), 1u) == gridDim.x - 1;
   __syncthreads();
   if (s_last) {
     __threadfence_system();
-    if (tid < WORLD) add_release_sys(flag(s_buf[tid], FLAG_DONE + a.rank), 1);
-    if (tid == 0) *flag(mine, FLAG_ARRIVE) = 0;
+    if (tid < WORLD) {
+      add_release_sys(flag(s_buf[tid], FLAG_DONE + a.rank), 1);
+      if (!lost && !wait_flag(flag(mine, FLAG_DONE + tid), target, a.polls)) s_lost = 1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      *flag(mine, FLAG_ARRIVE) = 0;
+      *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_CALLS)) = target;
+      __threadfence();
+    }
   }
-  if (!lost && tid < WORLD && !wait_flag(flag(mine, FLAG_DONE + tid), target, a.polls)) s_lost = 1;
-  __syncthreads();
   if (s_lost && tid == 0) atomicCAS(a.err, 0, ERR_WAIT_PEER);
-  if (s_last && tid == 0) {
-    *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_CALLS)) = target;
-    __threadfence();
-  }
 }
 
 // Flagged words.  A thread owns quads of four 4-byte words of the partial (four fp32 values, or eight bf16): it stores
@@ -295,6 +328,144 @@ __global__ void __launch_bounds__(LL_THREADS) peer_reduce_flagged_kernel(const P
   }
 }
 
+// Flagged words in two hops, for four and eight ranks: storing a whole partial into every rank's buffer costs
+// (world - 1) x 2 x its bytes on the links; here a rank sends each OTHER rank only that rank's 1/world share (hop one),
+// adds the shares it received to its own in rank order, rounds, and sends the finished share to every rank (hop two):
+// about (1 + out bytes / partial bytes) x 2 x the partial's bytes a rank, five times less at eight ranks.  Same flags,
+// epochs and parity as the one-hop form; the first ll_slot bytes of a parity's area hold hop one's slots (source rank r
+// at r * ll_slot / world), the next 2 * ll_slot bytes hop two's (owner s at s * 2 * ll_slot / world).
+template <int WORLD, bool BF16>
+__global__ void __launch_bounds__(LL_THREADS) peer_reduce_hops_kernel(const PeerArgs a) {
+  __shared__ uint32_t s_epoch;
+  __shared__ char* s_buf[WORLD];
+  const int tid = threadIdx.x;
+  char* mine = a.mine;
+#pragma unroll
+  for (int r = 0; r < WORLD; ++r)
+    if (tid == r) s_buf[r] = a.buf[r];
+  if (tid == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_LL_CALLS)) + 1;
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const bool send = a.mode == MODE_HOPS || a.mode == MODE_HOPS_SEND, middle = a.mode == MODE_HOPS || a.mode == MODE_HOPS_MIDDLE,
+             collect = a.mode == MODE_HOPS || a.mode == MODE_HOPS_COLLECT;
+  constexpr int VALUES = BF16 ? 8 : 4;                       // values a quad of four 4-byte words
+  const int64_t quads = (BF16 ? a.total / 2 : a.total) / 4, per = quads / WORLD;
+  const int vecs = (a.out_f32 ? VALUES : VALUES / 2) / 2;    // 16-byte vectors (two result words and their flags) a quad
+  const size_t area = a.ll_off + static_cast<size_t>(epoch & 1) * WORLD * a.ll_slot;
+  const size_t a_stride = a.ll_slot / WORLD, b_base = area + a.ll_slot, b_stride = 2 * a.ll_slot / WORLD;
+  const int64_t t0 = static_cast<int64_t>(blockIdx.x) * LL_THREADS + tid, tstep = static_cast<int64_t>(gridDim.x) * LL_THREADS;
+  bool lost = false;
+
+  if (send) {                                                // hop one: every quad another rank owns goes to that rank
+    for (int64_t q = t0; q < quads; q += tstep) {
+      const int owner = static_cast<int>(q / per);
+      if (owner == a.rank) continue;
+      const uint4 v = *reinterpret_cast<const uint4*>(mine + a.part_off + q * 16);
+      char* dst = s_buf[owner] + area + a.rank * a_stride + (q - owner * per) * 32;
+      st_volatile16(dst, make_uint4(v.x, epoch, v.y, epoch));
+      st_volatile16(dst + 16, make_uint4(v.z, epoch, v.w, epoch));
+    }
+  }
+  if (middle) {                                              // this rank's share: collect, add in rank order, round, hand on
+    for (int64_t ql = t0; ql < per; ql += tstep) {
+      const int64_t q = a.rank * per + ql;
+      const uint4 v = *reinterpret_cast<const uint4*>(mine + a.part_off + q * 16);
+      uint4 got[WORLD][2];
+      bool ok = false;
+      for (uint32_t i = 0; i < a.polls && !ok; ++i) {
+        ok = true;
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r)
+          if (r != a.rank) {
+            const char* src = mine + area + r * a_stride + ql * 32;
+            got[r][0] = ld_volatile16(src);
+            got[r][1] = ld_volatile16(src + 16);
+            ok &= got[r][0].y == epoch && got[r][0].w == epoch && got[r][1].y == epoch && got[r][1].w == epoch;
+          }
+        if (!ok && i >= 64) __nanosleep(i < 512 ? 50 : 500);
+      }
+      if (!ok) {
+        lost = true;
+        continue;
+      }
+      float acc[VALUES];
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r) {
+        const bool own = r == a.rank;
+        const uint32_t w[4] = {own ? v.x : got[r][0].x, own ? v.y : got[r][0].z, own ? v.z : got[r][1].x, own ? v.w : got[r][1].z};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if constexpr (BF16) {
+            const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xFFFF0000u);
+            acc[2 * j] = r == 0 ? lo : acc[2 * j] + lo;
+            acc[2 * j + 1] = r == 0 ? hi : acc[2 * j + 1] + hi;
+          } else {
+            acc[j] = r == 0 ? __uint_as_float(w[j]) : acc[j] + __uint_as_float(w[j]);
+          }
+        }
+      }
+      uint32_t word[VALUES];                                 // the quad of the result as it lies in memory
+      if (a.out_f32) {
+#pragma unroll
+        for (int j = 0; j < VALUES; ++j) word[j] = __float_as_uint(acc[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < VALUES / 2; ++j) {
+          const __nv_bfloat162 t = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+          word[j] = *reinterpret_cast<const uint32_t*>(&t);
+        }
+      }
+      uint32_t* o = reinterpret_cast<uint32_t*>(mine + a.out_off) + q * (2 * vecs);
+#pragma unroll
+      for (int j = 0; j < VALUES; ++j)
+        if (j < 2 * vecs) o[j] = word[j];
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r)
+        if (r != a.rank) {
+          char* dst = s_buf[r] + b_base + a.rank * b_stride + ql * (vecs * 16);
+#pragma unroll
+          for (int j = 0; j < VALUES / 2; ++j)
+            if (j < vecs) st_volatile16(dst + 16 * j, make_uint4(word[2 * j], epoch, word[2 * j + 1], epoch));
+        }
+    }
+  }
+  if (collect) {                                             // hop two's other end: the shares the other ranks finished
+    for (int64_t q = t0; q < quads; q += tstep) {
+      const int owner = static_cast<int>(q / per);
+      if (owner == a.rank) continue;
+      const char* src = mine + b_base + owner * b_stride + (q - owner * per) * (vecs * 16);
+      uint4 got[VALUES / 2];
+      bool ok = false;
+      for (uint32_t i = 0; i < a.polls && !ok; ++i) {
+        ok = true;
+#pragma unroll
+        for (int j = 0; j < VALUES / 2; ++j)
+          if (j < vecs) {
+            got[j] = ld_volatile16(src + 16 * j);
+            ok &= got[j].y == epoch && got[j].w == epoch;
+          }
+        if (!ok && i >= 64) __nanosleep(i < 512 ? 50 : 500);
+      }
+      if (!ok) {
+        lost = true;
+        continue;
+      }
+      uint32_t* o = reinterpret_cast<uint32_t*>(mine + a.out_off) + q * (2 * vecs);
+#pragma unroll
+      for (int j = 0; j < VALUES / 2; ++j)
+        if (j < vecs) o[2 * j] = got[j].x, o[2 * j + 1] = got[j].z;
+    }
+  }
+  if (lost) atomicCAS(a.err, 0, ERR_WAIT_PEER);
+  if (!collect) return;                                      // the halves of a test leave the epoch to the last one
+  __syncthreads();
+  if (tid == 0 && atomicAdd(flag(mine, FLAG_LL_ARRIVE), 1u) == gridDim.x - 1) {
+    *flag(mine, FLAG_LL_ARRIVE) = 0;
+    *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_LL_CALLS)) = epoch;
+    __threadfence();
+  }
+}
+
 struct DeviceFacts {
   int sms = 0, per_sm[3][2] = {};              // resident blocks of the share kernel by world (2, 4, 8) and partial type
 };
@@ -311,8 +482,17 @@ cudaError_t launch_world(const PeerArgs& a, int grid_cap, cudaStream_t s) {
   if (a.mode >= MODE_FLAGGED) {
     const int64_t quads = (a.parts_bf16 ? a.total / 2 : a.total) / 4;
     int64_t grid = (quads + LL_THREADS - 1) / LL_THREADS;
-    if (grid > 4 * f.sms) grid = 4 * f.sms;
+    if (grid > 2 * f.sms) grid = 2 * f.sms;                    // every block resident: threads wait for other ranks' threads
     if (grid_cap > 0 && grid > grid_cap) grid = grid_cap;
+    if (a.mode >= MODE_HOPS) {
+      if constexpr (WORLD >= 4) {
+        if (a.parts_bf16) peer_reduce_hops_kernel<WORLD, true><<<static_cast<unsigned>(grid), LL_THREADS, 0, s>>>(a);
+        else peer_reduce_hops_kernel<WORLD, false><<<static_cast<unsigned>(grid), LL_THREADS, 0, s>>>(a);
+        return cudaGetLastError();
+      } else {
+        return cudaErrorInvalidValue;
+      }
+    }
     if (a.parts_bf16) peer_reduce_flagged_kernel<WORLD, true><<<static_cast<unsigned>(grid), LL_THREADS, 0, s>>>(a);
     else peer_reduce_flagged_kernel<WORLD, false><<<static_cast<unsigned>(grid), LL_THREADS, 0, s>>>(a);
     return cudaGetLastError();
@@ -326,7 +506,9 @@ cudaError_t launch_world(const PeerArgs& a, int grid_cap, cudaStream_t s) {
     }
     const int64_t work = a.mode == MODE_SHARES ? a.total / a.world : a.total;
     int64_t grid = (work / 8 + PEER_THREADS - 1) / PEER_THREADS;
-    const int64_t resident = static_cast<int64_t>(per_sm) * f.sms;
+    // a thread that runs several pieces has the loads of one piece in flight while the stores of the piece before are
+    // still on their way: both directions of the links work at once (one block an SM: measured on eight ranks)
+    const int64_t resident = static_cast<int64_t>(a.mode == MODE_SHARES ? 1 : per_sm) * f.sms;
     if (grid > resident) grid = resident;
     if (grid_cap > 0 && grid > grid_cap) grid = grid_cap;
     if (grid < 1) grid = 1;
@@ -386,8 +568,8 @@ int tf_peer_close(void* ptr) {
 int tf_peer_reduce(void* const* bufs, int rank, int world, size_t part_off, size_t out_off, int64_t total, int parts_bf16,
                    int out_f32, int mode, size_t ll_off, size_t ll_slot, unsigned polls, int grid_cap, void* stream) {
   if (!bufs || (world != 2 && world != 4 && world != 8) || rank < 0 || rank >= world || total < 8 || mode < MODE_ALL ||
-      mode > MODE_FLAGGED_PULL)
-    return fail_moe(TF_ERR_ARG, "tf_peer_reduce: 2, 4 or 8 ranks, at least eight elements, a form 0..4");
+      mode > MODE_HOPS_COLLECT)
+    return fail_moe(TF_ERR_ARG, "tf_peer_reduce: 2, 4 or 8 ranks, at least eight elements, a form 0..8");
   if (total % (mode == MODE_SHARES ? 8 * world : 8)) return fail_moe(TF_ERR_ARG, "tf_peer_reduce: the elements split into pieces of eight (a rank)");
   if (part_off < FLAG_BYTES || out_off < FLAG_BYTES || part_off % 16 || out_off % 16)
     return fail_moe(TF_ERR_ALIGN, "tf_peer_reduce: offsets past the flags, 16-byte aligned");
@@ -398,6 +580,10 @@ int tf_peer_reduce(void* const* bufs, int rank, int world, size_t part_off, size
     const size_t top = part_off > out_off ? part_off + part_bytes : out_off + out_bytes;
     if (ll_off % 16 || ll_slot % 16 || ll_off < top || ll_slot < 2 * part_bytes)
       return fail_moe(TF_ERR_ARG, "tf_peer_reduce: the slots lie past partial and result and hold twice the partial each");
+  }
+  if (mode >= MODE_HOPS) {
+    if (world < 4 || total % (8 * world) || ll_slot % (16 * world))
+      return fail_moe(TF_ERR_ARG, "tf_peer_reduce: two hops take 4 or 8 ranks, elements and slots that split evenly over them");
   }
   int* err = device_error_word();
   if (!err) return fail_moe(TF_ERR_STATE, "tf_peer_reduce: tf_init has not run for the current device");

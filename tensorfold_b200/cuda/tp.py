@@ -59,12 +59,13 @@ class PeerReducer:
     """The rank-ordered all-reduce in one launch over peer memory (``tf_peer_reduce``): every rank owns one buffer that the
     other processes of the box map, producers write their partial straight into it (``partial``), and ``reduce`` returns
     the sum, the bits ``ordered_all_reduce`` gives.  Buffers: [flags | partial | result | slots].  Partials of up to
-    ``flagged_up_to`` bytes travel as flagged words (one trip over the links, no barrier); larger ones in shares between
-    two barriers (a rank sums 1/world and stores it to every rank).
+    ``flagged_up_to`` bytes travel as flagged words (no barrier; whole partials to every rank, or shares in two hops on
+    four and eight ranks); larger ones in shares between two barriers (a rank sums 1/world and stores it to every rank).
 
     The result tensor is a view of the buffer: it is overwritten by the next ``reduce``, and so is the partial."""
 
-    ALL, SHARES, FLAGGED, FLAGGED_PUSH, FLAGGED_PULL = range(5)
+    ALL, SHARES, FLAGGED, FLAGGED_PUSH, FLAGGED_PULL, HOPS, HOPS_SEND, HOPS_MIDDLE, HOPS_COLLECT = range(9)
+    HOPS_FROM = 64 << 10        # partial bytes from which four or eight ranks exchange shares in two hops of flagged words
 
     def __init__(self, elements: int, group=None, *, device=None, flagged_up_to: int = 1 << 19, bufs: list[int] | None = None,
                  rank: int | None = None) -> None:
@@ -107,7 +108,7 @@ class PeerReducer:
 
         flags = int(_lib.lib().tf_peer_flag_bytes())
         room = (-(-elements * 4 // 256)) * 256
-        slot = 2 * min(room, (-(-flagged_up_to // 256)) * 256)
+        slot = 2 * min(room, (-(-flagged_up_to // 256)) * 256)        # (a multiple of 512: splits into 16-byte pieces a rank)
         ll_off = flags + 2 * room
         return flags, flags, flags + room, ll_off, slot, ll_off + 2 * world * slot
 
@@ -136,7 +137,8 @@ class PeerReducer:
         if self.force is not None:
             return self.force
         if n * itemsize <= self.flagged_up_to:
-            return self.FLAGGED
+            two_hops = self.world >= 4 and n * itemsize >= self.HOPS_FROM and n % (8 * self.world) == 0
+            return self.HOPS if two_hops else self.FLAGGED
         return self.SHARES if n % (8 * self.world) == 0 else self.ALL
 
     def reduce(self, part: torch.Tensor, dtype: torch.dtype = torch.bfloat16, *, polls: int = 0, grid_cap: int = 0) -> torch.Tensor:

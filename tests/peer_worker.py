@@ -73,7 +73,10 @@ def main() -> None:
             g = torch.Generator().manual_seed(1000 * rank + shape[0])
             part = (torch.randn(shape, generator=g) * 2).to(dtype).cuda()
             want = tp.ordered_all_reduce(part)
-            forms = [red.ALL, red.SHARES] + ([red.FLAGGED] if part.numel() * part.element_size() <= red.flagged_up_to else [])
+            small = part.numel() * part.element_size() <= red.flagged_up_to
+            forms = [red.ALL, red.SHARES] + ([red.FLAGGED] if small else [])
+            if small and world >= 4 and part.numel() % (8 * world) == 0:
+                forms.append(red.HOPS)
             for form in forms + forms:                          # repeated calls reuse the buffers and keep the flags counting
                 red.force = form
                 home = red.partial(shape, dtype)

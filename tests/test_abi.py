@@ -111,7 +111,7 @@ def test_peer_reduction_layout_and_refusals():
                                            kw.get("ll", 1 << 21), kw.get("slot", 1 << 16), 0, 0, None)
     assert call(world=3) < 0 and call(rank=2) < 0 and call(total=7) < 0 and call(total=4100) < 0
     assert call(part=64) < 0 and call(part=4100) < 0 and call(out=4096 + 64) < 0
-    assert call(mode=7) < 0 and call(mode=1, total=4104) < 0
+    assert call(mode=9) < 0 and call(mode=1, total=4104) < 0 and call(mode=5) < 0
     assert call(mode=2, ll=4096) < 0 and call(mode=2, slot=1 << 10) < 0
     assert lib.tf_peer_reduce(None, 0, 2, 4096, 1 << 20, 4096, 0, 0, 0, 0, 0, 0, 0, None) < 0
     assert lib.tf_peer_alloc(16, None) < 0 and lib.tf_peer_export(None, None) < 0 and lib.tf_peer_open(None, None) < 0

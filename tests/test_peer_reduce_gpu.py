@@ -44,18 +44,19 @@ def test_both_forms_give_the_rank_ordered_sum(world, part_dtype):
         parts = [(torch.randn(shape, generator=g) * 3).to(part_dtype).to(DEV) for _ in range(world)]
         for out_dtype in (torch.bfloat16, torch.float32):
             want = distributed.sum_rank_partials(parts, out_dtype)
-            for form in (R.ALL, R.SHARES, R.FLAGGED):            # every rank sums all; a rank sums its share for all; flagged words
+            forms = (R.ALL, R.SHARES, R.FLAGGED) + ((R.HOPS,) if world >= 4 else ())
+            for form in forms:             # every rank sums all; a rank sums its share for all; flagged words in one hop, in two
                 outs = []
                 for r, red in enumerate(ranks):
                     red.partial(shape, part_dtype).copy_(parts[r])
                     red._view(red.out_off, shape, out_dtype).zero_()
                 torch.cuda.synchronize()
-                halves = (R.FLAGGED_PUSH, R.FLAGGED_PULL) if form == R.FLAGGED else (form,)
+                halves = {R.FLAGGED: (R.FLAGGED_PUSH, R.FLAGGED_PULL), R.HOPS: (R.HOPS_SEND, R.HOPS_MIDDLE, R.HOPS_COLLECT)}.get(form, (form,))
                 for half in halves:                              # all ranks store their words before any rank collects
                     for red in ranks:
                         red.force = half
                         out = red.reduce(red.partial(shape, part_dtype), out_dtype, grid_cap=3 if form == R.ALL else 0)
-                        if half != R.FLAGGED_PUSH:
+                        if half == halves[-1]:
                             outs.append(out)
                 torch.cuda.synchronize()
                 for r, o in enumerate(outs):
@@ -111,7 +112,8 @@ def test_bad_arguments_launch_nothing():
     assert refused(part_off=0) < 0 and refused(part_off=4104) < 0
     assert refused(out_off=4096 + 1024) < 0                       # the result would overlap the partial
     assert refused(total=4104, mode=1) < 0                        # does not split into pieces of eight a rank
-    assert refused(mode=5) < 0 and refused(mode=2, ll_slot=1 << 14) < 0 and refused(mode=2, ll_off=4096) < 0
+    assert refused(mode=9) < 0 and refused(mode=2, ll_slot=1 << 14) < 0 and refused(mode=2, ll_off=4096) < 0
+    assert refused(mode=5) < 0                                    # two hops need four ranks
     torch.cuda.synchronize()
 
 
