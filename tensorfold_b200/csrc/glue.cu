@@ -7,7 +7,6 @@
 #include <stdint.h>
 
 #include "../../include/tensorfold_b200.h"
-#include "tf_ptx.cuh"
 
 namespace tf {
 
@@ -56,7 +55,6 @@ __global__ void __launch_bounds__(GLUE_THREADS) add_rmsnorm_kernel(const __nv_bf
                                                                    const __nv_bfloat16* __restrict__ w, int d, float eps,
                                                                    __nv_bfloat16* __restrict__ h, __nv_bfloat16* __restrict__ y,
                                                                    float* __restrict__ xs, int gs) {
-  chain_entry();
   __shared__ float warp_ss[GLUE_THREADS / 32];
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pieces = d / 8, rounds = (pieces + GLUE_THREADS - 1) / GLUE_THREADS;
@@ -112,7 +110,6 @@ __global__ void __launch_bounds__(GLUE_THREADS) add_rmsnorm_kernel(const __nv_bf
 __global__ void __launch_bounds__(GLUE_THREADS) swiglu_kernel(const __nv_bfloat16* __restrict__ gate,
                                                               const __nv_bfloat16* __restrict__ up, int n,
                                                               __nv_bfloat16* __restrict__ out, float* __restrict__ xs, int gs) {
-  chain_entry();
   const int row = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
   const int pieces = n / 8, lanes = gs / 8;
   const int c = blockIdx.x * GLUE_THREADS + tid;
@@ -146,10 +143,10 @@ int tf_add_rmsnorm(const void* x, const void* r, const void* w, int rows, int d,
   if (d % gs) return fail_moe(TF_ERR_ARG, "tf_add_rmsnorm: the row length must be a multiple of the group");
   if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (r && (!aligned16(r) || !aligned16(h))))
     return fail_moe(TF_ERR_ALIGN, "tf_add_rmsnorm: tensors must be 16-byte aligned");
-  const cudaError_t e = launch_chained(
-      add_rmsnorm_kernel, dim3(rows), dim3(GLUE_THREADS), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x),
-      static_cast<const __nv_bfloat16*>(r), static_cast<const __nv_bfloat16*>(w), d, eps, static_cast<__nv_bfloat16*>(r ? h : nullptr),
-      static_cast<__nv_bfloat16*>(y), xs, gs);
+  add_rmsnorm_kernel<<<rows, GLUE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(r), static_cast<const __nv_bfloat16*>(w), d, eps,
+      static_cast<__nv_bfloat16*>(r ? h : nullptr), static_cast<__nv_bfloat16*>(y), xs, gs);
+  const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_add_rmsnorm");
 }
 
@@ -159,9 +156,9 @@ int tf_swiglu(const void* gate, const void* up, int rows, int n, void* out, floa
   if (n % gs) return fail_moe(TF_ERR_ARG, "tf_swiglu: the row length must be a multiple of the group");
   if (!aligned16(gate) || !aligned16(up) || !aligned16(out)) return fail_moe(TF_ERR_ALIGN, "tf_swiglu: tensors must be 16-byte aligned");
   dim3 grid((n / 8 + GLUE_THREADS - 1) / GLUE_THREADS, rows);
-  const cudaError_t e = launch_chained(swiglu_kernel, grid, dim3(GLUE_THREADS), 0, static_cast<cudaStream_t>(stream),
-                                       static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), n,
-                                       static_cast<__nv_bfloat16*>(out), xs, gs);
+  swiglu_kernel<<<grid, GLUE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), n, static_cast<__nv_bfloat16*>(out), xs, gs);
+  const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_swiglu");
 }
 

@@ -8,7 +8,6 @@
 #include <cstdio>
 
 #include "../../include/tensorfold_b200.h"
-#include "tf_ptx.cuh"
 
 namespace tf {
 
@@ -120,7 +119,6 @@ __device__ void plan_scatter_block(const int* __restrict__ picks, int pairs, int
 __global__ void __launch_bounds__(PLAN_BLOCK) plan_kernel(const int* __restrict__ picks, int pairs, int experts, int tile,
                                                          int* members, int* items, int* counts, int* rank, int* hist,
                                                          int max_items, int nblk, int phase) {
-  chain_entry();
   __shared__ int shared[PLAN_MAX_EXPERTS + 128];
   if (phase == 0) {
     plan_rank_block(picks, pairs, experts, rank, hist, blockIdx.x, shared);
@@ -143,7 +141,6 @@ __global__ void __launch_bounds__(PLAN_BLOCK) plan_kernel(const int* __restrict_
 
 __global__ void router_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int rows, int d,
                               const __nv_bfloat16* __restrict__ w, int ne, float* __restrict__ out, int64_t ldo) {
-  chain_entry();
   const int lane = threadIdx.x & 31, e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), r = blockIdx.y;
   if (e >= ne || r >= rows) return;
   const __nv_bfloat16* xr = x + r * ldx;
@@ -178,7 +175,6 @@ __device__ __forceinline__ void router_mma(float (&c)[4], uint32_t a0, uint32_t 
 __global__ void __launch_bounds__(128) router_tiles_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int rows, int d,
                                                            const __nv_bfloat16* __restrict__ w, int ne,
                                                            float* __restrict__ out, int64_t ldo) {
-  chain_entry();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int e0 = (blockIdx.x * 4 + warp) * 16, r0 = blockIdx.y * 16;
   if (e0 >= ne) return;
@@ -225,7 +221,6 @@ constexpr int ROUTER_STAGE = (64 + 32) * 128;                // 64 rows of x and
 __global__ void __launch_bounds__(128) router_tiles_staged_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int rows,
                                                                   int d, const __nv_bfloat16* __restrict__ w, int ne,
                                                                   float* __restrict__ out, int64_t ldo) {
-  chain_entry();
   extern __shared__ __align__(128) uint8_t router_smem[];    // [ROUTER_BUFS][x tile | expert tile]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int e0 = blockIdx.x * 32, r0 = blockIdx.y * 64;
@@ -309,7 +304,6 @@ __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__floa
 // zero weight for every other slot (the shared slot among them), so the planner and the combine leave them out.
 __global__ void topk_kernel(const float* __restrict__ logits, int64_t ldl, int rows, int experts, int topk, int shared,
                             int first, int count, int* __restrict__ pick, float* __restrict__ wts) {
-  chain_entry();
   const int lane = threadIdx.x & 31, r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= rows) return;
   const float* l = logits + r * ldl;
@@ -368,7 +362,6 @@ __global__ void topk_kernel(const float* __restrict__ logits, int64_t ldl, int r
 template <bool YBF16>
 __global__ void combine_kernel(const void* __restrict__ y, const float* __restrict__ wts, int rows, int slots, int d,
                                __nv_bfloat16* __restrict__ out) {
-  chain_entry();
   const int r = blockIdx.y;
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
   if (r >= rows || c >= d) return;
@@ -399,7 +392,6 @@ __global__ void combine_kernel(const void* __restrict__ y, const float* __restri
 template <bool YBF16>
 __global__ void __launch_bounds__(128) combine_wide_kernel(const void* __restrict__ y, const float* __restrict__ wts, int rows,
                                                            int slots, int d, __nv_bfloat16* __restrict__ out) {
-  chain_entry();
   const int r = blockIdx.y;
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (r >= rows || c >= d) return;
@@ -452,11 +444,11 @@ int tf_moe_plan(const int* picks, int pairs, int experts, int tile, int* members
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int nblk = (pairs + PLAN_BLOCK - 1) / PLAN_BLOCK;
   if (nblk == 1) {
-    launch_chained(plan_kernel, dim3(1), dim3(PLAN_BLOCK), 0, s, picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, 1, -1);
+    plan_kernel<<<1, PLAN_BLOCK, 0, s>>>(picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, 1, -1);
   } else {
-    launch_chained(plan_kernel, dim3(nblk), dim3(PLAN_BLOCK), 0, s, picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, nblk, 0);
-    launch_chained(plan_kernel, dim3(1), dim3(PLAN_BLOCK), 0, s, picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, nblk, 1);
-    launch_chained(plan_kernel, dim3(nblk), dim3(PLAN_BLOCK), 0, s, picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, nblk, 2);
+    plan_kernel<<<nblk, PLAN_BLOCK, 0, s>>>(picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, nblk, 0);
+    plan_kernel<<<1, PLAN_BLOCK, 0, s>>>(picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, nblk, 1);
+    plan_kernel<<<nblk, PLAN_BLOCK, 0, s>>>(picks, pairs, experts, tile, members, items, counts, rank, hist, max_items, nblk, 2);
   }
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_plan");
@@ -525,9 +517,9 @@ int tf_moe_router(const void* x, int64_t ldx, int rows, int d, const void* w, in
   if (rows < 1 || d < 1 || ne < 1 || !x || !w || !out || ldx < d || ldo < ne) return fail_moe(TF_ERR_ARG, "tf_moe_router: bad arguments");
   if (rows > 65535) return fail_moe(TF_ERR_ARG, "tf_moe_router: too many rows");
   dim3 grid((ne + 7) / 8, rows);
-  const cudaError_t e = launch_chained(router_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream),
-                                       static_cast<const __nv_bfloat16*>(x), ldx, rows, d, static_cast<const __nv_bfloat16*>(w), ne,
-                                       out, ldo);
+  router_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x), ldx, rows, d,
+                                                                     static_cast<const __nv_bfloat16*>(w), ne, out, ldo);
+  const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_router");
 }
 
@@ -541,14 +533,14 @@ int tf_moe_router_tiles(const void* x, int64_t ldx, int rows, int d, const void*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
-  cudaError_t e;
   if (d % 64 == 0 && ldx % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
     dim3 grid((ne + 31) / 32, (rows + 63) / 64);             // staged through shared memory: the same bits, faster
-    e = launch_chained(router_tiles_staged_kernel, grid, dim3(128), ROUTER_BUFS * ROUTER_STAGE, st, xp, ldx, rows, d, wp, ne, out, ldo);
+    router_tiles_staged_kernel<<<grid, 128, ROUTER_BUFS * ROUTER_STAGE, st>>>(xp, ldx, rows, d, wp, ne, out, ldo);
   } else {
     dim3 grid((ne + 63) / 64, (rows + 15) / 16);
-    e = launch_chained(router_tiles_kernel, grid, dim3(128), 0, st, xp, ldx, rows, d, wp, ne, out, ldo);
+    router_tiles_kernel<<<grid, 128, 0, st>>>(xp, ldx, rows, d, wp, ne, out, ldo);
   }
+  const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_router_tiles");
 }
 
@@ -557,8 +549,9 @@ int tf_moe_topk(const float* logits, int64_t ldl, int rows, int experts, int top
   if (rows < 1 || experts < 1 || experts > 1024 || topk < 1 || topk > 32 || topk > experts || !logits || !pick || !wts ||
       ldl < experts + (shared ? 1 : 0))
     return fail_moe(TF_ERR_ARG, "tf_moe_topk: bad arguments (at most 1024 experts, top 32)");
-  const cudaError_t e = launch_chained(topk_kernel, dim3((rows + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream), logits, ldl,
-                                       rows, experts, topk, shared, 0, 0, pick, wts);
+  topk_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, ldl, rows, experts, topk, shared, 0, 0, pick,
+                                                                             wts);
+  const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_topk");
 }
 
@@ -567,8 +560,9 @@ int tf_moe_topk_local(const float* logits, int64_t ldl, int rows, int experts, i
   if (rows < 1 || experts < 1 || experts > 1024 || topk < 1 || topk > 32 || topk > experts || !logits || !pick || !wts ||
       ldl < experts || first < 0 || count < 1 || first + count > experts)
     return fail_moe(TF_ERR_ARG, "tf_moe_topk_local: bad arguments (at most 1024 experts, top 32, a range inside them)");
-  const cudaError_t e = launch_chained(topk_kernel, dim3((rows + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream), logits, ldl,
-                                       rows, experts, topk, shared, first, count, pick, wts);
+  topk_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, ldl, rows, experts, topk, shared, first,
+                                                                             count, pick, wts);
+  const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_topk_local");
 }
 
@@ -577,17 +571,15 @@ int tf_moe_combine(const void* y, int y_bf16, const float* wts, int rows, int sl
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (d % 8 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
     dim3 wide((d / 8 + 127) / 128, rows);
-    const cudaError_t e = y_bf16 ? launch_chained(combine_wide_kernel<true>, wide, dim3(128), 0, s, y, wts, rows, slots, d,
-                                                  static_cast<__nv_bfloat16*>(out))
-                                 : launch_chained(combine_wide_kernel<false>, wide, dim3(128), 0, s, y, wts, rows, slots, d,
-                                                  static_cast<__nv_bfloat16*>(out));
+    if (y_bf16) combine_wide_kernel<true><<<wide, 128, 0, s>>>(y, wts, rows, slots, d, static_cast<__nv_bfloat16*>(out));
+    else combine_wide_kernel<false><<<wide, 128, 0, s>>>(y, wts, rows, slots, d, static_cast<__nv_bfloat16*>(out));
+    const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_combine");
   }
   dim3 grid((d / 2 + 127) / 128 + 1, rows);
-  const cudaError_t e = y_bf16 ? launch_chained(combine_kernel<true>, grid, dim3(128), 0, s, y, wts, rows, slots, d,
-                                                static_cast<__nv_bfloat16*>(out))
-                               : launch_chained(combine_kernel<false>, grid, dim3(128), 0, s, y, wts, rows, slots, d,
-                                                static_cast<__nv_bfloat16*>(out));
+  if (y_bf16) combine_kernel<true><<<grid, 128, 0, s>>>(y, wts, rows, slots, d, static_cast<__nv_bfloat16*>(out));
+  else combine_kernel<false><<<grid, 128, 0, s>>>(y, wts, rows, slots, d, static_cast<__nv_bfloat16*>(out));
+  const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_moe_combine");
 }
 

@@ -287,27 +287,8 @@ __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v 
 
 // Programmatic dependent launch: wait for the grid this one depends on (no-op without the launch attribute), and
 // let the dependent grid start its own prologue.
-// Launch with programmatic stream serialisation: the kernel may be scheduled while the previous kernel of the stream is
-// still running.  Kernels launched this way call chain_entry() first: it lets THEIR successor be scheduled early and
-// then waits until everything before them in the stream has finished and its writes are visible, so the body runs in
-// stream order as always; what overlaps is the launch itself (a microsecond or two between short kernels).
-template <typename... KArgs, typename... Args>
-inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr, cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
-
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void chain_entry() {
-  pdl_launch_dependents();
-  pdl_wait();
-}
 
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
