@@ -231,7 +231,8 @@ int tf_sum_ranks(const void* parts, int world, int64_t total, int parts_bf16, vo
  *      ranks.  Same slots (ll_slot a multiple of 16 * world); total a multiple of 8 * world.
  *   3, 4 and 6, 7, 8  the halves of modes 2 and 5 as launches of their own (a test driving all ranks from one process
  *      runs every rank's 3 then every rank's 4; every rank's 6, then 7, then 8).
- * polls: limit of each wait on a peer (0: about a second); a wait that runs out sets device error 4 (tf_device_error)
+ * polls: limit of each wait on a peer (0: several seconds, more than ranks drift apart while they start up; tests pass a
+ * short one); a wait that runs out sets device error 4 (tf_device_error)
  * and the kernel returns; the buffers must then be freed and made anew.  grid_cap > 0 bounds the blocks (testing).
  * No counterpart in the reference, which reduces its two ranks with an all-gather and a torch add
  * (families/qwen3_5/cuda/distributed.py:249-284). */

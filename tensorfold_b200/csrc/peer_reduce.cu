@@ -186,8 +186,10 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_reduce_kernel(const PeerArg
     if (tid == 0) st_release_gpu(flag(mine, FLAG_GO), s_lost ? target | 0x80000000u : target);   // (top bit: the wait was lost)
   } else {
     if (tid == 0) {
+      // block 0 always sets the flag, after its own (bounded) waits on the other ranks: this wait gets several times
+      // their limit, so that it never gives up before block 0 has
       bool seen = false;
-      for (uint32_t i = 0; i < a.polls && !seen; ++i) {
+      for (uint64_t i = 0; i < 16ull * a.polls && !seen; ++i) {
         const uint32_t v = ld_acquire_gpu(flag(mine, FLAG_GO));
         seen = (v & 0x7FFFFFFFu) == target;
         if (seen && (v >> 31)) s_lost = 1;
@@ -594,7 +596,7 @@ int tf_peer_reduce(void* const* bufs, int rank, int world, size_t part_off, size
   }
   a.mine = a.buf[rank];
   a.rank = rank, a.world = world, a.part_off = part_off, a.out_off = out_off, a.ll_off = ll_off, a.ll_slot = ll_slot, a.total = total;
-  a.parts_bf16 = parts_bf16, a.out_f32 = out_f32, a.mode = mode, a.polls = polls ? polls : (1u << 20), a.err = err;
+  a.parts_bf16 = parts_bf16, a.out_f32 = out_f32, a.mode = mode, a.polls = polls ? polls : (1u << 23), a.err = err;
   const cudaStream_t s = static_cast<cudaStream_t>(stream);
   const cudaError_t e = world == 2 ? launch_world<2>(a, grid_cap, s) : world == 4 ? launch_world<4>(a, grid_cap, s) : launch_world<8>(a, grid_cap, s);
   return e == cudaSuccess ? TF_OK : cuda_fail_moe(e, "tf_peer_reduce");
