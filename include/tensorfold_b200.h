@@ -50,7 +50,8 @@ int tf_selftest_lost_wait(int polls, void* stream);
 /* Performance knobs that never change a result bit.  key "qmm_lanes": 128-column super-blocks a thread block streams side
  * by side (1, 2 or 4; 0 = default); "stream_lanes": the same for tf_qmm_set's persistent kernel; "stream_blocks": blocks
  * of that kernel an SM may hold (0 = as many as fit); "grouped_tiled": 1 runs tf_moe_experts through the tiled kernel
- * (one thread block a plan item and column block) instead of the persistent kernel's grouped form.  No counterpart
+ * (one thread block a plan item and column block) instead of the persistent kernel's grouped form; "peer_plain": 1 keeps
+ * tf_peer_reduce's share form on plain loads (no bulk copies into shared memory).  No counterpart
  * in the reference. */
 int tf_tune(const char* key, int value);
 

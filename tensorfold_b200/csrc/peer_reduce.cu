@@ -157,26 +157,14 @@ __device__ __forceinline__ void store8(const PeerArgs& a, char* buf, int64_t i, 
   }
 }
 
-template <int WORLD, bool BF16>
-__global__ void __launch_bounds__(PEER_THREADS) peer_reduce_kernel(const PeerArgs a) {
-  __shared__ uint32_t s_target;
-  __shared__ int s_lost, s_last;
-  __shared__ char* s_buf[WORLD];               // the buffers by a run-time index
+// The two ends of a launch of the share forms (called by every thread of every block; `s_lost`, `s_last` and `s_buf` live in
+// the block's shared memory).  shares_begin: this rank's partial was written by an earlier kernel of this stream: block 0
+// announces it to every rank and waits for everyone's announcement, then lets the other blocks of this launch go
+// through a flag in local memory (a few threads poll across the links instead of a few thousand).
+template <int WORLD>
+__device__ __forceinline__ void shares_begin(const PeerArgs& a, char* const* s_buf, uint32_t target, int& s_lost) {
   const int tid = threadIdx.x;
   char* mine = a.mine;
-#pragma unroll
-  for (int r = 0; r < WORLD; ++r)
-    if (tid == r) s_buf[r] = a.buf[r];
-  if (tid == 0) {
-    s_target = *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_CALLS)) + 1;
-    s_lost = 0;
-  }
-  __syncthreads();
-  const uint32_t target = s_target;
-
-  // this rank's partial was written by an earlier kernel of this stream: block 0 announces it to every rank and waits
-  // for everyone's announcement, then lets the other blocks of this launch go through a flag in local memory (a few
-  // threads poll across the links instead of a few thousand)
   if (blockIdx.x == 0) {
     if (tid < WORLD) {
       add_release_sys(flag(s_buf[tid], FLAG_READY + a.rank), 1);
@@ -199,6 +187,52 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_reduce_kernel(const PeerArg
     }
   }
   __syncthreads();
+}
+
+// shares_end: count the blocks in; the last one tells every rank that this rank has finished reading and writing, and
+// stays until every rank has said so (all shares have landed here, nobody still reads this rank's partial): the launch
+// ends with it.
+template <int WORLD>
+__device__ __forceinline__ void shares_end(const PeerArgs& a, char* const* s_buf, uint32_t target, bool lost, int& s_lost, int& s_last) {
+  const int tid = threadIdx.x;
+  char* mine = a.mine;
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(flag(mine, FLAG_ARRIVE), 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (tid < WORLD) {
+      add_release_sys(flag(s_buf[tid], FLAG_DONE + a.rank), 1);
+      if (!lost && !wait_flag(flag(mine, FLAG_DONE + tid), target, a.polls)) s_lost = 1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      *flag(mine, FLAG_ARRIVE) = 0;
+      *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_CALLS)) = target;
+      __threadfence();
+    }
+  }
+  if (s_lost && tid == 0) atomicCAS(a.err, 0, ERR_WAIT_PEER);
+}
+
+template <int WORLD, bool BF16>
+__global__ void __launch_bounds__(PEER_THREADS) peer_reduce_kernel(const PeerArgs a) {
+  __shared__ uint32_t s_target;
+  __shared__ int s_lost, s_last;
+  __shared__ char* s_buf[WORLD];               // the buffers by a run-time index
+  const int tid = threadIdx.x;
+  char* mine = a.mine;
+#pragma unroll
+  for (int r = 0; r < WORLD; ++r)
+    if (tid == r) s_buf[r] = a.buf[r];
+  if (tid == 0) {
+    s_target = *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_CALLS)) + 1;
+    s_lost = 0;
+  }
+  __syncthreads();
+  const uint32_t target = s_target;
+  shares_begin<WORLD>(a, s_buf, target, s_lost);
   const bool lost = s_lost != 0;
 
   if (!lost) {
@@ -220,27 +254,115 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_reduce_kernel(const PeerArg
       }
     }
   }
+  shares_end<WORLD>(a, s_buf, target, lost, s_lost, s_last);
+}
 
-  // count the blocks in; the last one tells every rank that this rank has finished reading and writing, and stays until
-  // every rank has said so (all shares have landed here, nobody still reads this rank's partial): the launch ends with it
-  __threadfence_system();
-  __syncthreads();
-  if (tid == 0) s_last = atomicAdd(flag(mine, FLAG_ARRIVE), 1u) == gridDim.x - 1;
-  __syncthreads();
-  if (s_last) {
-    __threadfence_system();
-    if (tid < WORLD) {
-      add_release_sys(flag(s_buf[tid], FLAG_DONE + a.rank), 1);
-      if (!lost && !wait_flag(flag(mine, FLAG_DONE + tid), target, a.polls)) s_lost = 1;
-    }
-    __syncthreads();
-    if (tid == 0) {
-      *flag(mine, FLAG_ARRIVE) = 0;
-      *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_CALLS)) = target;
-      __threadfence();
-    }
+// The share form with bulk copies: a block brings 4 KB of every rank's partial into its shared memory with one bulk
+// copy a rank (three such stages in flight), adds from there and stores the sums to every rank.  Plain loads over the
+// links are bounded by the outstanding misses an SM may have (16-byte loads moved about 450 GB/s a direction on eight
+// ranks); a bulk copy keeps whole kilobytes in flight per request.
+constexpr int BULK_THREADS = 256, BULK_CHUNK = 4096, BULK_STAGES = 3;
+
+template <int WORLD, bool BF16>
+__global__ void __launch_bounds__(BULK_THREADS) peer_reduce_bulk_kernel(const PeerArgs a) {
+  extern __shared__ __align__(128) uint8_t bulk_smem[];       // [stage][rank][4 KB], then a barrier a stage and the abort word
+  __shared__ uint32_t s_target;
+  __shared__ int s_lost, s_last;
+  __shared__ char* s_buf[WORLD];
+  const int tid = threadIdx.x, lane = tid & 31;
+  char* mine = a.mine;
+  const uint32_t base32 = smem_addr(bulk_smem);
+  const uint32_t full32 = base32 + BULK_STAGES * WORLD * BULK_CHUNK, abort32 = full32 + 8 * BULK_STAGES;
+#pragma unroll
+  for (int r = 0; r < WORLD; ++r)
+    if (tid == r) s_buf[r] = a.buf[r];
+  if (tid == 0) {
+    s_target = *reinterpret_cast<volatile uint32_t*>(flag(mine, FLAG_CALLS)) + 1;
+    s_lost = 0;
+    for (int i = 0; i < BULK_STAGES; ++i)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full32 + 8 * i), "r"(1) : "memory");
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(abort32), "r"(0) : "memory");
+    mbar_fence_init();
   }
-  if (s_lost && tid == 0) atomicCAS(a.err, 0, ERR_WAIT_PEER);
+  __syncthreads();
+  const uint32_t target = s_target;
+  shares_begin<WORLD>(a, s_buf, target, s_lost);
+  const bool lost = s_lost != 0;
+
+  if (!lost) {
+    constexpr int ESIZE = BF16 ? 2 : 4, VALUES = 16 / ESIZE;  // a thread's piece: 16 bytes of every rank's chunk
+    const int64_t share_bytes = a.total / WORLD * ESIZE, chunks = share_bytes / BULK_CHUNK;
+    const size_t in0 = a.part_off + static_cast<size_t>(a.rank) * share_bytes;
+    const int n_mine = blockIdx.x < chunks ? static_cast<int>((chunks - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+    auto issue = [&](int j) {                                 // thread 0: the block's j-th chunk, one bulk copy a rank
+      const int st = j % BULK_STAGES;
+      const size_t at = in0 + (static_cast<size_t>(blockIdx.x) + static_cast<size_t>(j) * gridDim.x) * BULK_CHUNK;
+      mbar32_expect_tx(full32 + 8 * st, WORLD * BULK_CHUNK);
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r) bulk_load32(base32 + (st * WORLD + r) * BULK_CHUNK, a.buf[r] + at, BULK_CHUNK, full32 + 8 * st);
+    };
+    if (tid == 0)
+      for (int j = 0; j < BULK_STAGES && j < n_mine; ++j) issue(j);
+    bool dead = false;
+    for (int j = 0; j < n_mine; ++j) {
+      const int st = j % BULK_STAGES;
+      if (!dead && !mbar32_wait(full32 + 8 * st, (j / BULK_STAGES) & 1, abort32)) {
+        dead = true;                                          // (the other warps see the abort word and give up as well)
+        if (lane == 0) {
+          asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort32), "r"(1) : "memory");
+          s_lost = 1;
+        }
+      }
+      if (!dead) {
+        float acc[VALUES];
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) {
+          const uint4 q = lds128(base32 + (st * WORLD + r) * BULK_CHUNK + tid * 16);
+          const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if constexpr (BF16) {
+              const float lo = __uint_as_float(u[e] << 16), hi = __uint_as_float(u[e] & 0xFFFF0000u);
+              acc[2 * e] = r == 0 ? lo : acc[2 * e] + lo;
+              acc[2 * e + 1] = r == 0 ? hi : acc[2 * e + 1] + hi;
+            } else {
+              acc[e] = r == 0 ? __uint_as_float(u[e]) : acc[e] + __uint_as_float(u[e]);
+            }
+          }
+        }
+        // element index of the piece inside the whole partial
+        const int64_t i = (static_cast<int64_t>(a.rank) * share_bytes +
+                           (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(j) * gridDim.x) * BULK_CHUNK + tid * 16) / ESIZE;
+        if (a.out_f32) {
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r) {
+            char* o = a.buf[r] + a.out_off + i * 4;
+            st_peer16(o, make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3])));
+            if constexpr (BF16)
+              st_peer16(o + 16, make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]), __float_as_uint(acc[6]), __float_as_uint(acc[7])));
+          }
+        } else {
+          uint32_t u[VALUES / 2];
+#pragma unroll
+          for (int e = 0; e < VALUES / 2; ++e) {
+            const __nv_bfloat162 t = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+            u[e] = *reinterpret_cast<const uint32_t*>(&t);
+          }
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r) {
+            char* o = a.buf[r] + a.out_off + i * 2;
+            if constexpr (BF16) st_peer16(o, make_uint4(u[0], u[1], u[2], u[3]));
+            else asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(o), "r"(u[0]), "r"(u[1]) : "memory");
+          }
+        }
+      }
+      __syncthreads();                                        // every thread has read the stage: it may be filled again
+      if (tid == 0 && !dead && j + BULK_STAGES < n_mine) issue(j + BULK_STAGES);
+    }
+    if (dead)
+      for (int i = 0; i < 64; ++i) __nanosleep(20000);        // copies in flight land before the shared memory is released
+  }
+  shares_end<WORLD>(a, s_buf, target, lost, s_lost, s_last);
 }
 
 // Flagged words.  A thread owns quads of four 4-byte words of the partial (four fp32 values, or eight bf16): it stores
@@ -468,6 +590,8 @@ __global__ void __launch_bounds__(LL_THREADS) peer_reduce_hops_kernel(const Peer
   }
 }
 
+int g_peer_plain = 0;                            // 1: the share form with plain loads only (tuning, tests)
+
 struct DeviceFacts {
   int sms = 0, per_sm[3][2] = {};              // resident blocks of the share kernel by world (2, 4, 8) and partial type
 };
@@ -499,6 +623,26 @@ cudaError_t launch_world(const PeerArgs& a, int grid_cap, cudaStream_t s) {
     else peer_reduce_flagged_kernel<WORLD, false><<<static_cast<unsigned>(grid), LL_THREADS, 0, s>>>(a);
     return cudaGetLastError();
   }
+  const int64_t share_bytes = a.total / WORLD * (a.parts_bf16 ? 2 : 4);
+  if (a.mode == MODE_SHARES && share_bytes % BULK_CHUNK == 0 && !g_peer_plain) {
+    constexpr int SMEM = BULK_STAGES * WORLD * BULK_CHUNK + 8 * BULK_STAGES + 16;
+    auto go = [&](auto kernel) -> cudaError_t {
+      static bool configured[64][2] = {};                      // (both kernels have one pointer type: index by the partial's type)
+      if (!configured[dev][a.parts_bf16 ? 1 : 0]) {
+        cudaError_t q = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (q != cudaSuccess) return q;
+        configured[dev][a.parts_bf16 ? 1 : 0] = true;
+      }
+      // every block resident (the last one to finish signals for all): two blocks of 96 KB an SM at most
+      int64_t grid = share_bytes / BULK_CHUNK;
+      const int64_t resident = static_cast<int64_t>(SMEM > 100 * 1024 ? 1 : 2) * f.sms;
+      if (grid > resident) grid = resident;
+      if (grid_cap > 0 && grid > grid_cap) grid = grid_cap;
+      kernel<<<static_cast<unsigned>(grid), BULK_THREADS, SMEM, s>>>(a);
+      return cudaGetLastError();
+    };
+    return a.parts_bf16 ? go(peer_reduce_bulk_kernel<WORLD, true>) : go(peer_reduce_bulk_kernel<WORLD, false>);
+  }
   auto run = [&](auto kernel) -> cudaError_t {
     int& per_sm = f.per_sm[WORLD == 2 ? 0 : WORLD == 4 ? 1 : 2][a.parts_bf16 ? 1 : 0];
     if (!per_sm) {
@@ -521,6 +665,9 @@ cudaError_t launch_world(const PeerArgs& a, int grid_cap, cudaStream_t s) {
 }
 
 }  // namespace
+
+void peer_reduce_plain(int on) { g_peer_plain = on; }   // tf_tune("peer_plain", v)
+
 }  // namespace tf
 
 using namespace tf;

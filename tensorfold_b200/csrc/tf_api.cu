@@ -58,6 +58,7 @@ std::mutex g_init_mutex;
 }  // namespace
 
 cudaError_t prefill_configure();      // qmm_prefill.cu
+void peer_reduce_plain(int on);       // peer_reduce.cu
 cudaError_t moe_static_init(int device);   // moe.cu: the built-in plan scratch's address on that device
 int encode_rows(CUtensorMap* map, const void* x, int64_t ldx, int rows, int k, int box_rows);
 
@@ -424,6 +425,10 @@ int tf_tune(const char* key, int value) {
   }
   if (key != nullptr && std::string(key) == "stream_blocks" && value >= 0 && value <= 8) {
     g_stream_blocks = value;
+    return TF_OK;
+  }
+  if (key != nullptr && std::string(key) == "peer_plain" && (value == 0 || value == 1)) {
+    peer_reduce_plain(value);
     return TF_OK;
   }
   if (key != nullptr && std::string(key) == "grouped_tiled" && (value == 0 || value == 1)) {

@@ -68,6 +68,37 @@ def test_both_forms_give_the_rank_ordered_sum(world, part_dtype):
             _lib.lib().tf_peer_free(b)
 
 
+def test_bulk_copies_and_plain_loads_give_the_same_sums():
+    """The share form brings the partials in with bulk copies where a share splits into 4 KB pieces; with the tuning
+    switch it uses plain loads.  Same additions in the same order: same bits."""
+
+    world, shape = 4, (64, 1024)
+    ranks, bufs = local_ranks(world, shape[0] * shape[1])
+    try:
+        g = torch.Generator().manual_seed(9)
+        for part_dtype in (torch.bfloat16, torch.float32):
+            parts = [(torch.randn(shape, generator=g) * 3).to(part_dtype).to(DEV) for _ in range(world)]
+            got = {}
+            for plain in (0, 1):
+                _lib.check(_lib.lib().tf_tune(b"peer_plain", plain), "tune")
+                for r, red in enumerate(ranks):
+                    red.force = R.SHARES
+                    red.partial(shape, part_dtype).copy_(parts[r])
+                torch.cuda.synchronize()
+                outs = [red.reduce(red.partial(shape, part_dtype), torch.bfloat16) for red in ranks]
+                torch.cuda.synchronize()
+                got[plain] = outs[0].clone()
+                assert all(torch.equal(o, outs[0]) for o in outs)
+            assert torch.equal(got[0], got[1])
+            assert torch.equal(got[0], distributed.sum_rank_partials(parts))
+        assert _lib.device_error(parts[0]) == 0
+    finally:
+        _lib.lib().tf_tune(b"peer_plain", 0)
+        torch.cuda.synchronize()
+        for b in bufs:
+            _lib.lib().tf_peer_free(b)
+
+
 def test_a_missing_peer_ends_the_wait_with_an_error():
     """Rank 1 never calls: rank 0's launch gives up after its poll limit, reports error 4 and leaves the context usable."""
 
