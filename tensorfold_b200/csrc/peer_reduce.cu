@@ -1,16 +1,19 @@
 // Rank-ordered all-reduce of partial sums over peer memory (NVLink / NVSwitch), one launch a rank: the ranks' buffers are
 // mapped into every process; the partials of all ranks are added in rank order in fp32 ((p0 + p1) + p2 ...), rounded
 // once, and every rank ends with the same bits.  Generalises the two-rank rank0.float() + rank1.float() of
-// families/qwen3_5/cuda/distributed.py:249-284 (an all-gather and an add there).  Three forms:
+// families/qwen3_5/cuda/distributed.py:249-284 (an all-gather and an add there).  The forms:
 //
 //   flagged words (small partials)  a rank stores its partial into a slot of every other rank's buffer as 8-byte
 //       {data, epoch} words (16-byte stores of two such words; each half carries its own flag), then polls the slots
 //       of its own buffer until every word shows this call's epoch, and adds.  No barrier, no fence: one trip over the
 //       links.  Slots alternate with the parity of the epoch: a slot is rewritten two calls later, which the writer
 //       can only reach after this rank has sent its next partial, that is, after it has finished reading this one.
-//   shares (large partials)  ranks tell one another that their partials are in place, a rank reads its 1/world share of
-//       every partial with plain peer loads, adds, stores the sum into every rank's result, and the ranks tell one
-//       another that they are done (all shares have landed; nobody still reads this rank's partial).
+//   flagged words in two hops (four and eight ranks, partials from 64 KB)  the same words, but a rank sends every other
+//       rank only that rank's 1/world share, adds the shares it receives and sends the finished share to every rank.
+//   shares (large partials)  ranks tell one another that their partials are in place, a rank brings its 1/world share
+//       of every partial into shared memory with bulk copies (plain peer loads where a share does not split into 4 KB
+//       pieces), adds, stores the sum into every rank's result, and the ranks tell one another that they are done (all
+//       shares have landed; nobody still reads this rank's partial).
 //   all (testing, and totals that do not split)  as shares, but every rank reads every partial whole.
 //
 // Each rank's buffer starts with a page of 32-bit flags, 128 bytes apart: ready[r] and done[r] (how many reductions of
@@ -19,8 +22,8 @@
 // counting), and a count of the blocks of the running launch that have finished.  Every wait has a poll limit; a wait
 // that runs out sets ERR_WAIT_PEER in the device error word, the kernel skips its remaining waits and returns.
 //
-// In the share forms all blocks of a launch must be resident at once (the last one to finish signals for all): the grid
-// is bounded by the occupancy the runtime reports.
+// In the share forms all blocks of a launch must be resident at once (the last one to finish signals for all), and in
+// the flagged forms threads wait for other ranks' threads: the grids are bounded by what an SM holds.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
