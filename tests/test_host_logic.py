@@ -133,3 +133,21 @@ def test_default_split_is_shape_only_and_fills_the_lanes_once():
             assert 1 <= sk <= qmm.default_split(n, k)
             assert sk == 1 or (k // 64) // sk >= 6
             assert -(-n // 128) * sk * share <= qmm.LANES or sk == 1
+
+
+def test_decode_items_and_reduction_forms_follow_sizes_only():
+    """Load-time choices that never change a bit: pairs an item of the decode plan holds, and the form a reduction takes."""
+
+    from tensorfold_b200.cuda import experts, tp
+
+    assert experts.decode_tile(96, 128) == 8 and experts.decode_tile(16 * 9, 161) == 8      # few pairs an expert
+    assert experts.decode_tile(128 * 7, 128) == 16 and experts.decode_tile(513, 128) == 16
+    assert experts.max_items(96, 128, 8) == 96 + 12 and experts.max_items(2048 * 7, 129, 128) == 129 + 112
+    red = object.__new__(tp.PeerReducer)                       # the rule needs no buffers
+    red.force, red.flagged_up_to = None, 1 << 19
+    for world, n, itemsize, want in ((2, 16 * 6144, 4, tp.PeerReducer.FLAGGED), (8, 6144, 2, tp.PeerReducer.FLAGGED),
+                                     (8, 16 * 6144, 4, tp.PeerReducer.HOPS), (4, 16 * 5120, 2, tp.PeerReducer.HOPS),
+                                     (8, 2048 * 6144, 2, tp.PeerReducer.SHARES), (2, 256 * 6144, 2, tp.PeerReducer.SHARES),
+                                     (8, 16 * 6144 + 8, 4, tp.PeerReducer.FLAGGED), (8, 2048 * 6144 + 8, 2, tp.PeerReducer.ALL)):
+        red.world = world
+        assert red.form(n, itemsize) == want, (world, n, itemsize)
